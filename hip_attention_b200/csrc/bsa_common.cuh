@@ -1,0 +1,66 @@
+// Shared pieces of the block-sparse attention kernels: the key list of a query block and the
+// per-(row, key) admission rule.
+//
+// A query block attends three groups of keys, concatenated into one virtual list
+//   [ sink tokens | selected blocks (ks blocks of block_size_k tokens) | window tokens ]
+// which the kernels walk in tiles.  For a query row at position p (the block's largest position is
+// pmax) a key at position t is admitted when
+//   sink / selected entry ("far" keys):  t <= p - window
+//   window entry:                        p - window < t <= p
+// and a selected entry must also satisfy sink <= t <= pmax and t < T.  The two rules are disjoint,
+// so a token that appears in two groups is counted once.
+#pragma once
+#include "common.cuh"
+
+namespace hipattn {
+
+struct KeyList {
+  int n_sink, n_sel, n_win, w_start, total;
+  int pmax;
+  const int64_t* idx;  // selected block starts of this query block
+  int block_k, sink, T;
+};
+
+__device__ __forceinline__ KeyList make_key_list(const hipattn_bsa_params_t& p, int b, int h, int d, int pmin, int pmax) {
+  KeyList kl;
+  const int64_t n = (int64_t)b * p.H + h;
+  const int d_idx = (int)(((int64_t)d * p.block_size_q) / p.index_block_q);
+  kl.idx = p.indices + n * p.idx_stride_n + (int64_t)d_idx * p.idx_stride_d;
+  long long ks = p.ks[n * p.ks_stride_n + (int64_t)d_idx * p.ks_stride_d];
+  ks = ks < 0 ? 0 : (ks > p.K ? p.K : ks);
+  kl.block_k = p.block_size_k;
+  kl.sink = p.sink;
+  kl.T = p.T;
+  kl.pmax = pmax;
+  kl.n_sink = max(0, min(p.sink, pmax + 1));
+  kl.n_sel = (int)ks * p.block_size_k;
+  kl.w_start = max(0, pmin - p.window + 1);
+  kl.n_win = p.window > 0 ? max(0, pmax + 1 - kl.w_start) : 0;
+  kl.total = kl.n_sink + kl.n_sel + kl.n_win;
+  return kl;
+}
+
+// Position of entry j of the virtual list, or -1 when the entry admits no row.  *is_window tells
+// which admission rule applies.
+__device__ __forceinline__ int key_position(const KeyList& kl, int j, bool* is_window) {
+  *is_window = false;
+  if (j < 0 || j >= kl.total) return -1;
+  if (j < kl.n_sink) return j;
+  j -= kl.n_sink;
+  if (j < kl.n_sel) {
+    const long long start = kl.idx[j / kl.block_k];
+    const long long t = start + (j % kl.block_k);
+    if (t < kl.sink || t > kl.pmax || t >= kl.T) return -1;
+    return (int)t;
+  }
+  j -= kl.n_sel;
+  *is_window = true;
+  return kl.w_start + j;
+}
+
+__device__ __forceinline__ bool admits(int p_row, int t, bool is_window, int window) {
+  if (t < 0) return false;
+  return is_window ? (t > p_row - window && t <= p_row) : (t <= p_row - window);
+}
+
+}  // namespace hipattn

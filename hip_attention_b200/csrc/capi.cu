@@ -1,0 +1,135 @@
+// C ABI glue: error reporting, argument validation, kernel selection for attention, and the
+// log-sum-exp merge of partial outputs.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace hipattn {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int validate_tokens(const hipattn_tokens_t& t, int elem_bytes, int D, const char* name) {
+  const int64_t row_align = 16 / elem_bytes;
+  if (t.cache != nullptr) {
+    HIPATTN_REQUIRE(t.block_table && t.cache_seq_lens, HIPATTN_ERR_INVALID, "%s: paged cache without block_table / cache_seq_lens", name);
+    HIPATTN_REQUIRE(t.page_size > 0 && t.n_pages > 0 && t.table_width > 0, HIPATTN_ERR_INVALID,
+                    "%s: page_size %d, n_pages %lld, table_width %d must be positive", name, t.page_size,
+                    (long long)t.n_pages, t.table_width);
+    HIPATTN_REQUIRE(((uintptr_t)t.cache % 16) == 0 && t.stride_page % row_align == 0 && t.stride_off % row_align == 0 &&
+                        t.stride_ch % row_align == 0,
+                    HIPATTN_ERR_INVALID, "%s: cache rows must start on 16-byte boundaries", name);
+  } else {
+    HIPATTN_REQUIRE(t.dense != nullptr, HIPATTN_ERR_INVALID, "%s: neither a dense tensor nor a page pool was given", name);
+    HIPATTN_REQUIRE(((uintptr_t)t.dense % 16) == 0 && t.stride_b % row_align == 0 && t.stride_t % row_align == 0 &&
+                        t.stride_h % row_align == 0,
+                    HIPATTN_ERR_INVALID, "%s: rows must start on 16-byte boundaries", name);
+  }
+  HIPATTN_REQUIRE(D % row_align == 0, HIPATTN_ERR_INVALID, "%s: head dimension %d is not a multiple of 16 bytes", name, D);
+  return HIPATTN_OK;
+}
+
+int bsa_generic(const hipattn_bsa_params_t& p, cudaStream_t stream);
+int bsa_mma(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
+
+namespace {
+
+template <int DT>
+__global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_parts, int D,
+                             typename Elem<DT>::type* __restrict__ out, int64_t out_stride, float* __restrict__ lse_out) {
+  const int64_t row = blockIdx.x;
+  const float* lse = part_lse + row * n_parts;
+  float m = -INFINITY;
+  for (int s = 0; s < n_parts; ++s) m = fmaxf(m, lse[s]);
+  float tot = 0.f;
+  for (int s = 0; s < n_parts; ++s)
+    if (lse[s] > -INFINITY) tot += exp2f(lse[s] - m);
+  for (int e = threadIdx.x; e < D; e += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_parts; ++s)
+      if (lse[s] > -INFINITY) acc += exp2f(lse[s] - m) * part_o[(row * n_parts + s) * D + e];
+    out[row * out_stride + e] = Elem<DT>::from_f32(tot > 0.f ? acc / tot : 0.f);
+  }
+  if (lse_out && threadIdx.x == 0) lse_out[row] = tot > 0.f ? m + log2f(tot) : -INFINITY;
+}
+
+}  // namespace
+}  // namespace hipattn
+
+using namespace hipattn;
+
+extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream) {
+  HIPATTN_REQUIRE(p != nullptr, HIPATTN_ERR_INVALID, "attention params are null");
+  HIPATTN_REQUIRE(p->q && p->pos && p->indices && p->ks && p->status, HIPATTN_ERR_INVALID,
+                  "attention: q, pos, indices, ks and status are required");
+  HIPATTN_REQUIRE(p->B > 0 && p->TQ > 0 && p->H > 0 && p->HKV > 0 && p->H % p->HKV == 0 && p->T > 0, HIPATTN_ERR_INVALID,
+                  "attention: bad shape B=%d TQ=%d H=%d HKV=%d T=%d", p->B, p->TQ, p->H, p->HKV, p->T);
+  HIPATTN_REQUIRE(p->block_size_q > 0 && p->index_block_q >= p->block_size_q && p->index_block_q % p->block_size_q == 0,
+                  HIPATTN_ERR_INVALID, "attention: index_block_q %d must be a multiple of block_size_q %d", p->index_block_q,
+                  p->block_size_q);
+  HIPATTN_REQUIRE(p->block_size_k > 0 && p->K >= 0 && p->sink >= 0 && p->window >= 0, HIPATTN_ERR_INVALID,
+                  "attention: bad mask geometry");
+  HIPATTN_REQUIRE(p->n_splits >= 1 && p->n_splits <= 64, HIPATTN_ERR_INVALID, "attention: n_splits %d outside [1, 64]", p->n_splits);
+  if (p->n_splits > 1) {
+    HIPATTN_REQUIRE(p->TQ == 1 && p->part_o && p->part_lse, HIPATTN_ERR_INVALID,
+                    "attention: key splits need TQ == 1 and the part_o / part_lse buffers");
+  } else {
+    HIPATTN_REQUIRE(p->out != nullptr, HIPATTN_ERR_INVALID, "attention: out is null");
+  }
+  const int eb = p->dtype == HIPATTN_F32 ? 4 : 2;
+  const int64_t ra = 16 / eb;
+  HIPATTN_REQUIRE(((uintptr_t)p->q % 16) == 0 && p->q_stride_b % ra == 0 && p->q_stride_t % ra == 0 && p->q_stride_h % ra == 0,
+                  HIPATTN_ERR_INVALID, "attention: q rows must start on 16-byte boundaries");
+  int rc = validate_tokens(p->k, eb, p->D, "k");
+  if (rc) return rc;
+  rc = validate_tokens(p->v, eb, p->D, "v");
+  if (rc) return rc;
+  bool handled = false;
+  rc = bsa_mma(*p, (cudaStream_t)stream, &handled);
+  if (handled) return rc;
+  return bsa_generic(*p, (cudaStream_t)stream);
+}
+
+extern "C" int hipattn_merge_partials(const float* part_o, const float* part_lse, int64_t rows, int32_t n_parts, int32_t D,
+                                      int32_t dtype, void* out, int64_t out_stride, float* lse_out, void* stream) {
+  HIPATTN_REQUIRE(part_o && part_lse && out, HIPATTN_ERR_INVALID, "merge_partials: null pointer");
+  HIPATTN_REQUIRE(rows > 0 && n_parts > 0 && D > 0, HIPATTN_ERR_INVALID, "merge_partials: bad sizes");
+  const int threads = D >= 128 ? 128 : 64;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case HIPATTN_F32:
+      merge_kernel<HIPATTN_F32><<<(unsigned)rows, threads, 0, s>>>(part_o, part_lse, n_parts, D, (float*)out, out_stride, lse_out);
+      break;
+    case HIPATTN_F16:
+      merge_kernel<HIPATTN_F16><<<(unsigned)rows, threads, 0, s>>>(part_o, part_lse, n_parts, D, (__half*)out, out_stride, lse_out);
+      break;
+    case HIPATTN_BF16:
+      merge_kernel<HIPATTN_BF16><<<(unsigned)rows, threads, 0, s>>>(part_o, part_lse, n_parts, D, (__nv_bfloat16*)out, out_stride, lse_out);
+      break;
+    default: set_error("merge_partials: unknown dtype %d", dtype); return HIPATTN_ERR_INVALID;
+  }
+  return check_launch("merge_kernel");
+}
+
+extern "C" uint32_t hipattn_encode_score(float score) {
+  uint32_t bits;
+  memcpy(&bits, &score, 4);
+  return encode_score_bits(bits);
+}
+extern "C" float hipattn_decode_score(uint32_t code) {
+  uint32_t bits = decode_score_bits(code);
+  float f;
+  memcpy(&f, &bits, 4);
+  return f;
+}
+
+extern "C" const char* hipattn_error_string(void) { return g_error; }
+extern "C" int hipattn_abi_version(void) { return 1; }

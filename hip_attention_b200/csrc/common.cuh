@@ -1,0 +1,126 @@
+// Shared device / host helpers for libhipattn_sm100.so.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/hipattn.h"
+
+namespace hipattn {
+
+// ---------------------------------------------------------------------------------------------
+// host-side error reporting
+// ---------------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+
+#define HIPATTN_REQUIRE(cond, code, ...) \
+  do {                                   \
+    if (!(cond)) {                       \
+      ::hipattn::set_error(__VA_ARGS__); \
+      return (code);                     \
+    }                                    \
+  } while (0)
+
+#define HIPATTN_CUDA_OK(expr)                                                          \
+  do {                                                                                 \
+    cudaError_t e_ = (expr);                                                           \
+    if (e_ != cudaSuccess) {                                                           \
+      ::hipattn::set_error("%s failed: %s", #expr, cudaGetErrorString(e_));            \
+      return HIPATTN_ERR_CUDA;                                                         \
+    }                                                                                  \
+  } while (0)
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("launch of %s failed: %s", what, cudaGetErrorString(e));
+    return HIPATTN_ERR_CUDA;
+  }
+  return HIPATTN_OK;
+}
+
+int validate_tokens(const hipattn_tokens_t& t, int elem_bytes, int D, const char* name);
+
+// ---------------------------------------------------------------------------------------------
+// element types
+// ---------------------------------------------------------------------------------------------
+template <int DT>
+struct Elem;
+template <>
+struct Elem<HIPATTN_F32> {
+  using type = float;
+  static constexpr int bytes = 4;
+  __device__ static __forceinline__ float to_f32(float x) { return x; }
+  __device__ static __forceinline__ float round(float x) { return x; }
+  __device__ static __forceinline__ float from_f32(float x) { return x; }
+};
+template <>
+struct Elem<HIPATTN_F16> {
+  using type = __half;
+  static constexpr int bytes = 2;
+  __device__ static __forceinline__ float to_f32(__half x) { return __half2float(x); }
+  __device__ static __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+  __device__ static __forceinline__ __half from_f32(float x) { return __float2half_rn(x); }
+};
+template <>
+struct Elem<HIPATTN_BF16> {
+  using type = __nv_bfloat16;
+  static constexpr int bytes = 2;
+  __device__ static __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+  __device__ static __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+  __device__ static __forceinline__ __nv_bfloat16 from_f32(float x) { return __float2bfloat16_rn(x); }
+};
+
+// ---------------------------------------------------------------------------------------------
+// order-preserving score encoding: a < b  <=>  enc(a) < enc(b)
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ uint32_t encode_score_bits(uint32_t bits) {
+  return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+}
+__host__ __device__ __forceinline__ uint32_t decode_score_bits(uint32_t code) {
+  return (code & 0x80000000u) ? (code & 0x7fffffffu) : ~code;
+}
+__device__ __forceinline__ uint32_t encode_score(float s) { return encode_score_bits(__float_as_uint(s)); }
+__device__ __forceinline__ float decode_score(uint32_t c) { return __uint_as_float(decode_score_bits(c)); }
+
+// ---------------------------------------------------------------------------------------------
+// token addressing: dense K[b, t, h, :] or paged cache[block_table[b, t / P], t % P, h, :]
+// ---------------------------------------------------------------------------------------------
+// Returns the element offset of row (b, t, hkv) from the base pointer returned in *base.
+// Out-of-range page ids are clamped to page 0 and flagged; positions at or beyond cache_seq_lens[b]
+// read page 0 (as the reference does: the table lookup is masked with other=0).
+__device__ __forceinline__ const char* token_row(const hipattn_tokens_t& tk, int b, int64_t t, int hkv, int elem_bytes,
+                                                 uint32_t* status) {
+  if (tk.cache == nullptr) {
+    int64_t off = (int64_t)b * tk.stride_b + t * tk.stride_t + (int64_t)hkv * tk.stride_h;
+    return (const char*)tk.dense + off * elem_bytes;
+  }
+  int64_t seq = tk.seq_lens_is_i64 ? ((const int64_t*)tk.cache_seq_lens)[b] : (int64_t)((const int32_t*)tk.cache_seq_lens)[b];
+  int64_t page = 0;
+  int64_t pi = t / tk.page_size;
+  if (t >= 0 && t < seq && pi < tk.table_width) {
+    int64_t o = (int64_t)b * tk.table_stride_b + pi;
+    page = tk.table_is_i64 ? ((const int64_t*)tk.block_table)[o] : (int64_t)((const int32_t*)tk.block_table)[o];
+    if (page < 0 || page >= tk.n_pages) {
+      if (status) atomicOr(status, HIPATTN_STATUS_PAGE_RANGE);
+      page = 0;
+    }
+  }
+  int64_t off = page * tk.stride_page + (t % tk.page_size) * tk.stride_off + (int64_t)hkv * tk.stride_ch;
+  return (const char*)tk.cache + off * elem_bytes;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__host__ __device__ __forceinline__ int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace hipattn

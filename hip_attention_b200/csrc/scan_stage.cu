@@ -1,0 +1,339 @@
+// Scan stage of the hierarchical mask estimator (strict arithmetic).
+//
+// For every (batch, query block, head, chunk) the kernel narrows [left, right) by repeated halving:
+// each round fetches two representative key rows (the midpoints of the two halves), scores them
+// against the mean-pooled query rows of the block and keeps the better half.  The score of a key is
+// max over pooled rows of round_to_dtype(dot(q', k')), where the dot product is accumulated in fp32
+// sequentially over the head dimension in ascending order, so that a CPU restatement reproduces it
+// bit for bit.  The best score of the surviving halves is reduced over heads with an atomic max on
+// an order-preserving integer image.
+//
+// Mapping: one CTA = 32 * NW consecutive chunks of one (batch, query block, head); a lane owns one
+// chunk and both of its candidate keys.  Key rows are gathered with 16-byte cp.async (16 lanes per
+// 256-byte row, fully coalesced) into a per-warp staging area; pooled queries sit in shared memory as
+// fp32 and are read as warp-wide broadcasts, so the inner loop is 8 FMAs per shared-memory load.
+// CTAs are ordered so that all query blocks and heads of one KV head run together and its keys stay
+// resident in L2.
+#include "common.cuh"
+
+namespace hipattn {
+namespace {
+
+constexpr int kPad = 16;  // bytes of padding per staged key row: keeps 16-byte lane reads conflict free
+
+template <int DT, int D>
+struct RowGeom {
+  static constexpr int kRowBytes = D * Elem<DT>::bytes;
+  static constexpr int kRowStride = kRowBytes + kPad;
+  static constexpr int kPieces = kRowBytes / 16;   // 16-byte pieces per row
+  static constexpr int kVec = 16 / Elem<DT>::bytes;  // elements per piece
+};
+
+// unpack one 16-byte piece of key elements, apply the key scale and round to the element type
+template <int DT>
+__device__ __forceinline__ void unpack_scaled(const uint4& w, float k_scale, float* out);
+
+template <>
+__device__ __forceinline__ void unpack_scaled<HIPATTN_F32>(const uint4& w, float k_scale, float* out) {
+  out[0] = __fmul_rn(__uint_as_float(w.x), k_scale);
+  out[1] = __fmul_rn(__uint_as_float(w.y), k_scale);
+  out[2] = __fmul_rn(__uint_as_float(w.z), k_scale);
+  out[3] = __fmul_rn(__uint_as_float(w.w), k_scale);
+}
+template <>
+__device__ __forceinline__ void unpack_scaled<HIPATTN_BF16>(const uint4& w, float k_scale, float* out) {
+  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float lo = __uint_as_float(v[i] << 16);
+    float hi = __uint_as_float(v[i] & 0xffff0000u);
+    out[2 * i] = Elem<HIPATTN_BF16>::round(__fmul_rn(lo, k_scale));
+    out[2 * i + 1] = Elem<HIPATTN_BF16>::round(__fmul_rn(hi, k_scale));
+  }
+}
+template <>
+__device__ __forceinline__ void unpack_scaled<HIPATTN_F16>(const uint4& w, float k_scale, float* out) {
+  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 h = *reinterpret_cast<const __half2*>(&v[i]);
+    float2 f = __half22float2(h);
+    out[2 * i] = Elem<HIPATTN_F16>::round(__fmul_rn(f.x, k_scale));
+    out[2 * i + 1] = Elem<HIPATTN_F16>::round(__fmul_rn(f.y, k_scale));
+  }
+}
+
+template <int DT>
+__device__ __forceinline__ float mac(float q, float k, float acc) {
+  if (DT == HIPATTN_F32) return __fadd_rn(acc, __fmul_rn(q, k));  // two roundings, reproducible on a CPU
+  return fmaf(q, k, acc);                                         // 16-bit inputs: the product is exact
+}
+
+// RT = pooled query rows processed per pass over a staged key pair
+template <int DT, int D, int RT>
+__global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_params_t p, int nblk, int NW) {
+  using G = RowGeom<DT, D>;
+  using T = typename Elem<DT>::type;
+  extern __shared__ __align__(16) unsigned char smem[];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int Gq = p.H / p.HKV;
+  const int BDST = cdiv(p.TQ, p.block_size_q);
+  int64_t bid = blockIdx.x;
+  const int cblk = (int)(bid % nblk); bid /= nblk;
+  const int g = (int)(bid % Gq); bid /= Gq;
+  const int d = (int)(bid % BDST); bid /= BDST;
+  const int hkv = (int)(bid % p.HKV); bid /= p.HKV;
+  const int b = (int)bid;
+  const int h = hkv * Gq + g;
+
+  const int R = p.block_size_q / p.stride_q;
+  const int t0 = d * p.block_size_q;
+  int Rv = 0;  // valid strided rows form a prefix
+  if (t0 < p.TQ) Rv = min(R, (p.TQ - t0 + p.stride_q - 1) / p.stride_q);
+  const int Rpad = cdiv(max(Rv, 1), RT) * RT;
+
+  float* qtile = reinterpret_cast<float*>(smem);                       // [Rpad][D]
+  unsigned char* kstage = smem + (size_t)Rpad * D * sizeof(float);     // [NW][2][32][kRowStride]
+  __shared__ int s_pmin;
+
+  // ---- pooled queries: mean of stride_q consecutive rows, fp32 accumulation in row order ----
+  for (int i = threadIdx.x; i < Rpad * D; i += blockDim.x) {
+    const int r = i / D, e = i - r * D;
+    float v = 0.f;
+    if (r < Rv) {
+      float sum = 0.f, cnt = 0.f;
+      const int t = t0 + r * p.stride_q;
+      for (int o = 0; o < p.stride_q; ++o) {
+        if (t + o < p.TQ) {
+          const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(t + o) * p.q_stride_t +
+                        (int64_t)h * p.q_stride_h + e;
+          sum = __fadd_rn(sum, Elem<DT>::to_f32(*qp));
+          cnt += 1.f;
+        }
+      }
+      v = Elem<DT>::round(__fdiv_rn(sum, __fadd_rn(cnt, 1e-12f)));
+      v = Elem<DT>::round(__fmul_rn(v, p.q_scale));
+    }
+    qtile[i] = v;
+  }
+  if (warp == 0) {
+    long long m = 0x7fffffffffffffffLL;
+    for (int r = lane; r < Rv; r += 32) {
+      long long pv = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(t0 + r * p.stride_q) * p.pos_stride_t];
+      m = pv < m ? pv : m;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      long long x = __shfl_xor_sync(0xffffffffu, m, o);
+      m = x < m ? x : m;
+    }
+    if (lane == 0) s_pmin = (int)(m > 0x7fffffffLL ? 0x7fffffffLL : m);
+  }
+  __syncthreads();
+  if (Rv == 0) return;
+  const int pmin = s_pmin;
+  const int pt = max(pmin - p.scan_window, 0);
+
+  // ---- this lane's chunk ----
+  const int n = p.n_chunks;
+  const int c = (cblk * NW + warp) * 32 + lane;
+  const int64_t row = (int64_t)b * BDST + d;
+  int left = 0, right = 0;
+  const bool in_range = c < n;
+  if (in_range) {
+    left = p.left[row * n + c];
+    right = p.right[row * n + c];
+  }
+  // rounds: while (m >= 1) m /= 2, with m the largest chunk of the lane's group of block_chunk chunks
+  int gmax;
+  if ((p.block_chunk & 31) == 0) {
+    const int gbase = (((cblk * NW + warp) * 32) / p.block_chunk) * p.block_chunk;
+    gmax = 0;
+    for (int i = lane; i < p.block_chunk; i += 32) {
+      const int cc = gbase + i;
+      if (cc < n) gmax = max(gmax, p.right[row * n + cc] - p.left[row * n + cc]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
+  } else {  // block_chunk == 16: a group is one half-warp
+    gmax = in_range ? (right - left) : 0;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
+  }
+  const int my_rounds = gmax >= 1 ? 32 - __clz(gmax) : 0;
+  int max_rounds = my_rounds;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) max_rounds = max(max_rounds, __shfl_xor_sync(0xffffffffu, max_rounds, o));
+
+  float score = HIPATTN_SCORE_INIT;
+  unsigned char* wstage = kstage + (size_t)warp * 64 * G::kRowStride;
+  const unsigned char* my_l = wstage + (size_t)lane * G::kRowStride;
+  const unsigned char* my_r = wstage + (size_t)(32 + lane) * G::kRowStride;
+  const int ntile = Rpad / RT;
+
+  for (int it = 0; it < max_rounds; ++it) {
+    const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
+    if (!__any_sync(0xffffffffu, act)) break;  // a chunk that is inactive now stays inactive
+    const int mid = (left + right) >> 1;
+    int tl = (left + mid) >> 1, tr = (mid + right) >> 1;
+    const char* src_l = nullptr;
+    const char* src_r = nullptr;
+    if (act) {
+      if (p.k.cache == nullptr && (tl < 0 || tr >= p.T)) {
+        atomicOr(p.status, HIPATTN_STATUS_TOKEN_RANGE);
+        tl = min(max(tl, 0), p.T - 1);
+        tr = min(max(tr, 0), p.T - 1);
+      }
+      src_l = token_row(p.k, b, tl, hkv, Elem<DT>::bytes, p.status);
+      src_r = token_row(p.k, b, tr, hkv, Elem<DT>::bytes, p.status);
+    }
+    // cooperative gather: 64 rows, kPieces lanes per row
+    __syncwarp();
+    constexpr int kRowsPerIter = 32 / G::kPieces > 0 ? 32 / G::kPieces : 1;
+    if (G::kPieces <= 32) {
+      const int sub = lane / G::kPieces, piece = lane % G::kPieces;
+      for (int r0 = 0; r0 < 64; r0 += kRowsPerIter) {
+        const int rr = r0 + sub;             // staged row: side * 32 + owner lane
+        const int owner = rr & 31, side = rr >> 5;
+        const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)(side ? src_r : src_l), owner);
+        if (a != 0ull && sub < kRowsPerIter)
+          cp_async16(wstage + (size_t)rr * G::kRowStride + piece * 16, (const char*)a + piece * 16);
+      }
+    } else {  // rows longer than 512 bytes: every lane copies several pieces
+      for (int rr = 0; rr < 64; ++rr) {
+        const int owner = rr & 31, side = rr >> 5;
+        const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)(side ? src_r : src_l), owner);
+        if (a != 0ull)
+          for (int piece = lane; piece < G::kPieces; piece += 32)
+            cp_async16(wstage + (size_t)rr * G::kRowStride + piece * 16, (const char*)a + piece * 16);
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+
+    float sl = -INFINITY, sr = -INFINITY;
+    if (act) {
+      for (int tile = 0; tile < ntile; ++tile) {
+        float accl[RT], accr[RT];
+#pragma unroll
+        for (int r = 0; r < RT; ++r) accl[r] = accr[r] = 0.f;
+        const float* qt = qtile + (size_t)tile * RT * D;
+#pragma unroll 2
+        for (int pc = 0; pc < G::kPieces; ++pc) {
+          float kl[G::kVec], kr[G::kVec];
+          unpack_scaled<DT>(*reinterpret_cast<const uint4*>(my_l + pc * 16), p.k_scale, kl);
+          unpack_scaled<DT>(*reinterpret_cast<const uint4*>(my_r + pc * 16), p.k_scale, kr);
+#pragma unroll
+          for (int r = 0; r < RT; ++r) {
+#pragma unroll
+            for (int e4 = 0; e4 < G::kVec; e4 += 4) {
+              const float4 qv = *reinterpret_cast<const float4*>(qt + r * D + pc * G::kVec + e4);
+              accl[r] = mac<DT>(qv.x, kl[e4 + 0], accl[r]);
+              accr[r] = mac<DT>(qv.x, kr[e4 + 0], accr[r]);
+              accl[r] = mac<DT>(qv.y, kl[e4 + 1], accl[r]);
+              accr[r] = mac<DT>(qv.y, kr[e4 + 1], accr[r]);
+              accl[r] = mac<DT>(qv.z, kl[e4 + 2], accl[r]);
+              accr[r] = mac<DT>(qv.z, kr[e4 + 2], accr[r]);
+              accl[r] = mac<DT>(qv.w, kl[e4 + 3], accl[r]);
+              accr[r] = mac<DT>(qv.w, kr[e4 + 3], accr[r]);
+            }
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+          if (tile * RT + r < Rv) {
+            sl = fmaxf(sl, Elem<DT>::round(accl[r]));
+            sr = fmaxf(sr, Elem<DT>::round(accr[r]));
+          }
+        }
+      }
+      const bool win = sl > sr;
+      if (win) right = mid; else left = mid;
+      score = fmaxf(score, win ? sl : sr);
+    }
+  }
+
+  if (in_range) {
+    if (score > HIPATTN_SCORE_INIT) atomicMax(p.score_max + row * n + c, encode_score(score));
+    const int64_t o = (row * p.H + h) * n + c;
+    if (p.left_out) p.left_out[o] = left;
+    if (p.right_out) p.right_out[o] = right;
+    if (p.score_out) p.score_out[o] = score;
+  }
+}
+
+template <int DT, int D, int RT>
+int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
+  using G = RowGeom<DT, D>;
+  const int R = p.block_size_q / p.stride_q;
+  const int Rpad = cdiv(R, RT) * RT;
+  const size_t q_bytes = (size_t)Rpad * D * sizeof(float);
+  int NW = 4;
+  while (NW > 1 && q_bytes + (size_t)NW * 64 * G::kRowStride > 100 * 1024) NW >>= 1;
+  const size_t smem = q_bytes + (size_t)NW * 64 * G::kRowStride;
+  HIPATTN_REQUIRE(smem <= 227 * 1024, HIPATTN_ERR_UNSUPPORTED,
+                  "scan stage needs %zu bytes of shared memory (query rows %d, head dim %d)", smem, R, D);
+  const int BDST = cdiv(p.TQ, p.block_size_q);
+  const int nblk = cdiv(p.n_chunks, 32 * NW);
+  const int64_t grid = (int64_t)p.B * p.HKV * BDST * (p.H / p.HKV) * nblk;
+  HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
+  auto kern = scan_stage_kernel<DT, D, RT>;
+  HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)grid, 32 * NW, smem, stream>>>(p, nblk, NW);
+  return check_launch("scan_stage_kernel");
+}
+
+template <int DT, int D>
+int dispatch_rows(const hipattn_scan_params_t& p, cudaStream_t stream) {
+  const int R = p.block_size_q / p.stride_q;
+  // rows that can be valid: a single query row (decode) needs one accumulator pair only
+  const int rows = min(R, cdiv(p.TQ, p.stride_q));
+  if (rows <= 1) return launch<DT, D, 1>(p, stream);
+  if (R <= 16) return launch<DT, D, 16>(p, stream);
+  if (R <= 32) return launch<DT, D, 32>(p, stream);
+  return launch<DT, D, 64>(p, stream);
+}
+
+template <int DT>
+int dispatch_dim(const hipattn_scan_params_t& p, cudaStream_t stream) {
+  switch (p.D) {
+    case 64: return dispatch_rows<DT, 64>(p, stream);
+    case 128: return dispatch_rows<DT, 128>(p, stream);
+    case 256: return dispatch_rows<DT, 256>(p, stream);
+    default:
+      set_error("scan stage: head dimension %d is not built (64, 128, 256)", p.D);
+      return HIPATTN_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+}  // namespace hipattn
+
+extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) {
+  using namespace hipattn;
+  HIPATTN_REQUIRE(p != nullptr, HIPATTN_ERR_INVALID, "scan params are null");
+  HIPATTN_REQUIRE(p->q && p->pos && p->left && p->right && p->score_max && p->status, HIPATTN_ERR_INVALID,
+                  "scan stage: q, pos, left, right, score_max and status are required");
+  HIPATTN_REQUIRE(p->B > 0 && p->TQ > 0 && p->H > 0 && p->HKV > 0 && p->H % p->HKV == 0 && p->T > 0,
+                  HIPATTN_ERR_INVALID, "scan stage: bad shape B=%d TQ=%d H=%d HKV=%d T=%d", p->B, p->TQ, p->H, p->HKV, p->T);
+  HIPATTN_REQUIRE(p->block_size_q > 0 && p->stride_q > 0 && p->block_size_q % p->stride_q == 0, HIPATTN_ERR_INVALID,
+                  "scan stage: block_size_q %d must be a positive multiple of stride_q %d", p->block_size_q, p->stride_q);
+  HIPATTN_REQUIRE(p->block_size_q / p->stride_q <= 256, HIPATTN_ERR_UNSUPPORTED, "scan stage: more than 256 pooled rows");
+  HIPATTN_REQUIRE(p->n_chunks >= 0, HIPATTN_ERR_INVALID, "scan stage: negative chunk count");
+  HIPATTN_REQUIRE(p->block_chunk >= 16 && (p->block_chunk & (p->block_chunk - 1)) == 0, HIPATTN_ERR_INVALID,
+                  "scan stage: block_chunk %d must be a power of two >= 16", p->block_chunk);
+  if (p->n_chunks == 0) return HIPATTN_OK;
+  const int eb = p->dtype == HIPATTN_F32 ? 4 : 2;
+  int rc = validate_tokens(p->k, eb, p->D, "k");
+  if (rc) return rc;
+  HIPATTN_REQUIRE(((uintptr_t)p->q % eb) == 0, HIPATTN_ERR_INVALID, "scan stage: q is misaligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (p->dtype) {
+    case HIPATTN_F32: return dispatch_dim<HIPATTN_F32>(*p, s);
+    case HIPATTN_F16: return dispatch_dim<HIPATTN_F16>(*p, s);
+    case HIPATTN_BF16: return dispatch_dim<HIPATTN_BF16>(*p, s);
+    default: set_error("scan stage: unknown dtype %d", p->dtype); return HIPATTN_ERR_INVALID;
+  }
+}

@@ -1,0 +1,196 @@
+/*
+ * hipattn.h -- C ABI of libhipattn_sm100.so: HiP / InfiniteHiP attention for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes (device pointers unless stated otherwise) and a
+ * CUDA stream given as an opaque pointer (cudaStream_t).  No entry point allocates, frees or
+ * synchronises; the caller owns all buffers.  Return value: HIPATTN_OK or an HIPATTN_ERR_* code;
+ * hipattn_error_string() gives a description of the last error on the calling thread.
+ *
+ * The functions replace, one to one, the device work the reference operator
+ * `hip_attention_12` (src/hip_attn/v1_2/attention_extend.py:1918) performs through Triton kernels
+ * and torch tensor ops.  The citation above each declaration names the reference code it stands for
+ * (paths relative to the DeepAuto-AI/hip-attention checkout).
+ */
+#ifndef HIPATTN_H_
+#define HIPATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HIPATTN_OK 0
+#define HIPATTN_ERR_INVALID 1     /* bad argument (null pointer, size out of range, misaligned row) */
+#define HIPATTN_ERR_UNSUPPORTED 2 /* valid request this build has no kernel for (dtype / head dim)  */
+#define HIPATTN_ERR_CUDA 3        /* a CUDA runtime call failed                                     */
+
+#define HIPATTN_F32 0
+#define HIPATTN_F16 1
+#define HIPATTN_BF16 2
+
+/* Bits of the device status word written by the kernels (0 = clean). */
+#define HIPATTN_STATUS_PAGE_RANGE 1u  /* a block-table entry pointed outside the page pool; clamped */
+#define HIPATTN_STATUS_TOKEN_RANGE 2u /* a token index fell outside [0, T); clamped                 */
+
+#define HIPATTN_SCORE_INIT (-32000.0f) /* attention_extend.py:2040-2045 */
+#define HIPATTN_INDEX_PAD INT64_MAX    /* attention_extend.py:2913 */
+#define HIPATTN_MAX_CHUNKS 16384       /* chunks per (batch, query block) the selection kernels sort on chip */
+
+/*
+ * Where the rows of K (or V) live: a dense tensor [B, T, HKV, D] or a page pool
+ * [n_pages, P, HKV, D] addressed through block_table[b, t / P] (src/hip_attn/v1_2/uvm_gpu_cache.py:865-890,
+ * 1034-1042).  Strides are in elements; the last dimension must be contiguous and every row must
+ * start on a 16-byte boundary.  `cache != NULL` selects paging.
+ */
+typedef struct hipattn_tokens {
+  const void* dense;
+  int64_t stride_b, stride_t, stride_h;
+  const void* cache;
+  int64_t stride_page, stride_off, stride_ch;
+  const void* block_table;   /* [B, table_width], int32 or int64 */
+  int64_t table_stride_b;
+  const void* cache_seq_lens; /* [B], int32 or int64 */
+  int64_t n_pages;
+  int32_t table_width;
+  int32_t table_is_i64;
+  int32_t seq_lens_is_i64;
+  int32_t page_size;
+} hipattn_tokens_t;
+
+/*
+ * One scan stage of the mask estimator.
+ * Replaces chunk_controllable_sampling_mask_cuda (attention_extend.py:413-1249) with the dense /
+ * paged branches of load_tokens (uvm_gpu_cache.py:843-912, 1034-1046) and the head max-reduce that
+ * follows it (attention_extend.py:2566-2570).
+ *
+ * The chunk list is shared by all heads of a (batch, query block): left/right are [B, BDST, n].
+ * score_max [B, BDST, n] receives the maximum over heads of the per-head chunk score in an
+ * order-preserving unsigned encoding (see hipattn_encode_score); it must hold
+ * encode(HIPATTN_SCORE_INIT) on entry (hipattn_init_chunks / hipattn_select_stage write that).
+ * left_out / right_out / score_out are optional per-head results [B, BDST, H, n].
+ */
+typedef struct hipattn_scan_params {
+  const void* q;             /* [B, TQ, H, D] */
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  const int64_t* pos;        /* [B, TQ] absolute positions */
+  int64_t pos_stride_b, pos_stride_t;
+  hipattn_tokens_t k;
+  const int32_t* left;
+  const int32_t* right;
+  uint32_t* score_max;
+  int32_t* left_out;
+  int32_t* right_out;
+  float* score_out;
+  uint32_t* status;          /* one word, OR-ed with HIPATTN_STATUS_* */
+  int32_t dtype, D, B, TQ, H, HKV, T;
+  int32_t block_size_q;      /* stage_block_size_q */
+  int32_t stride_q;          /* stage_block_stride_q */
+  int32_t n_chunks;
+  int32_t block_chunk;       /* group size that fixes the number of halving rounds (BLOCK_CHUNK) */
+  int32_t scan_window;       /* max(0, sliding_window - first chunk size), attention_extend.py:1976-1978 */
+  float q_scale, k_scale;    /* already rounded to the element type, attention_extend.py:924-940 */
+} hipattn_scan_params_t;
+
+int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);
+
+/*
+ * Initial chunk list of stage 0 (attention_extend.py:2027-2046): left[c] = sink + c * chunk,
+ * right = min(left + chunk, T - scan_window), score_max = encode(HIPATTN_SCORE_INIT).
+ * Arrays are [rows, n] with rows = B * BDST.
+ */
+int hipattn_init_chunks(int32_t* left, int32_t* right, uint32_t* score_max, int64_t rows, int32_t n,
+                        int32_t sink, int32_t chunk, int32_t T, int32_t scan_window, void* stream);
+
+/*
+ * Selection between two stages, per (batch, query block) row:
+ * top-k by (score descending, chunk position ascending) (attention_extend.py:2710-2721), then the
+ * slice / realign / sort-by-left / split transform that builds the next stage's chunk list
+ * (attention_extend.py:2072-2165).  Writes next_left / next_right [rows, k_keep * (c_prev / c_next)]
+ * and next_score_max = encode(HIPATTN_SCORE_INIT).  n <= HIPATTN_MAX_CHUNKS.
+ */
+int hipattn_select_stage(const uint32_t* score_max, const int32_t* left, int64_t rows, int32_t n,
+                         int32_t k_keep, int32_t sink, int32_t c_prev, int32_t c_next,
+                         int32_t* next_left, int32_t* next_right, uint32_t* next_score_max, void* stream);
+
+/*
+ * Selection after the last stage and conversion to the block-sparse index format
+ * (attention_extend.py:2722-2728, 2772-2776, 2906-2925): order all chunks by (score descending,
+ * position ascending), keep the first K = second_stage_k / c_last, align, then per head sort,
+ * replace duplicates by HIPATTN_INDEX_PAD, sort again and count the entries below
+ * pos[b, d * block_size_q] + block_size_q.
+ * left_heads: narrowed per-head left bounds [rows, H, n] with head stride `left_head_stride`
+ * (pass the shared [rows, n] list with stride 0 when all heads agree).
+ * indices [B * H, BDST, K] int64; ks [B * H, BDST] int64; ks_start_end [B * H, BDST, 2] int32.
+ */
+int hipattn_finalize_indices(const uint32_t* score_max, const int32_t* left_heads, int64_t left_row_stride,
+                             int64_t left_head_stride, const int64_t* pos, int64_t pos_stride_b,
+                             int64_t pos_stride_t, int32_t B, int32_t BDST, int32_t H, int32_t n, int32_t K,
+                             int32_t c_last, int32_t block_size_q, int64_t* indices, int64_t* ks,
+                             int32_t* ks_start_end, void* stream);
+
+/*
+ * Block-sparse attention over {selected blocks, sink, sliding window}.
+ * Replaces block_sparse_attention_cuda (attention_extend_bsa.py:621-1638) for prefill and
+ * _fwd_kernel_stage1 (attention_decode_bsa.py:23-1044) for decode; masking rules of
+ * block_sparse_attention_cuda_step (attention_extend_bsa.py:511-565).
+ *
+ * n_splits == 1: writes out [B, TQ, H, D] in the element type.
+ * n_splits  > 1: (decode, TQ == 1) the key set is cut into n_splits ranges; split s writes the
+ *   normalised partial output part_o [B, H, n_splits, D] fp32 and its base-2 log-sum-exp part_lse
+ *   [B, H, n_splits] (-inf for an empty range), to be combined by hipattn_merge_partials.
+ * lse_out (optional) [B, TQ, H] fp32 receives the base-2 log-sum-exp of every row (n_splits == 1).
+ */
+typedef struct hipattn_bsa_params {
+  const void* q;
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  void* out;
+  int64_t o_stride_b, o_stride_t, o_stride_h;
+  const int64_t* pos;
+  int64_t pos_stride_b, pos_stride_t;
+  hipattn_tokens_t k, v;
+  const int64_t* indices;    /* [B * H, BDST, K] */
+  int64_t idx_stride_n, idx_stride_d;
+  const int64_t* ks;         /* [B * H, BDST] */
+  int64_t ks_stride_n, ks_stride_d;
+  float* part_o;
+  float* part_lse;
+  float* lse_out;
+  uint32_t* status;
+  int32_t dtype, D, B, TQ, H, HKV, T;
+  int32_t block_size_q;      /* query rows per attention block (scope of the block's largest position) */
+  int32_t index_block_q;     /* query rows per row of indices / ks (a multiple of block_size_q) */
+  int32_t block_size_k;      /* tokens per selected block (last stage chunk size) */
+  int32_t K;
+  int32_t sink, window;      /* attention window = max(sliding_window, first chunk size) */
+  int32_t n_splits;
+  int32_t heads_share_mask;  /* 1: indices / ks are identical for the heads of a KV group */
+  float logit_softcap;       /* 0 = off; attention_extend_bsa.py:389-390 */
+} hipattn_bsa_params_t;
+
+int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream);
+
+/*
+ * Log-sum-exp merge of partial outputs (attention_decode_bsa.py:1149-1225).
+ * part_o [rows, n_parts, D] fp32 normalised, part_lse [rows, n_parts] base-2; writes out [rows, D]
+ * in `dtype` (row stride out_stride elements) and, optionally, merged lse [rows].
+ */
+int hipattn_merge_partials(const float* part_o, const float* part_lse, int64_t rows, int32_t n_parts,
+                           int32_t D, int32_t dtype, void* out, int64_t out_stride, float* lse_out,
+                           void* stream);
+
+/* Order-preserving image of an fp32 score: a < b  <=>  encode(a) < encode(b) (host helper). */
+uint32_t hipattn_encode_score(float score);
+float hipattn_decode_score(uint32_t code);
+
+/* Element-wise helpers used by the host wrapper to hand results back in the reference's types. */
+int hipattn_decode_scores(const uint32_t* codes, float* scores, int64_t count, void* stream);
+int hipattn_widen_i32(const int32_t* src, int64_t* dst, int64_t count, void* stream);
+
+const char* hipattn_error_string(void);
+int hipattn_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HIPATTN_H_ */
