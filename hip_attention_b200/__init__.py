@@ -5,7 +5,7 @@ same call, same argument and metadata types, CUDA kernels behind a C ABI (``incl
 """
 from .metadata import (EnsembleScoreStage, EvalScoreStage, HiPAttentionArgs, HiPAttentionCacheAccessStatistics,
                        HiPAttentionOutputMetadata, HiPAttentionStageInputCache, NopStage, ScanStage, Stage)
-from .operator import hip_attention_12, hip_attention_impl, read_status
+from .operator import PhaseTimer, hip_attention_12, hip_attention_impl, read_status
 
 # the names the reference exports for this generation of the operator
 HiPAttentionArgs12 = HiPAttentionArgs
@@ -15,7 +15,7 @@ ScanStage12 = ScanStage
 dual_stage_quadratic_hip_attention = hip_attention_12
 
 __all__ = [
-    "hip_attention_12", "dual_stage_quadratic_hip_attention", "hip_attention_impl", "read_status",
+    "hip_attention_12", "dual_stage_quadratic_hip_attention", "hip_attention_impl", "read_status", "PhaseTimer",
     "HiPAttentionArgs", "HiPAttentionArgs12", "HiPAttentionOutputMetadata", "HiPAttentionOutputMetadata12",
     "HiPAttentionCacheAccessStatistics", "HiPAttentionCacheAccessStatistics12", "HiPAttentionStageInputCache",
     "Stage", "ScanStage", "ScanStage12", "NopStage", "EvalScoreStage", "EnsembleScoreStage",

@@ -56,8 +56,8 @@ SYMBOLS = {
     "hipattn_finalize_indices": (i32, [vp, vp, i64, i64, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     "hipattn_bsa_attention": (i32, [C.POINTER(BsaParams), vp]),
     "hipattn_merge_partials": (i32, [vp, vp, i64, i32, i32, i32, vp, i64, vp, vp]),
-    "hipattn_encode_score": (C.c_uint32, [f32]),
-    "hipattn_decode_score": (f32, [C.c_uint32]),
+    "hipattn_encode_score": (i32, [f32]),
+    "hipattn_decode_score": (f32, [i32]),
     "hipattn_decode_scores": (i32, [vp, vp, i64, vp]),
     "hipattn_widen_i32": (i32, [vp, vp, i64, vp]),
     "hipattn_error_string": (C.c_char_p, []),

@@ -119,12 +119,12 @@ extern "C" int hipattn_merge_partials(const float* part_o, const float* part_lse
   return check_launch("merge_kernel");
 }
 
-extern "C" uint32_t hipattn_encode_score(float score) {
+extern "C" int32_t hipattn_encode_score(float score) {
   uint32_t bits;
   memcpy(&bits, &score, 4);
   return encode_score_bits(bits);
 }
-extern "C" float hipattn_decode_score(uint32_t code) {
+extern "C" float hipattn_decode_score(int32_t code) {
   uint32_t bits = decode_score_bits(code);
   float f;
   memcpy(&f, &bits, 4);

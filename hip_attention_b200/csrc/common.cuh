@@ -73,16 +73,22 @@ struct Elem<HIPATTN_BF16> {
 };
 
 // ---------------------------------------------------------------------------------------------
-// order-preserving score encoding: a < b  <=>  enc(a) < enc(b)
+// order-preserving score encoding: a < b  <=>  enc(a) < enc(b) as signed 32-bit integers, so the
+// head max is an integer max (atomicMax on the device, MAX all-reduce on int32 across GPUs)
 // ---------------------------------------------------------------------------------------------
-__host__ __device__ __forceinline__ uint32_t encode_score_bits(uint32_t bits) {
-  return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+__host__ __device__ __forceinline__ int32_t encode_score_bits(uint32_t bits) {
+  return (int32_t)((bits & 0x80000000u) ? (bits ^ 0x7fffffffu) : bits);
 }
-__host__ __device__ __forceinline__ uint32_t decode_score_bits(uint32_t code) {
-  return (code & 0x80000000u) ? (code & 0x7fffffffu) : ~code;
+__host__ __device__ __forceinline__ uint32_t decode_score_bits(int32_t code) {
+  const uint32_t c = (uint32_t)code;
+  return (c & 0x80000000u) ? (c ^ 0x7fffffffu) : c;
 }
-__device__ __forceinline__ uint32_t encode_score(float s) { return encode_score_bits(__float_as_uint(s)); }
-__device__ __forceinline__ float decode_score(uint32_t c) { return __uint_as_float(decode_score_bits(c)); }
+__device__ __forceinline__ int32_t encode_score(float s) { return encode_score_bits(__float_as_uint(s)); }
+__device__ __forceinline__ float decode_score(int32_t c) { return __uint_as_float(decode_score_bits(c)); }
+// ascending sort key: best score first, lower position first among equal scores
+__device__ __forceinline__ unsigned long long score_sort_key(int32_t code, unsigned position) {
+  return ((unsigned long long)(~((uint32_t)code ^ 0x80000000u)) << 32) | position;
+}
 
 // ---------------------------------------------------------------------------------------------
 // token addressing: dense K[b, t, h, :] or paged cache[block_table[b, t / P], t % P, h, :]

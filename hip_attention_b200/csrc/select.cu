@@ -2,7 +2,7 @@
 // stage's chunks, and the final conversion to sorted unique block indices.
 //
 // One CTA owns one (batch, query block) row and sorts it in shared memory with a bitonic network on
-// composite 64-bit keys (~score image << 32 | position), which makes the order total:
+// composite 64-bit keys (inverted score image << 32 | position), which makes the order total:
 // higher score first, lower chunk position first among equal scores.
 #include "common.cuh"
 
@@ -36,9 +36,9 @@ __device__ void bitonic_sort(K* a, int N) {
   }
 }
 
-__global__ void init_chunks_kernel(int32_t* left, int32_t* right, uint32_t* score_max, int64_t total, int n, int sink,
+__global__ void init_chunks_kernel(int32_t* left, int32_t* right, int32_t* score_max, int64_t total, int n, int sink,
                                    int chunk, int T, int scan_window) {
-  const uint32_t init = encode_score(HIPATTN_SCORE_INIT);
+  const int32_t init = encode_score(HIPATTN_SCORE_INIT);
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int c = (int)(i % n);
     const int l = sink + c * chunk;
@@ -49,18 +49,18 @@ __global__ void init_chunks_kernel(int32_t* left, int32_t* right, uint32_t* scor
 }
 
 // Load the row's scores as ascending sort keys: best score first, lower position first on ties.
-__device__ void load_score_keys(unsigned long long* keys, const uint32_t* score_max, int n, int n_pad) {
+__device__ void load_score_keys(unsigned long long* keys, const int32_t* score_max, int n, int n_pad) {
   for (int i = threadIdx.x; i < n_pad; i += blockDim.x)
-    keys[i] = i < n ? ((unsigned long long)(~score_max[i]) << 32) | (unsigned)i : ~0ull;
+    keys[i] = i < n ? score_sort_key(score_max[i], (unsigned)i) : ~0ull;
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(kSortThreads) select_stage_kernel(const uint32_t* __restrict__ score_max,
+__global__ void __launch_bounds__(kSortThreads) select_stage_kernel(const int32_t* __restrict__ score_max,
                                                                     const int32_t* __restrict__ left, int n, int n_pad,
                                                                     int k_keep, int k_pad, int sink, int c_prev,
                                                                     int c_next, int32_t* __restrict__ next_left,
                                                                     int32_t* __restrict__ next_right,
-                                                                    uint32_t* __restrict__ next_score_max) {
+                                                                    int32_t* __restrict__ next_score_max) {
   extern __shared__ __align__(16) unsigned char smem[];
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem);
   const int64_t row = blockIdx.x;
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(kSortThreads) select_stage_kernel(const uint32
 
   const int s = c_prev / c_next;
   const int64_t out_n = (int64_t)k_keep * s;
-  const uint32_t init = encode_score(HIPATTN_SCORE_INIT);
+  const int32_t init = encode_score(HIPATTN_SCORE_INIT);
   for (int64_t o = threadIdx.x; o < out_n; o += blockDim.x) {
     const int j = (int)(o / s), i = (int)(o - (int64_t)j * s);
     const int la = (int)(keys[j] >> 32);
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(kSortThreads) select_stage_kernel(const uint32
 }
 
 __global__ void __launch_bounds__(kSortThreads)
-    finalize_kernel(const uint32_t* __restrict__ score_max, const int32_t* __restrict__ left_heads, int64_t left_row_stride,
+    finalize_kernel(const int32_t* __restrict__ score_max, const int32_t* __restrict__ left_heads, int64_t left_row_stride,
                     int64_t left_head_stride, const int64_t* __restrict__ pos, int64_t pos_stride_b, int64_t pos_stride_t,
                     int BDST, int H, int n, int n_pad, int K, int K_pad, int c_last, int block_size_q,
                     int64_t* __restrict__ indices, int64_t* __restrict__ ks, int32_t* __restrict__ ks_start_end) {
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(kSortThreads)
   }
 }
 
-__global__ void decode_scores_kernel(const uint32_t* codes, float* scores, int64_t count) {
+__global__ void decode_scores_kernel(const int32_t* codes, float* scores, int64_t count) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
     scores[i] = decode_score(codes[i]);
 }
@@ -188,7 +188,7 @@ inline unsigned grid_for(int64_t total, int threads) {
 
 using namespace hipattn;
 
-extern "C" int hipattn_init_chunks(int32_t* left, int32_t* right, uint32_t* score_max, int64_t rows, int32_t n,
+extern "C" int hipattn_init_chunks(int32_t* left, int32_t* right, int32_t* score_max, int64_t rows, int32_t n,
                                    int32_t sink, int32_t chunk, int32_t T, int32_t scan_window, void* stream) {
   HIPATTN_REQUIRE(rows >= 0 && n >= 0 && chunk > 0 && sink >= 0, HIPATTN_ERR_INVALID, "init_chunks: bad sizes");
   if (rows * n == 0) return HIPATTN_OK;
@@ -198,9 +198,9 @@ extern "C" int hipattn_init_chunks(int32_t* left, int32_t* right, uint32_t* scor
   return check_launch("init_chunks_kernel");
 }
 
-extern "C" int hipattn_select_stage(const uint32_t* score_max, const int32_t* left, int64_t rows, int32_t n, int32_t k_keep,
+extern "C" int hipattn_select_stage(const int32_t* score_max, const int32_t* left, int64_t rows, int32_t n, int32_t k_keep,
                                     int32_t sink, int32_t c_prev, int32_t c_next, int32_t* next_left,
-                                    int32_t* next_right, uint32_t* next_score_max, void* stream) {
+                                    int32_t* next_right, int32_t* next_score_max, void* stream) {
   HIPATTN_REQUIRE(score_max && left && next_left && next_right && next_score_max, HIPATTN_ERR_INVALID,
                   "select_stage: null pointer");
   HIPATTN_REQUIRE(rows > 0 && n > 0 && k_keep > 0 && k_keep <= n, HIPATTN_ERR_INVALID,
@@ -217,7 +217,7 @@ extern "C" int hipattn_select_stage(const uint32_t* score_max, const int32_t* le
   return check_launch("select_stage_kernel");
 }
 
-extern "C" int hipattn_finalize_indices(const uint32_t* score_max, const int32_t* left_heads, int64_t left_row_stride,
+extern "C" int hipattn_finalize_indices(const int32_t* score_max, const int32_t* left_heads, int64_t left_row_stride,
                                         int64_t left_head_stride, const int64_t* pos, int64_t pos_stride_b,
                                         int64_t pos_stride_t, int32_t B, int32_t BDST, int32_t H, int32_t n, int32_t K,
                                         int32_t c_last, int32_t block_size_q, int64_t* indices, int64_t* ks,
@@ -239,7 +239,7 @@ extern "C" int hipattn_finalize_indices(const uint32_t* score_max, const int32_t
   return check_launch("finalize_kernel");
 }
 
-extern "C" int hipattn_decode_scores(const uint32_t* codes, float* scores, int64_t count, void* stream) {
+extern "C" int hipattn_decode_scores(const int32_t* codes, float* scores, int64_t count, void* stream) {
   if (count <= 0) return HIPATTN_OK;
   HIPATTN_REQUIRE(codes && scores, HIPATTN_ERR_INVALID, "decode_scores: null pointer");
   decode_scores_kernel<<<grid_for(count, 256), 256, 0, (cudaStream_t)stream>>>(codes, scores, count);

@@ -160,9 +160,30 @@ class _Mask:
     __slots__ = ("indices", "ks", "ks_start_end", "stage_inputs", "heads_share")
 
 
+class PhaseTimer:
+    """Optional per-phase CUDA-event timing of one call (events are recorded on the current stream;
+    read them with ``milliseconds()`` after a synchronise)."""
+
+    def __init__(self):
+        self.marks = []
+
+    def mark(self, name: str) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.marks.append((name, ev))
+
+    def milliseconds(self) -> dict:
+        out = {}
+        for (_, e0), (name, e1) in zip(self.marks[:-1], self.marks[1:]):
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        return out
+
+
 def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, args: HiPAttentionArgs,
                    restart: Optional[Tuple[int, Tensor, Tensor]], want_stage_inputs: bool,
-                   debug: Optional[dict] = None) -> _Mask:
+                   debug: Optional[dict] = None, score_reduce=None, timer: Optional[PhaseTimer] = None) -> _Mask:
+    """Run the scan stages.  ``score_reduce(score_int32)`` is called after every scan, before the
+    selection: a KV-head-parallel caller all-reduces (MAX) the head-reduced scores there."""
     lib = L.load()
     dev = q.device
     st = _stream(dev)
@@ -185,7 +206,7 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         first, left, right = restart
         n = left.shape[-1]
         score = torch.empty((rows, n), dtype=torch.int32, device=dev)
-        score.fill_(int(np.array(lib.hipattn_encode_score(SCORE_INIT), dtype=np.uint32).view(np.int32)))
+        score.fill_(int(lib.hipattn_encode_score(SCORE_INIT)))
         out.stage_inputs = [None] * first
     else:
         n = _cdiv(max(0, T - sink - sw), c0)
@@ -226,7 +247,12 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         sp.block_size_q, sp.stride_q = bq, s_i.stage_block_stride_q
         sp.n_chunks, sp.block_chunk, sp.scan_window = n, block_chunk, scan_window
         sp.q_scale, sp.k_scale = q_scale, k_scale
+        if timer: timer.mark("start")
         L.check(lib.hipattn_scan_stage(C.byref(sp), st), f"scan_stage[{i}]")
+        if timer: timer.mark(f"scan{i}")
+        if score_reduce is not None:
+            score_reduce(score)
+            if timer: timer.mark("reduce")
         if debug is not None:
             debug.setdefault("stages", []).append(dict(left_in=left, right_in=right, left=left_out, right=right_out,
                                                        score=score_out, score_max=score, block_chunk=block_chunk))
@@ -242,6 +268,7 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
             ns = torch.empty((rows, n2), **i32)
             L.check(lib.hipattn_select_stage(_ptr(score), _ptr(left), rows, n, k_keep, sink, s_i.stage_chunk_size,
                                              nxt.stage_chunk_size, _ptr(nl), _ptr(nr), _ptr(ns), st), f"select_stage[{i}]")
+            if timer: timer.mark("select")
             left, right, score, n = nl, nr, ns, n2
         else:
             K = min(args.second_stage_k // c_last, n)
@@ -255,6 +282,7 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
             L.check(lib.hipattn_finalize_indices(_ptr(score), _ptr(lh), row_stride, head_stride, pos.data_ptr(),
                                                  pos.stride(0), pos.stride(1), B, BDST, H, n, K, c_last, bq,
                                                  _ptr(indices), _ptr(ks), _ptr(kse), st), "finalize_indices")
+            if timer: timer.mark("select")
             out.indices, out.ks, out.ks_start_end = indices, ks, kse
     if n == 0:
         # nothing to scan: K shorter than sink + window
@@ -370,8 +398,12 @@ def _check_inputs(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args: HiP
 
 def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args: HiPAttentionArgs,
                        cached_metadata: Optional[HiPAttentionOutputMetadata] = None, *, return_lse: bool = False,
-                       debug: Optional[dict] = None):
-    """Implementation behind ``hip_attention_12``; ``return_lse`` adds the base-2 log-sum-exp [B, TQ, H]."""
+                       debug: Optional[dict] = None, score_reduce=None, timer: Optional[PhaseTimer] = None):
+    """Implementation behind ``hip_attention_12``.
+
+    ``return_lse`` adds the base-2 log-sum-exp [B, TQ, H]; ``score_reduce`` is handed to the estimator
+    (see ``_estimate_mask``); ``timer`` collects per-phase CUDA-event times; ``debug`` collects the
+    per-head outputs of every scan stage."""
     _check_inputs(q, k, v, args)
     _reject_unsupported(args)
     args = args.clone()
@@ -443,7 +475,8 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
                 i0 = len(stage_caches) - 1
                 l32, r32 = _restart_inputs(stage_caches[i0], B * BDST)
                 restart = (i0, l32, r32)
-            m = _estimate_mask(q, ktok_scan, T, HKV, pos, args, restart, stage_caches is not None, debug)
+            m = _estimate_mask(q, ktok_scan, T, HKV, pos, args, restart, stage_caches is not None, debug,
+                               score_reduce, timer)
             if stage_caches is not None:
                 for i in range(len(stage_caches), len(stages)):
                     si = m.stage_inputs[i] if i < len(m.stage_inputs) else None
@@ -478,10 +511,12 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
         if args.sliding_window_size == 777:
             raise NotImplementedError("the sliding_window_size == 777 sentinel of the serving adapter is not built")
         decode = TQ == 1 and not args.disable_flashdecode and os.environ.get("HIP_DISABLE_FLASHDECODE", "0") != "1"
+        if timer: timer.mark("start")
         context, lse = _attention(q_bsa, ktok, vtok, T, HKV, pos, indices, ks, sink=args.sink_token_size, window=sw_attn,
                                   block_size_k=c_last, bsa_block_q=bsa_bq, index_block_q=index_block_q,
                                   heads_share=heads_share, decode=decode, softcap=args.logit_softcap,
                                   want_lse=return_lse)
+        if timer: timer.mark("attention")
 
         if fresh_mask and _cdiv(TQ, bsa_bq) != BDST:
             # break the mask down to the attention block size (attention_extend.py:3036-3051)

@@ -66,7 +66,7 @@ typedef struct hipattn_tokens {
  *
  * The chunk list is shared by all heads of a (batch, query block): left/right are [B, BDST, n].
  * score_max [B, BDST, n] receives the maximum over heads of the per-head chunk score in an
- * order-preserving unsigned encoding (see hipattn_encode_score); it must hold
+ * order-preserving signed-integer encoding (see hipattn_encode_score); it must hold
  * encode(HIPATTN_SCORE_INIT) on entry (hipattn_init_chunks / hipattn_select_stage write that).
  * left_out / right_out / score_out are optional per-head results [B, BDST, H, n].
  */
@@ -78,7 +78,7 @@ typedef struct hipattn_scan_params {
   hipattn_tokens_t k;
   const int32_t* left;
   const int32_t* right;
-  uint32_t* score_max;
+  int32_t* score_max;
   int32_t* left_out;
   int32_t* right_out;
   float* score_out;
@@ -99,7 +99,7 @@ int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);
  * right = min(left + chunk, T - scan_window), score_max = encode(HIPATTN_SCORE_INIT).
  * Arrays are [rows, n] with rows = B * BDST.
  */
-int hipattn_init_chunks(int32_t* left, int32_t* right, uint32_t* score_max, int64_t rows, int32_t n,
+int hipattn_init_chunks(int32_t* left, int32_t* right, int32_t* score_max, int64_t rows, int32_t n,
                         int32_t sink, int32_t chunk, int32_t T, int32_t scan_window, void* stream);
 
 /*
@@ -109,9 +109,9 @@ int hipattn_init_chunks(int32_t* left, int32_t* right, uint32_t* score_max, int6
  * (attention_extend.py:2072-2165).  Writes next_left / next_right [rows, k_keep * (c_prev / c_next)]
  * and next_score_max = encode(HIPATTN_SCORE_INIT).  n <= HIPATTN_MAX_CHUNKS.
  */
-int hipattn_select_stage(const uint32_t* score_max, const int32_t* left, int64_t rows, int32_t n,
+int hipattn_select_stage(const int32_t* score_max, const int32_t* left, int64_t rows, int32_t n,
                          int32_t k_keep, int32_t sink, int32_t c_prev, int32_t c_next,
-                         int32_t* next_left, int32_t* next_right, uint32_t* next_score_max, void* stream);
+                         int32_t* next_left, int32_t* next_right, int32_t* next_score_max, void* stream);
 
 /*
  * Selection after the last stage and conversion to the block-sparse index format
@@ -123,7 +123,7 @@ int hipattn_select_stage(const uint32_t* score_max, const int32_t* left, int64_t
  * (pass the shared [rows, n] list with stride 0 when all heads agree).
  * indices [B * H, BDST, K] int64; ks [B * H, BDST] int64; ks_start_end [B * H, BDST, 2] int32.
  */
-int hipattn_finalize_indices(const uint32_t* score_max, const int32_t* left_heads, int64_t left_row_stride,
+int hipattn_finalize_indices(const int32_t* score_max, const int32_t* left_heads, int64_t left_row_stride,
                              int64_t left_head_stride, const int64_t* pos, int64_t pos_stride_b,
                              int64_t pos_stride_t, int32_t B, int32_t BDST, int32_t H, int32_t n, int32_t K,
                              int32_t c_last, int32_t block_size_q, int64_t* indices, int64_t* ks,
@@ -179,12 +179,13 @@ int hipattn_merge_partials(const float* part_o, const float* part_lse, int64_t r
                            int32_t D, int32_t dtype, void* out, int64_t out_stride, float* lse_out,
                            void* stream);
 
-/* Order-preserving image of an fp32 score: a < b  <=>  encode(a) < encode(b) (host helper). */
-uint32_t hipattn_encode_score(float score);
-float hipattn_decode_score(uint32_t code);
+/* Order-preserving image of an fp32 score: a < b  <=>  encode(a) < encode(b) as signed integers
+ * (host helpers; across GPUs the head max is an int32 MAX all-reduce of score_max). */
+int32_t hipattn_encode_score(float score);
+float hipattn_decode_score(int32_t code);
 
 /* Element-wise helpers used by the host wrapper to hand results back in the reference's types. */
-int hipattn_decode_scores(const uint32_t* codes, float* scores, int64_t count, void* stream);
+int hipattn_decode_scores(const int32_t* codes, float* scores, int64_t count, void* stream);
 int hipattn_widen_i32(const int32_t* src, int64_t* dst, int64_t count, void* stream);
 
 const char* hipattn_error_string(void);
