@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(_PKG, "libhipattn_sm100.so")
 F32, F16, BF16 = 0, 1, 2
 STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE = 1, 2
 MAX_CHUNKS = 16384
+NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
 ABI_VERSION = 1
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
@@ -56,6 +57,7 @@ SYMBOLS = {
     "hipattn_finalize_indices": (i32, [vp, vp, i64, i64, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     "hipattn_bsa_attention": (i32, [C.POINTER(BsaParams), vp]),
     "hipattn_merge_partials": (i32, [vp, vp, i64, i32, i32, i32, vp, i64, vp, vp]),
+    "hipattn_bsa_decode_noalloc": (i32, [C.POINTER(BsaParams), vp]),
     "hipattn_encode_score": (i32, [f32]),
     "hipattn_decode_score": (f32, [i32]),
     "hipattn_decode_scores": (i32, [vp, vp, i64, vp]),

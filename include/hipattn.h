@@ -179,6 +179,26 @@ int hipattn_merge_partials(const float* part_o, const float* part_lse, int64_t r
                            int32_t D, int32_t dtype, void* out, int64_t out_stride, float* lse_out,
                            void* stream);
 
+/*
+ * Decode attention (TQ == 1) with key splits for callers that cannot allocate device memory.
+ * No counterpart in the reference, which allocates its split buffer with torch on every call
+ * (attention_decode_bsa.py:1082-1086).
+ *
+ * Same parameters as hipattn_bsa_attention, except that part_o / part_lse are ignored: the partial
+ * results of the p->n_splits key ranges go to an array that is part of the library image, and the
+ * merged result is written to p->out (contiguous [B, 1, H, D]) and, if given, p->lse_out [B, 1, H].
+ * The call performs no cudaMalloc / cudaFree and calls no allocating routine.
+ *
+ * Limit: B * H * n_splits * (D + 1) * 4 bytes <= HIPATTN_NOALLOC_SCRATCH_BYTES, otherwise
+ * HIPATTN_ERR_UNSUPPORTED.  That many bytes are resident on every GPU that loads the library until
+ * the process exits.  The first call on a device looks up the array's device address (one
+ * cudaGetSymbolAddress, with that device current); make that first call before starting any stream
+ * capture.  All calls on a device share the array: calls that may overlap on the GPU race with each
+ * other and must be ordered by the caller (same stream, or events).
+ */
+#define HIPATTN_NOALLOC_SCRATCH_BYTES (16 * 1024 * 1024)
+int hipattn_bsa_decode_noalloc(const hipattn_bsa_params_t* p, void* stream);
+
 /* Order-preserving image of an fp32 score: a < b  <=>  encode(a) < encode(b) as signed integers
  * (host helpers; across GPUs the head max is an int32 MAX all-reduce of score_max). */
 int32_t hipattn_encode_score(float score);
