@@ -309,6 +309,9 @@ int dispatch_dim(const hipattn_scan_params_t& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int scan_stage_mma(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
+
 }  // namespace hipattn
 
 extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) {
@@ -330,6 +333,10 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
   if (rc) return rc;
   HIPATTN_REQUIRE(((uintptr_t)p->q % eb) == 0, HIPATTN_ERR_INVALID, "scan stage: q is misaligned");
   cudaStream_t s = (cudaStream_t)stream;
+  HIPATTN_REQUIRE(p->mode >= HIPATTN_SCAN_AUTO && p->mode <= HIPATTN_SCAN_CHECK, HIPATTN_ERR_INVALID, "scan stage: unknown mode %d", p->mode);
+  bool handled = false;
+  rc = scan_stage_mma(*p, s, &handled);
+  if (handled) return rc;
   switch (p->dtype) {
     case HIPATTN_F32: return dispatch_dim<HIPATTN_F32>(*p, s);
     case HIPATTN_F16: return dispatch_dim<HIPATTN_F16>(*p, s);

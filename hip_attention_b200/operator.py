@@ -247,6 +247,9 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         sp.block_size_q, sp.stride_q = bq, s_i.stage_block_stride_q
         sp.n_chunks, sp.block_chunk, sp.scan_window = n, block_chunk, scan_window
         sp.q_scale, sp.k_scale = q_scale, k_scale
+        sp.mode = _scan_mode()
+        if debug is not None and "scan_stats" in debug:
+            sp.stats = debug["scan_stats"].data_ptr()
         if timer: timer.mark("start")
         L.check(lib.hipattn_scan_stage(C.byref(sp), st), f"scan_stage[{i}]")
         if timer: timer.mark(f"scan{i}")
@@ -293,6 +296,15 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         out.ks_start_end = torch.zeros((B * H, BDST, 2), dtype=torch.int32, device=dev)
     out.heads_share = not per_head_final
     return out
+
+
+def _scan_mode() -> int:
+    """HIPATTN_SCAN_MODE = auto (default) | strict | check selects the arithmetic path of the scan kernels."""
+    name = os.environ.get("HIPATTN_SCAN_MODE", "auto")
+    try:
+        return {"auto": L.SCAN_AUTO, "strict": L.SCAN_STRICT, "check": L.SCAN_CHECK}[name]
+    except KeyError:
+        raise ValueError(f"HIPATTN_SCAN_MODE={name!r}: expected auto, strict or check") from None
 
 
 def _stage_cache_entry(left: Tensor, right: Tensor, B: int, BDST: int, H: int) -> HiPAttentionStageInputCache:

@@ -58,6 +58,10 @@ typedef struct hipattn_tokens {
   int32_t page_size;
 } hipattn_tokens_t;
 
+#define HIPATTN_SCAN_AUTO 0   /* tensor-core scores with exact fallback where built, else strict */
+#define HIPATTN_SCAN_STRICT 1 /* sequential fp32 dot products only */
+#define HIPATTN_SCAN_CHECK 2  /* as AUTO, but every key is also scored strictly and compared (slow) */
+
 /*
  * One scan stage of the mask estimator.
  * Replaces chunk_controllable_sampling_mask_cuda (attention_extend.py:413-1249) with the dense /
@@ -83,6 +87,8 @@ typedef struct hipattn_scan_params {
   int32_t* right_out;
   float* score_out;
   uint32_t* status;          /* one word, OR-ed with HIPATTN_STATUS_* */
+  uint64_t* stats;           /* optional, 4 words: keys scored, keys re-scored strictly, wrong shortcuts
+                                (check mode), largest deviation / allowed radius as float bits (check mode) */
   int32_t dtype, D, B, TQ, H, HKV, T;
   int32_t block_size_q;      /* stage_block_size_q */
   int32_t stride_q;          /* stage_block_stride_q */
@@ -90,6 +96,7 @@ typedef struct hipattn_scan_params {
   int32_t block_chunk;       /* group size that fixes the number of halving rounds (BLOCK_CHUNK) */
   int32_t scan_window;       /* max(0, sliding_window - first chunk size), attention_extend.py:1976-1978 */
   float q_scale, k_scale;    /* already rounded to the element type, attention_extend.py:924-940 */
+  int32_t mode;              /* HIPATTN_SCAN_AUTO / _STRICT / _CHECK */
 } hipattn_scan_params_t;
 
 int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);

@@ -228,3 +228,40 @@ def test_bad_page_table_is_clamped_and_flagged():
     torch.cuda.synchronize()
     assert read_status("cuda") & 1
     assert torch.isfinite(out.float()).all()
+
+
+def _scan_check_run(dtype, TQ=512, T=16384):
+    """Run the estimator in check mode on a bench-shaped problem; returns (stats, indices)."""
+    import bench
+    from hip_attention_b200 import hip_attention_impl
+    w = dict(bench.WORKLOADS["prefill_128k"], TQ=TQ, T=T, keep=[4096, 2048, 1024],
+             dtype={torch.bfloat16: "bf16", torch.float16: "fp16"}[dtype])
+    q, k, v = bench.make_qkv(w, "cuda")
+    args = bench.make_args(w)
+    stats = torch.zeros(4, dtype=torch.int64, device="cuda")
+    out, md = hip_attention_impl(q, k, v, args, debug={"scan_stats": stats})
+    torch.cuda.synchronize()
+    return stats.cpu(), md, (q, k, v, w)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scan_tensor_core_path_is_exact(dtype, monkeypatch):
+    """The tensor-core scan takes a shortcut only where rounding is certain.  In check mode every key
+    is also scored by the strict definition: no shortcut may be wrong, and the observed deviation must
+    stay well inside the assumed error radius.  Strict and automatic modes give identical masks."""
+    import numpy as np
+    monkeypatch.setenv("HIPATTN_SCAN_MODE", "check")
+    stats, md_check, _ = _scan_check_run(dtype)
+    keys, fallbacks, wrong = int(stats[0]), int(stats[1]), int(stats[2])
+    ratio = float(np.array([int(stats[3]) & 0xffffffff], dtype=np.uint32).view(np.float32)[0])
+    assert keys > 1_000_000
+    assert wrong == 0, f"{wrong} shortcuts disagree with the strict score"
+    assert ratio < 0.5, f"deviation reached {ratio:.3f} of the assumed radius"
+    assert fallbacks / keys < 0.25
+    monkeypatch.setenv("HIPATTN_SCAN_MODE", "auto")
+    _, md_auto, _ = _scan_check_run(dtype)
+    monkeypatch.setenv("HIPATTN_SCAN_MODE", "strict")
+    _, md_strict, _ = _scan_check_run(dtype)
+    assert torch.equal(md_auto.indices, md_strict.indices) and torch.equal(md_auto.ks, md_strict.ks)
+    assert torch.equal(md_check.indices, md_strict.indices)
+    print(f"scan check {dtype}: keys {keys} fallbacks {fallbacks} ({100 * fallbacks / keys:.2f} %) max ratio {ratio:.4f}")
