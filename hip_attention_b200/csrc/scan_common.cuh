@@ -1,0 +1,109 @@
+// Pieces shared by the two scan kernels: pooled queries and the per-call work split.
+#pragma once
+#include "common.cuh"
+
+namespace hipattn {
+
+template <int DT>
+__device__ __forceinline__ void widen_piece(const uint4& w, float* out);
+template <>
+__device__ __forceinline__ void widen_piece<HIPATTN_F32>(const uint4& w, float* out) {
+  out[0] = __uint_as_float(w.x); out[1] = __uint_as_float(w.y); out[2] = __uint_as_float(w.z); out[3] = __uint_as_float(w.w);
+}
+template <>
+__device__ __forceinline__ void widen_piece<HIPATTN_BF16>(const uint4& w, float* out) {
+  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(v[i] << 16);
+    out[2 * i + 1] = __uint_as_float(v[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void widen_piece<HIPATTN_F16>(const uint4& w, float* out) {
+  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v[i]));
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+
+// One 16-byte piece of a pooled, scaled query row (attention_extend.py:607-734, 924-931): the mean of
+// stride_q consecutive query rows starting at row t, accumulated in fp32 in row order, divided by the
+// number of rows present, rounded to the element type, multiplied by the query scale, rounded again.
+template <int DT>
+__device__ __forceinline__ void pooled_query_piece(const hipattn_scan_params_t& p, int b, int h, int t, int piece, float* out) {
+  using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / Elem<DT>::bytes;
+  float sum[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) sum[e] = 0.f;
+  float cnt = 0.f;
+  const T* base = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)h * p.q_stride_h + piece * VEC;
+#pragma unroll 4
+  for (int o = 0; o < p.stride_q; ++o) {
+    if (t + o < p.TQ) {
+      float v[VEC];
+      widen_piece<DT>(*reinterpret_cast<const uint4*>(base + (int64_t)(t + o) * p.q_stride_t), v);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) sum[e] = __fadd_rn(sum[e], v[e]);
+      cnt += 1.f;
+    }
+  }
+  const float den = __fadd_rn(cnt, 1e-12f);
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    const float m = Elem<DT>::round(__fdiv_rn(sum[e], den));
+    out[e] = Elem<DT>::round(__fmul_rn(m, p.q_scale));
+  }
+}
+
+// Smallest position among the strided rows of a query block (computed by one warp).
+__device__ __forceinline__ int block_min_position(const hipattn_scan_params_t& p, int b, int t0, int Rv, int lane) {
+  long long m = 0x7fffffffffffffffLL;
+  for (int r = lane; r < Rv; r += 32) {
+    const long long pv = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(t0 + r * p.stride_q) * p.pos_stride_t];
+    m = pv < m ? pv : m;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const long long x = __shfl_xor_sync(0xffffffffu, m, o);
+    m = x < m ? x : m;
+  }
+  return (int)(m > 0x7fffffffLL ? 0x7fffffffLL : m);
+}
+
+// Number of halving rounds of the lane's chunk: while (m >= 1) m /= 2 with m the largest chunk of the
+// lane's group of block_chunk chunks (attention_extend.py:602-606, 736-737).  `wbase` is the first
+// chunk of the warp; the warp's 32 chunks lie in one group when block_chunk is a multiple of 32.
+__device__ __forceinline__ int chunk_rounds(const hipattn_scan_params_t& p, int64_t row, int n, int wbase, int lane,
+                                            bool in_range, int left, int right) {
+  int gmax;
+  if ((p.block_chunk & 31) == 0) {
+    const int gbase = (wbase / p.block_chunk) * p.block_chunk;
+    gmax = 0;
+    for (int i = lane; i < p.block_chunk; i += 32) {
+      const int cc = gbase + i;
+      if (cc < n) gmax = max(gmax, p.right[row * n + cc] - p.left[row * n + cc]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
+  } else {  // block_chunk == 16: a group is one half-warp
+    gmax = in_range ? (right - left) : 0;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
+  }
+  return gmax >= 1 ? 32 - __clz(gmax) : 0;
+}
+
+// CTAs per (batch, query block, head): enough to fill the GPU a few times over, never more than the
+// number of chunk blocks.  With many query blocks (prefill) one CTA walks all chunk blocks and the
+// pooled queries are computed once.
+inline int scan_ctas_per_unit(int64_t units, int chunk_blocks) {
+  const int64_t want = (148 * 2 * 4 + units - 1) / units;
+  return (int)(want < 1 ? 1 : (want > chunk_blocks ? chunk_blocks : want));
+}
+
+}  // namespace hipattn

@@ -14,7 +14,7 @@
 // fp32 and are read as warp-wide broadcasts, so the inner loop is 8 FMAs per shared-memory load.
 // CTAs are ordered so that all query blocks and heads of one KV head run together and its keys stay
 // resident in L2.
-#include "common.cuh"
+#include "scan_common.cuh"
 
 namespace hipattn {
 namespace {
@@ -71,7 +71,7 @@ __device__ __forceinline__ float mac(float q, float k, float acc) {
 
 // RT = pooled query rows processed per pass over a staged key pair
 template <int DT, int D, int RT>
-__global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_params_t p, int nblk, int NW) {
+__global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int NW) {
   using G = RowGeom<DT, D>;
   using T = typename Elem<DT>::type;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -97,80 +97,48 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
   unsigned char* kstage = smem + (size_t)Rpad * D * sizeof(float);     // [NW][2][32][kRowStride]
   __shared__ int s_pmin;
 
-  // ---- pooled queries: mean of stride_q consecutive rows, fp32 accumulation in row order ----
-  for (int i = threadIdx.x; i < Rpad * D; i += blockDim.x) {
-    const int r = i / D, e = i - r * D;
-    float v = 0.f;
-    if (r < Rv) {
-      float sum = 0.f, cnt = 0.f;
-      const int t = t0 + r * p.stride_q;
-      for (int o = 0; o < p.stride_q; ++o) {
-        if (t + o < p.TQ) {
-          const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(t + o) * p.q_stride_t +
-                        (int64_t)h * p.q_stride_h + e;
-          sum = __fadd_rn(sum, Elem<DT>::to_f32(*qp));
-          cnt += 1.f;
-        }
-      }
-      v = Elem<DT>::round(__fdiv_rn(sum, __fadd_rn(cnt, 1e-12f)));
-      v = Elem<DT>::round(__fmul_rn(v, p.q_scale));
-    }
-    qtile[i] = v;
+  // ---- pooled queries (once per CTA) ----
+  for (int i = threadIdx.x; i < Rpad * G::kPieces; i += blockDim.x) {
+    const int r = i / G::kPieces, pc = i % G::kPieces;
+    float v[G::kVec];
+#pragma unroll
+    for (int e = 0; e < G::kVec; ++e) v[e] = 0.f;
+    if (r < Rv) pooled_query_piece<DT>(p, b, h, t0 + r * p.stride_q, pc, v);
+#pragma unroll
+    for (int e = 0; e < G::kVec; e += 4)
+      *reinterpret_cast<float4*>(qtile + (size_t)r * D + pc * G::kVec + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
   }
   if (warp == 0) {
-    long long m = 0x7fffffffffffffffLL;
-    for (int r = lane; r < Rv; r += 32) {
-      long long pv = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(t0 + r * p.stride_q) * p.pos_stride_t];
-      m = pv < m ? pv : m;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      long long x = __shfl_xor_sync(0xffffffffu, m, o);
-      m = x < m ? x : m;
-    }
-    if (lane == 0) s_pmin = (int)(m > 0x7fffffffLL ? 0x7fffffffLL : m);
+    const int m = block_min_position(p, b, t0, Rv, lane);
+    if (lane == 0) s_pmin = m;
   }
   __syncthreads();
   if (Rv == 0) return;
   const int pmin = s_pmin;
   const int pt = max(pmin - p.scan_window, 0);
-
-  // ---- this lane's chunk ----
   const int n = p.n_chunks;
-  const int c = (cblk * NW + warp) * 32 + lane;
   const int64_t row = (int64_t)b * BDST + d;
+  unsigned char* wstage = kstage + (size_t)warp * 64 * G::kRowStride;
+  const unsigned char* my_l = wstage + (size_t)lane * G::kRowStride;
+  const unsigned char* my_r = wstage + (size_t)(32 + lane) * G::kRowStride;
+  const int ntile = Rpad / RT;
+
+  // ---- chunk blocks of this CTA ----
+  for (int cb = cblk; cb < nblk_total; cb += nblk) {
+  const int wbase = (cb * NW + warp) * 32;
+  const int c = wbase + lane;
   int left = 0, right = 0;
   const bool in_range = c < n;
   if (in_range) {
     left = p.left[row * n + c];
     right = p.right[row * n + c];
   }
-  // rounds: while (m >= 1) m /= 2, with m the largest chunk of the lane's group of block_chunk chunks
-  int gmax;
-  if ((p.block_chunk & 31) == 0) {
-    const int gbase = (((cblk * NW + warp) * 32) / p.block_chunk) * p.block_chunk;
-    gmax = 0;
-    for (int i = lane; i < p.block_chunk; i += 32) {
-      const int cc = gbase + i;
-      if (cc < n) gmax = max(gmax, p.right[row * n + cc] - p.left[row * n + cc]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
-  } else {  // block_chunk == 16: a group is one half-warp
-    gmax = in_range ? (right - left) : 0;
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
-  }
-  const int my_rounds = gmax >= 1 ? 32 - __clz(gmax) : 0;
+  const int my_rounds = chunk_rounds(p, row, n, wbase, lane, in_range, left, right);
   int max_rounds = my_rounds;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) max_rounds = max(max_rounds, __shfl_xor_sync(0xffffffffu, max_rounds, o));
 
   float score = HIPATTN_SCORE_INIT;
-  unsigned char* wstage = kstage + (size_t)warp * 64 * G::kRowStride;
-  const unsigned char* my_l = wstage + (size_t)lane * G::kRowStride;
-  const unsigned char* my_r = wstage + (size_t)(32 + lane) * G::kRowStride;
-  const int ntile = Rpad / RT;
 
   for (int it = 0; it < max_rounds; ++it) {
     const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
@@ -262,6 +230,7 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
     if (p.right_out) p.right_out[o] = right;
     if (p.score_out) p.score_out[o] = score;
   }
+  }  // chunk blocks
 }
 
 template <int DT, int D, int RT>
@@ -276,12 +245,14 @@ int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
   HIPATTN_REQUIRE(smem <= 227 * 1024, HIPATTN_ERR_UNSUPPORTED,
                   "scan stage needs %zu bytes of shared memory (query rows %d, head dim %d)", smem, R, D);
   const int BDST = cdiv(p.TQ, p.block_size_q);
-  const int nblk = cdiv(p.n_chunks, 32 * NW);
-  const int64_t grid = (int64_t)p.B * p.HKV * BDST * (p.H / p.HKV) * nblk;
+  const int nblk_total = cdiv(p.n_chunks, 32 * NW);
+  const int64_t units = (int64_t)p.B * p.H * BDST;
+  const int nblk = scan_ctas_per_unit(units, nblk_total);
+  const int64_t grid = units * nblk;
   HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
   auto kern = scan_stage_kernel<DT, D, RT>;
   HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)grid, 32 * NW, smem, stream>>>(p, nblk, NW);
+  kern<<<(unsigned)grid, 32 * NW, smem, stream>>>(p, nblk, nblk_total, NW);
   return check_launch("scan_stage_kernel");
 }
 
@@ -331,7 +302,9 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
   const int eb = p->dtype == HIPATTN_F32 ? 4 : 2;
   int rc = validate_tokens(p->k, eb, p->D, "k");
   if (rc) return rc;
-  HIPATTN_REQUIRE(((uintptr_t)p->q % eb) == 0, HIPATTN_ERR_INVALID, "scan stage: q is misaligned");
+  const int64_t ra = 16 / eb;
+  HIPATTN_REQUIRE(((uintptr_t)p->q % 16) == 0 && p->q_stride_b % ra == 0 && p->q_stride_t % ra == 0 && p->q_stride_h % ra == 0,
+                  HIPATTN_ERR_INVALID, "scan stage: q rows must start on 16-byte boundaries");
   cudaStream_t s = (cudaStream_t)stream;
   HIPATTN_REQUIRE(p->mode >= HIPATTN_SCAN_AUTO && p->mode <= HIPATTN_SCAN_CHECK, HIPATTN_ERR_INVALID, "scan stage: unknown mode %d", p->mode);
   bool handled = false;

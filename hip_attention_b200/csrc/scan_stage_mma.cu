@@ -18,7 +18,7 @@
 // staged in row (l / 4) * 8 + (l % 4) * 2 + e, which is the MMA column whose accumulator lives in
 // lane l itself (columns are held by lanes with the same lane % 4), so no exchange is needed after
 // the row reduction.
-#include "common.cuh"
+#include "scan_common.cuh"
 
 namespace hipattn {
 namespace {
@@ -77,7 +77,7 @@ __device__ __forceinline__ uint32_t pack_scalar2(float x) {
 enum { ST_KEYS = 0, ST_FALLBACK = 1, ST_WRONG = 2, ST_RATIO_BITS = 3 };
 
 template <int DT, int D, int MT>
-__global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_params_t p, int nblk, int NW, int check) {
+__global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int NW, int check) {
   using T = typename Elem<DT>::type;
   constexpr int ROWB = D * 2;                 // bytes per key / query row
   constexpr int STRIDE = ROWB + kPadBytes;    // padded row stride: conflict-free ldmatrix and lane reads
@@ -109,85 +109,39 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
   __shared__ int s_pmin;
   __shared__ float s_qmax;
 
-  // ---- pooled queries (identical arithmetic to the strict kernel) ----
+  // ---- pooled queries (identical arithmetic to the strict kernel), once per CTA ----
   if (threadIdx.x == 0) s_qmax = 0.f;
   __syncthreads();
   float qmax_local = 0.f;
-  for (int i = threadIdx.x; i < Rpad * D; i += blockDim.x) {
-    const int r = i / D, e = i - r * D;
-    float v = 0.f;
-    if (r < Rv) {
-      float sum = 0.f, cnt = 0.f;
-      const int t = t0 + r * p.stride_q;
-      for (int o = 0; o < p.stride_q; ++o) {
-        if (t + o < p.TQ) {
-          const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(t + o) * p.q_stride_t +
-                        (int64_t)h * p.q_stride_h + e;
-          sum = __fadd_rn(sum, Elem<DT>::to_f32(*qp));
-          cnt += 1.f;
-        }
-      }
-      v = Elem<DT>::round(__fdiv_rn(sum, __fadd_rn(cnt, 1e-12f)));
-      v = Elem<DT>::round(__fmul_rn(v, p.q_scale));
+  for (int i = threadIdx.x; i < Rpad * PIECES; i += blockDim.x) {
+    const int r = i / PIECES, pc = i % PIECES;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    if (r < Rv) pooled_query_piece<DT>(p, b, h, t0 + r * p.stride_q, pc, v);
+    T* dst = reinterpret_cast<T*>(q16 + (size_t)r * STRIDE + pc * 16);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      dst[e] = Elem<DT>::from_f32(v[e]);
+      qmax_local = fmaxf(qmax_local, fabsf(v[e]));
     }
-    reinterpret_cast<T*>(q16 + (size_t)r * STRIDE)[e] = Elem<DT>::from_f32(v);
-    qmax_local = fmaxf(qmax_local, fabsf(v));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) qmax_local = fmaxf(qmax_local, __shfl_xor_sync(0xffffffffu, qmax_local, o));
   if (lane == 0) atomicMax(reinterpret_cast<int*>(&s_qmax), __float_as_int(qmax_local));  // non-negative floats order as ints
   if (warp == 0) {
-    long long m = 0x7fffffffffffffffLL;
-    for (int r = lane; r < Rv; r += 32) {
-      long long pv = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(t0 + r * p.stride_q) * p.pos_stride_t];
-      m = pv < m ? pv : m;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      long long x = __shfl_xor_sync(0xffffffffu, m, o);
-      m = x < m ? x : m;
-    }
-    if (lane == 0) s_pmin = (int)(m > 0x7fffffffLL ? 0x7fffffffLL : m);
+    const int m = block_min_position(p, b, t0, Rv, lane);
+    if (lane == 0) s_pmin = m;
   }
   __syncthreads();
   if (Rv == 0) return;
   const int pt = max(s_pmin - p.scan_window, 0);
   const float eps_q = kEps * s_qmax;
-
-  // ---- this lane's chunk ----
   const int n = p.n_chunks;
-  const int c = (cblk * NW + warp) * 32 + lane;
   const int64_t row = (int64_t)b * BDST + d;
-  int left = 0, right = 0;
-  const bool in_range = c < n;
-  if (in_range) {
-    left = p.left[row * n + c];
-    right = p.right[row * n + c];
-  }
-  int gmax;
-  if ((p.block_chunk & 31) == 0) {
-    const int gbase = (((cblk * NW + warp) * 32) / p.block_chunk) * p.block_chunk;
-    gmax = 0;
-    for (int i = lane; i < p.block_chunk; i += 32) {
-      const int cc = gbase + i;
-      if (cc < n) gmax = max(gmax, p.right[row * n + cc] - p.left[row * n + cc]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
-  } else {
-    gmax = in_range ? (right - left) : 0;
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
-  }
-  const int my_rounds = gmax >= 1 ? 32 - __clz(gmax) : 0;
-  int max_rounds = my_rounds;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) max_rounds = max(max_rounds, __shfl_xor_sync(0xffffffffu, max_rounds, o));
 
-  float score = HIPATTN_SCORE_INIT;
   unsigned char* wstage = kstage + (size_t)warp * 64 * STRIDE;
   float* wkf = kf32 + warp * D;
-  const int my_row_l = (lane >> 2) * 8 + (lane & 3) * 2;  // staged row of this lane's left key (right: + 1)
   const uint32_t kscale2 = pack_scalar2<DT>(p.k_scale);
   const uint32_t ones2 = pack_scalar2<DT>(1.0f);
   const uint32_t ones_frag[4] = {ones2, ones2, ones2, ones2};
@@ -232,6 +186,22 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
     for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
     return best;
   };
+
+  // ---- chunk blocks of this CTA ----
+  for (int cb = cblk; cb < nblk_total; cb += nblk) {
+  const int wbase = (cb * NW + warp) * 32;
+  const int c = wbase + lane;
+  int left = 0, right = 0;
+  const bool in_range = c < n;
+  if (in_range) {
+    left = p.left[row * n + c];
+    right = p.right[row * n + c];
+  }
+  const int my_rounds = chunk_rounds(p, row, n, wbase, lane, in_range, left, right);
+  int max_rounds = my_rounds;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) max_rounds = max(max_rounds, __shfl_xor_sync(0xffffffffu, max_rounds, o));
+  float score = HIPATTN_SCORE_INIT;
 
   for (int it = 0; it < max_rounds; ++it) {
     const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
@@ -378,6 +348,7 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
     if (p.right_out) p.right_out[o] = right;
     if (p.score_out) p.score_out[o] = score;
   }
+  }  // chunk blocks
   if (p.stats) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -406,12 +377,14 @@ int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
   const size_t smem = q_bytes + (size_t)NW * (64 * STRIDE + D * 4);
   HIPATTN_REQUIRE(smem <= 227 * 1024, HIPATTN_ERR_UNSUPPORTED, "scan stage needs %zu bytes of shared memory", smem);
   const int BDST = cdiv(p.TQ, p.block_size_q);
-  const int nblk = cdiv(p.n_chunks, 32 * NW);
-  const int64_t grid = (int64_t)p.B * p.HKV * BDST * (p.H / p.HKV) * nblk;
+  const int nblk_total = cdiv(p.n_chunks, 32 * NW);
+  const int64_t units = (int64_t)p.B * p.H * BDST;
+  const int nblk = scan_ctas_per_unit(units, nblk_total);
+  const int64_t grid = units * nblk;
   HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
   auto kern = scan_stage_mma_kernel<DT, D, MT>;
   HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)grid, 32 * NW, smem, stream>>>(p, nblk, NW, p.mode == 2 ? 1 : 0);
+  kern<<<(unsigned)grid, 32 * NW, smem, stream>>>(p, nblk, nblk_total, NW, p.mode == 2 ? 1 : 0);
   return check_launch("scan_stage_mma_kernel");
 }
 
