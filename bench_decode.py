@@ -1,0 +1,267 @@
+"""Decode workloads of bench.py (BASELINE configs 3 and 4); selected with ``bench.py --workload decode_128k | decode_1m``.
+
+``decode_128k``: 32 sequences of 131072 tokens in a paged cache (page 64, permuted page table); one step
+is one ``hip_attention_12`` call with one query row per sequence; the mask is re-estimated every 8th
+step and reused in between (``cached_metadata``), 64 steps are averaged.  The sequence length is held
+constant so that every step costs the same.
+``decode_1m``: one sequence of 1048576 tokens cut into 8 logical shards of 131072 tokens; each shard is
+an operator call on its pages (top-k 512 per shard, sink in the first, window in the last shard) and
+the partial outputs are merged by log-sum-exp.  With N GPUs each rank runs 8 / N shards and the
+partials are all-gathered.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import numpy as np
+import torch
+
+import bench
+
+
+def _paged_pool(w, dev, kv_heads=None, seqs=None, t0=0, t1=None):
+    """Build the page pool for sequences ``seqs`` (default all) over tokens [t0, t1)."""
+    B, T, HKV, D, P = w["B"], w["T"], w["HKV"], w["D"], w["page"]
+    t1 = T if t1 is None else t1
+    dt = bench._DT[w["dtype"]]
+    hk = range(HKV)[kv_heads] if kv_heads is not None else range(HKV)
+    nh = len(hk)
+    pages_per_seq = (t1 - t0) // P
+    n_pages = B * pages_per_seq + 17
+    g = torch.Generator(device="cpu")
+    g.manual_seed(w["seed"] + 7)
+    perm = torch.randperm(n_pages, generator=g)[: B * pages_per_seq].view(B, pages_per_seq).to(dev)
+    kc = torch.zeros((n_pages, P, nh, D), dtype=dt, device=dev)
+    vc = torch.zeros((n_pages, P, nh, D), dtype=dt, device=dev)
+    needles = None
+    for b in range(B):
+        gg = torch.Generator(device=dev)
+        gg.manual_seed(w["seed"] * 100 + b)
+        step = 131072
+        for s0 in range(0, T, step):  # full sequence is generated so that every slice sees the same values
+            k = torch.randn((1, step, HKV, D), generator=gg, device=dev, dtype=torch.float32)
+            k = bench.rope(k, torch.arange(s0, s0 + step, device=dev), w["theta"])
+            if w["heavy"] > 0:
+                hh = torch.rand((1, step), generator=gg, device=dev) < w["heavy"]
+                k = torch.where(hh[:, :, None, None], k * 4.0, k)
+            v = torch.randn((1, step, HKV, D), generator=gg, device=dev, dtype=torch.float32)
+            lo, hi = max(s0, t0), min(s0 + step, t1)
+            if lo < hi:
+                ks = k[0, lo - s0: hi - s0][:, list(hk)].to(dt)
+                vs = v[0, lo - s0: hi - s0][:, list(hk)].to(dt)
+                pg = perm[b, (lo - t0) // P: (hi - t0) // P]
+                kc[pg] = ks.view(-1, P, nh, D)
+                vc[pg] = vs.view(-1, P, nh, D)
+    return kc, vc, perm.to(torch.int32)
+
+
+def _queries(w, dev, steps, heads=None):
+    g = torch.Generator(device=dev)
+    g.manual_seed(w["seed"] * 1000 + 1)
+    q = torch.randn((steps, w["B"], 1, w["H"], w["D"]), generator=g, device=dev, dtype=torch.float32)
+    pos = torch.full((1,), w["T"] - 1, device=dev)
+    q = bench.rope(q.flatten(0, 1), pos.expand(1), w["theta"]).view_as(q) * (w["D"] ** -0.5)
+    q = q.to(bench._DT[w["dtype"]])
+    if heads is not None:
+        q = q[:, :, :, heads].contiguous()
+    return q
+
+
+def _emit(a, w, line):
+    print(json.dumps(line), flush=True)
+
+
+def run(a, w):
+    import torch.distributed as dist
+    from hip_attention_b200 import PhaseTimer, hip_attention_impl
+    from hip_attention_b200.sharded import hip_attention_12_sequence_sharded
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    steps = a.steps if a.steps != 5 else 64
+    B, T, H, HKV, D = w["B"], w["T"], w["H"], w["HKV"], w["D"]
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(bench.ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if w["kind"] == "decode":
+        if world > 1:
+            raise SystemExit("decode_128k is a single-GPU workload (independent sequences: run replicas)")
+        kc, vc, table = _paged_pool(w, dev)
+        seq = torch.full((B,), T, dtype=torch.int32, device=dev)
+        pos = torch.full((B, 1), T - 1, dtype=torch.int64, device=dev)
+        args = bench.make_args(w, k_cache=kc, v_cache=vc, block_table=table, cache_seq_lens=seq, position_ids=pos,
+                               extend_context_length=T)
+        qs = _queries(w, dev, steps)
+        refresh = w["refresh"]
+
+        def run_steps(n, timers=None, host=None):
+            md = None
+            for i in range(n):
+                t = PhaseTimer() if timers is not None else None
+                if host is not None:
+                    q = host["dq"]
+                    q.copy_(host["hq"][i], non_blocking=True)
+                else:
+                    q = qs[i]
+                out, md = hip_attention_impl(q, None, None, args, None if i % refresh == 0 else md, timer=t)
+                if host is not None:
+                    host["ho"].copy_(out, non_blocking=True)
+                if timers is not None:
+                    timers.append(t)
+            return out
+
+        run_steps(max(a.warmup, 3) * refresh // refresh + refresh)  # at least one refresh + cached steps
+        barrier()
+        sampler = bench.ClockSampler(local)
+        sampler.start()
+        timers = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run_steps(steps, timers)
+        e1.record()
+        barrier()
+        clocks = sampler.stop()
+        ms_step = e0.elapsed_time(e1) / steps
+        ph_refresh, ph_cached, n_r, n_c = {}, {}, 0, 0
+        for i, t in enumerate(timers):
+            tgt = ph_refresh if i % refresh == 0 else ph_cached
+            for k_, v_ in t.milliseconds().items():
+                tgt[k_] = tgt.get(k_, 0.0) + v_
+            n_r += i % refresh == 0
+            n_c += i % refresh != 0
+        ph_refresh = {k_: v_ / max(1, n_r) for k_, v_ in ph_refresh.items() if k_ != "start"}
+        ph_cached = {k_: v_ / max(1, n_c) for k_, v_ in ph_cached.items() if k_ != "start"}
+        host = {"hq": qs.cpu().pin_memory(), "dq": torch.empty_like(qs[0]),
+                "ho": torch.empty(qs[0].shape, dtype=qs.dtype).pin_memory()}
+        run_steps(refresh, host=host)
+        barrier()
+        e0.record()
+        run_steps(steps, host=host)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / steps
+        sb = bench.scan_bytes(w, H)
+        scan_ms = sum(v_ for k_, v_ in ph_refresh.items() if k_.startswith("scan"))
+        att_bytes = B * HKV * (w["keep"][-1] + w["sink"] + w["sw"]) * D * 2 * 2
+        att_ms = ph_cached.get("attention", 0.0)
+        line = {
+            "metric": "hip_decode_ms_per_step", "value": ms_step, "unit": "ms/step", "n_gpus": 1, "steps": steps,
+            "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": a.workload, "B": B, "TQ": 1, "T": T, "H": H, "HKV": HKV, "D": D, "page": w["page"],
+                       "mask_refresh_every": refresh, "l2": "page pool of 2 x 8.6 GB exceeds the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": qs[0].numel() * 2,
+                    "d2h_bytes_per_step": qs[0].numel() * 2},
+            "gpu_launches": None,
+            "phases_ms": {"refresh_step": ph_refresh, "cached_step": ph_cached},
+            "roofline": {"kernel": "scan_stage_kernel (refresh steps)", "bound": "hbm",
+                         "achieved": sb / 1e9 / (scan_ms / 1e3) if scan_ms else None, "peak": peak, "peak_source": peak_src,
+                         "unit": "GB/s", "frac": (sb / 1e9 / (scan_ms / 1e3)) / peak if scan_ms else None, "traffic": None,
+                         "algorithmic_bytes_per_refresh": sb},
+            "attention_roofline": {"kernel": "bsa_generic_kernel (split-KV decode)", "bound": "hbm",
+                                   "achieved": att_bytes / 1e9 / (att_ms / 1e3) if att_ms else None, "peak": peak,
+                                   "unit": "GB/s", "frac": (att_bytes / 1e9 / (att_ms / 1e3)) / peak if att_ms else None,
+                                   "algorithmic_bytes_per_step": att_bytes},
+        }
+        n_launch_refresh = 3 + len(w["chunks"]) + 3 * (len(w["chunks"]) - 1) + 1
+        line["gpu_launches"] = n_r * n_launch_refresh + n_c * 2
+        if not a.no_cpu_baseline:
+            line["cpu_baseline"] = _cpu_decode(w)
+        return _emit(a, w, line)
+
+    # ---- sequence-sharded million-token decode -----------------------------------------------------
+    S = w["shards"]
+    if S % world:
+        raise SystemExit(f"{S} shards cannot be split over {world} ranks")
+    per = S // world
+    L = T // S
+    shard_kv = []
+    for j in range(per):
+        s = rank * per + j
+        kc, vc, table = _paged_pool(w, dev, t0=s * L, t1=(s + 1) * L)
+        shard_kv.append((kc, vc, table, torch.full((B,), L, dtype=torch.int32, device=dev)))
+    qs = _queries(w, dev, steps)
+    args = bench.make_args(w)
+
+    def one(i, cached):
+        return hip_attention_12_sequence_sharded(qs[i], shard_kv, args, n_shards=S, shard_len=L, per_shard_k=w["keep"][-1],
+                                                 first_shard=rank * per, cached=cached)
+
+    for i in range(max(a.warmup, 3)):
+        out, mds = one(i, None)
+    barrier()
+    sampler = bench.ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        out, mds = one(i, None)   # every step re-estimates the mask: the worst case
+    e1.record()
+    barrier()
+    tms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    e0.record()
+    for i in range(steps):
+        out, _ = one(i, mds)      # cached masks: attention + merge only
+    e1.record()
+    barrier()
+    tms2 = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tms2, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        clocks = sampler.stop()
+        ms_step = float(tms.item()) / steps
+        wsh = dict(w, T=L)
+        sb = bench.scan_bytes(wsh, H) * S
+        line = {"metric": "hip_decode_ms_per_step", "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": steps,
+                "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
+                "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+                "config": {"workload": a.workload, "B": B, "TQ": 1, "T": T, "H": H, "HKV": HKV, "D": D, "page": w["page"],
+                           "logical_shards": S, "per_shard_top_k": w["keep"][-1], "mask": "re-estimated every step"},
+                "clocks": clocks, "cached_mask_ms_per_step": float(tms2.item()) / steps,
+                "roofline": {"kernel": "scan_stage_kernel", "bound": "hbm", "achieved": None, "peak": peak,
+                             "peak_source": peak_src, "unit": "GB/s", "frac": None, "traffic": None,
+                             "algorithmic_bytes_per_step": sb,
+                             "note": "whole-step figure: bytes / step time = %.1f GB/s" % (sb / 1e9 / (ms_step / 1e3))}}
+        _emit(a, w, line)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _cpu_decode(w):
+    """CPU oracle on one of the B sequences: one refresh step and one cached step, scaled to B sequences."""
+    from oracle import hip_oracle as O
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    w1 = dict(w, B=1)
+    q, k, v = bench.make_qkv(w1, "cpu")
+    cfg = bench.oracle_config(w1)
+    pos = torch.full((1, 1), w["T"] - 1, dtype=torch.int64)
+    ks, vs = O.DenseKV(k), O.DenseKV(v)
+    t0 = time.perf_counter()
+    m = O.estimate_mask(q, ks, pos, cfg)
+    t1 = time.perf_counter()
+    O.attention_on_mask(q, ks, vs, pos, m, sink=cfg.sink, sw=max(cfg.sw, cfg.stages[0].chunk_size), dtype=torch.float32)
+    t2 = time.perf_counter()
+    r = w["refresh"]
+    per_seq = ((t1 - t0) + r * (t2 - t1)) / r
+    return {"value": 1e3 * per_seq * w["B"], "unit": "ms/step", "cores": cores, "kind": "port",
+            "sample": f"1 of {w['B']} sequences (estimator {t1 - t0:.2f} s once per {r} steps, attention {t2 - t1:.3f} s per step), "
+                      f"scaled by {w['B']}"}

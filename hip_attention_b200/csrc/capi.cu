@@ -39,6 +39,7 @@ int validate_tokens(const hipattn_tokens_t& t, int elem_bytes, int D, const char
 
 int bsa_generic(const hipattn_bsa_params_t& p, cudaStream_t stream);
 int bsa_mma(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
+int bsa_decode(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
 
 namespace {
 
@@ -93,6 +94,8 @@ extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream
   rc = validate_tokens(p->v, eb, p->D, "v");
   if (rc) return rc;
   bool handled = false;
+  rc = bsa_decode(*p, (cudaStream_t)stream, &handled);
+  if (handled) return rc;
   rc = bsa_mma(*p, (cudaStream_t)stream, &handled);
   if (handled) return rc;
   return bsa_generic(*p, (cudaStream_t)stream);

@@ -334,9 +334,10 @@ def _restart_inputs(entry: HiPAttentionStageInputCache, rows: int) -> Tuple[Tens
 
 
 def _decode_splits(B: int, HKV: int, total_tokens: int) -> int:
-    want = _cdiv(2 * 148, max(1, B * HKV))
-    by_len = max(1, total_tokens // 128)
-    return int(max(1, min(16, want, by_len)))
+    """Key ranges per (sequence, KV head): enough CTAs for ~6 per SM, at least 256 keys per range."""
+    want = _cdiv(148 * 6, max(1, B * HKV))
+    by_len = max(1, total_tokens // 256)
+    return int(max(1, min(32, want, by_len)))
 
 
 def _attention(q: Tensor, ktok: L.Tokens, vtok: L.Tokens, T: int, HKV: int, pos: Tensor, indices: Tensor, ks: Tensor,
