@@ -241,11 +241,14 @@ def main():
     ap.add_argument("--workload", default="prefill_128k", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tq", type=int, default=0, help="profiling aid: shrink the number of queries (not a bench value)")
+    ap.add_argument("--batch", type=int, default=0, help="profiling aid: shrink the batch (not a bench value)")
     ap.add_argument("--cpu-blocks", type=int, default=6, help="query blocks of the CPU baseline sample")
     a = ap.parse_args()
     w = dict(WORKLOADS[a.workload])
     if a.tq:
         w["TQ"] = a.tq
+    if a.batch:
+        w["B"] = a.batch
     if a.impl == "reference":
         return run_reference_arm(a, w)
     if w["kind"] != "prefill":

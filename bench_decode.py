@@ -115,9 +115,9 @@ def run(a, w):
                 t = PhaseTimer() if timers is not None else None
                 if host is not None:
                     q = host["dq"]
-                    q.copy_(host["hq"][i], non_blocking=True)
+                    q.copy_(host["hq"][i % steps], non_blocking=True)
                 else:
-                    q = qs[i]
+                    q = qs[i % steps]
                 out, md = hip_attention_impl(q, None, None, args, None if i % refresh == 0 else md, timer=t)
                 if host is not None:
                     host["ho"].copy_(out, non_blocking=True)

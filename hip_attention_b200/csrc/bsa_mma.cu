@@ -9,6 +9,7 @@
 // accumulators; Q fragments live in registers; softmax is online in base 2; tiles whose keys are
 // admitted for every row skip the per-element admission test.
 #include "bsa_common.cuh"
+#include "mma_common.cuh"
 
 namespace hipattn {
 namespace {
@@ -24,42 +25,6 @@ struct TileMeta {
   int far_ok[2];       // per half tile: every key valid, far rule, admitted by every row
   int win_ok[2];       // per half tile: every key valid, window rule, admitted by every row
 };
-
-template <int DT>
-__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  if (DT == HIPATTN_BF16) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  } else {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-}
-__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
-}
-template <int DT>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  if (DT == HIPATTN_BF16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-  __half2 v = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// byte address of 16-byte piece `piece` of row `row` in a swizzled [rows][D] tile of 2-byte elements
-template <int D>
-__device__ __forceinline__ int swz(int row, int piece) {
-  return row * (D * 2) + ((piece ^ (row & 7)) << 4);
-}
 
 template <int DT, int D, int M>
 __global__ void __launch_bounds__(M * 2) bsa_mma_kernel(const hipattn_bsa_params_t p, int BQ, int n_sub) {

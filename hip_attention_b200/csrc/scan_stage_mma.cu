@@ -18,6 +18,7 @@
 // staged in row (l / 4) * 8 + (l % 4) * 2 + e, which is the MMA column whose accumulator lives in
 // lane l itself (columns are held by lanes with the same lane % 4), so no exchange is needed after
 // the row reduction.
+#include "mma_common.cuh"
 #include "scan_common.cuh"
 
 namespace hipattn {
@@ -25,23 +26,6 @@ namespace {
 
 constexpr float kEps = 1.0f / (1 << 21);
 constexpr int kPadBytes = 16;
-
-template <int DT>
-__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  if (DT == HIPATTN_BF16) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  } else {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-}
-__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
-}
 
 // element-wise product of two packed 16-bit pairs, rounded to nearest even (one rounding of the exact product)
 template <int DT>

@@ -334,10 +334,15 @@ def _restart_inputs(entry: HiPAttentionStageInputCache, rows: int) -> Tuple[Tens
 
 
 def _decode_splits(B: int, HKV: int, total_tokens: int) -> int:
-    """Key ranges per (sequence, KV head): enough CTAs for ~6 per SM, at least 256 keys per range."""
-    want = _cdiv(148 * 6, max(1, B * HKV))
-    by_len = max(1, total_tokens // 256)
-    return int(max(1, min(32, want, by_len)))
+    """Key ranges per (sequence, KV head).  One range when the batch alone fills the GPU (two CTAs per
+    SM); otherwise enough ranges to do so, each at least four tiles (256 keys) long."""
+    forced = os.environ.get("HIPATTN_DECODE_SPLITS")
+    if forced:
+        return max(1, min(64, int(forced)))
+    units = max(1, B * HKV)
+    if units >= 148:
+        return 1
+    return int(max(1, min(32, _cdiv(148 * 2, units), total_tokens // 256)))
 
 
 def _attention(q: Tensor, ktok: L.Tokens, vtok: L.Tokens, T: int, HKV: int, pos: Tensor, indices: Tensor, ks: Tensor,
