@@ -265,12 +265,13 @@ def next_stage_inputs(left: torch.Tensor, cfg: OracleConfig, i: int):
 
 def estimate_mask(q: torch.Tensor, ksrc, pos: torch.Tensor, cfg: OracleConfig,
                   restart: Optional[Tuple[int, torch.Tensor, torch.Tensor]] = None,
-                  keep_stage_outputs: bool = False) -> OracleMask:
+                  keep_stage_outputs: bool = False, score_reduce=None) -> OracleMask:
     """Run the hierarchical mask estimator.
 
     q [B, TQ, H, D] (pre-scaled by the caller), ksrc a DenseKV/PagedKV over K, pos [B, TQ] int64.
     restart = (stage index i, left, right) resumes from the cached inputs of stage i
-    (``attention_extend.py:2047-2071``).
+    (``attention_extend.py:2047-2071``).  score_reduce(tensor), if given, completes the head max in place
+    across the processes of a KV-head-parallel run.
     """
     B, TQ, H, D = q.shape
     T = ksrc.T
@@ -311,6 +312,9 @@ def estimate_mask(q: torch.Tensor, ksrc, pos: torch.Tensor, cfg: OracleConfig,
                                         G=G, block_chunk=block_chunk, dtype=q.dtype)
                 nl[b, d], nr[b, d], scores[b, d] = l2, r2, s2
         red = scores.max(dim=2, keepdim=True).values  # head reduce, ``attention_extend.py:2566-2570``
+        if score_reduce is not None:  # heads split over processes: finish the max across them
+            red = red.contiguous()
+            score_reduce(red)
         if keep_stage_outputs:
             out.stage_outputs.append((nl.clone(), nr.clone(), scores.clone(), red[:, :, 0].clone()))
         if i < len(cfg.stages) - 1:
