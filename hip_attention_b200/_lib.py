@@ -9,7 +9,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libhipattn_sm100.so")
 
 F32, F16, BF16 = 0, 1, 2
-STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE = 1, 2
+STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE, STATUS_TIMEOUT = 1, 2, 4
 MAX_CHUNKS = 16384
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
 ABI_VERSION = 2

@@ -1,0 +1,456 @@
+// Block-sparse attention, prefill, 16-bit types, head dim 128: tcgen05 / TMEM kernel.
+//
+// One CTA (128 threads, one warpgroup) owns 128 query rows -- two heads of a KV group x 64 rows, or
+// one head x 128 rows -- and walks the key list [sink | selected blocks | window] in tiles of 64 keys.
+// Two CTAs are resident per SM, so one CTA's softmax overlaps the other's tensor-core work.
+//
+//   S = Q K^T   tcgen05.mma (M 128, N 64, K 16) x 8, operands in shared memory (128-byte-swizzled
+//               canonical layouts, K-major), accumulator in TMEM columns [0, 64)
+//   softmax     thread t owns row t = TMEM lane t: tcgen05.ld of its 64 logits, admission rule,
+//               base-2 online softmax with a lazily updated maximum, P written to shared memory as
+//               the next A operand
+//   O += P V    tcgen05.mma (M 128, N 128, K 16) x 4 into TMEM columns [64, 192); V is staged row-major
+//               (MN-major operand)
+//
+// K / V rows are gathered by all threads with 16-byte cp.async through the page table directly into
+// the swizzled operand layouts.  O stays in TMEM for the whole key list: the running maximum used
+// for the exponentials is only raised (and O rescaled in TMEM) when the true maximum has grown by
+// more than 2^8, which keeps P within bf16 / fp16 range and makes rescaling rare.
+// Every wait on an mbarrier is bounded; a wait that runs out sets HIPATTN_STATUS_TIMEOUT and the CTA
+// leaves through the normal exit (TMEM freed), so a fault in the pipeline cannot hang the device.
+#include "bsa_common.cuh"
+
+namespace hipattn {
+namespace {
+
+constexpr int TK5 = 64;            // keys per tile
+constexpr int D5 = 128;            // head dimension
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr unsigned long long kWaitNs = 20ull * 1000 * 1000;  // 20 ms: a tile takes microseconds
+constexpr float kRescaleThreshold = 8.f;  // log2 of the growth that triggers a rescale
+
+struct Meta5 {
+  int tpos[TK5];
+  int twin[TK5];
+  long long koff[TK5];
+  long long voff[TK5];
+  int far_ok[2];
+  int win_ok[2];
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// shared-memory matrix descriptor, 128-byte swizzle (layout type 2), version 1
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// instruction descriptor: fp32 accumulator, A K-major, B K-major or MN-major
+__device__ __forceinline__ uint32_t make_idesc(int fmt, int M, int N, int b_mn_major) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u));
+}
+__device__ __forceinline__ void umma_commit(uint32_t mbar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+// wait on an mbarrier phase for at most kWaitNs; returns false (and raises the abort flag) when time runs out
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+  if (*abort_flag) return false;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
+    if (done) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kWaitNs) break;
+  }
+  *abort_flag = 1;
+  atomicOr(status, HIPATTN_STATUS_TIMEOUT);
+  return false;
+}
+
+template <int DT>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (DT == HIPATTN_BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// byte offset of 16-byte chunk `c` (0..7) of 128-byte row `r` inside a 128-byte-swizzled tile
+__device__ __forceinline__ int sw128(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
+
+template <int DT>
+__global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_params_t p, int BQ, int n_sub) {
+  using T = typename Elem<DT>::type;
+  constexpr int Q_BYTES = 2 * 128 * 128;      // [2 k-blocks][128 rows][128 B]
+  constexpr int KT_BYTES = 2 * TK5 * 128;     // [2 k-blocks][64 keys][128 B]
+  constexpr int P_BYTES = 128 * 128;          // [128 rows][64 keys] 16-bit
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  unsigned char* sQ = smem;                   // also the output staging area
+  unsigned char* sK = sQ + Q_BYTES;           // 2 buffers
+  unsigned char* sV = sK + 2 * KT_BYTES;      // 1 buffer: [2 d-blocks][64 keys][128 B]
+  unsigned char* sP = sV + KT_BYTES;
+  Meta5* meta = reinterpret_cast<Meta5*>(sP + P_BYTES);  // 3 entries
+  __shared__ __align__(8) unsigned long long s_mbar[2];   // S ready, O ready
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+  __shared__ int s_rowpos[128];
+  __shared__ int s_mm[4];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int Gq = p.H / p.HKV;
+  const int NH = 128 / BQ;
+  const int NBLK = cdiv(p.TQ, p.block_size_q);
+  const int hslots = p.H / NH;
+  int64_t bid = blockIdx.x;
+  const int sub = (int)(bid % n_sub); bid /= n_sub;
+  const int d = (int)(bid % NBLK); bid /= NBLK;
+  const int hs = (int)(bid % hslots); bid /= hslots;
+  const int b = (int)bid;
+  const int h0 = hs * NH;
+  const int hkv = h0 / Gq;
+  const int blk_t0 = d * p.block_size_q;
+  const int blk_rows = min(p.block_size_q, p.TQ - blk_t0);
+  const int row_t0 = blk_t0 + sub * BQ;
+  const int rows_here = max(0, min(BQ, blk_rows - sub * BQ));
+  const uint32_t mbar_s = smem_u32(&s_mbar[0]), mbar_o = smem_u32(&s_mbar[1]);
+
+  // ---- set-up: barriers, TMEM (256 columns), positions, Q tile ----
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar_s));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar_o));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    s_abort = 0;
+  }
+  if (tid < 4) s_mm[tid] = (tid & 1) ? -1 : 0x7fffffff;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  {
+    int lo = 0x7fffffff, hi = -1;
+    for (int i = tid; i < blk_rows; i += 128) {
+      const long long x = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(blk_t0 + i) * p.pos_stride_t];
+      const int v = (int)(x > 0x7ffffff0LL ? 0x7ffffff0LL : (x < 0 ? 0 : x));
+      lo = min(lo, v); hi = max(hi, v);
+    }
+    if (hi >= 0) { atomicMin(&s_mm[0], lo); atomicMax(&s_mm[1], hi); }
+  }
+  {
+    const int i = tid % BQ;
+    int pv = -0x40000000;
+    if (i < rows_here) {
+      const long long x = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(row_t0 + i) * p.pos_stride_t];
+      pv = (int)(x > 0x7ffffff0LL ? 0x7ffffff0LL : (x < 0 ? 0 : x));
+      atomicMin(&s_mm[2], pv);
+      atomicMax(&s_mm[3], pv);
+    }
+    s_rowpos[tid] = pv;
+  }
+  for (int i = tid; i < 128 * 16; i += 128) {
+    const int r = i >> 4, pc = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if ((r % BQ) < rows_here) {
+      const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(row_t0 + r % BQ) * p.q_stride_t +
+                    (int64_t)(h0 + r / BQ) * p.q_stride_h + pc * 8;
+      v = *reinterpret_cast<const uint4*>(qp);
+    }
+    *reinterpret_cast<uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(r, pc & 7)) = v;
+  }
+  fence_async_smem();
+  __syncthreads();
+  const int pmin = s_mm[0], pmax = s_mm[1];
+  const int rmin = s_mm[2], rmax = s_mm[3];
+  const KeyList kl = make_key_list(p, b, h0, d, pmin, pmax);
+  const int n_tiles = cdiv(kl.total, TK5);
+  const char* kbase = (const char*)(p.k.cache ? p.k.cache : p.k.dense);
+  const char* vbase = (const char*)(p.v.cache ? p.v.cache : p.v.dense);
+
+  auto make_meta = [&](int tile) {
+    if (tid < TK5) {
+      Meta5& m = meta[tile % 3];
+      bool w;
+      const int j = tile * TK5 + tid;
+      const int t = key_position(kl, j, &w);
+      m.tpos[tid] = t;
+      m.twin[tid] = (t >= 0 && w) ? 1 : 0;
+      long long ko = -1, vo = -1;
+      if (t >= 0) {
+        ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
+        vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
+      }
+      m.koff[tid] = ko;
+      m.voff[tid] = vo;
+      const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
+      const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
+      const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
+      if ((tid & 31) == 0) {
+        m.far_ok[tid >> 5] = f;
+        m.win_ok[tid >> 5] = g;
+      }
+    }
+  };
+  // rows of a tile: 64 keys x 16 pieces; piece pc belongs to 64-element block pc >> 3
+  auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst) {
+    for (int i = tid; i < TK5 * 16; i += 128) {
+      const int r = i >> 4, pc = i & 15;
+      const long long o = off[r];
+      unsigned char* a = dst + (pc >> 3) * (TK5 * 128) + sw128(r, pc & 7);
+      if (o >= 0) cp_async16(a, base + o + pc * 16);
+      else *reinterpret_cast<uint4*>(a) = make_uint4(0, 0, 0, 0);
+    }
+  };
+
+  constexpr int FMT = DT == HIPATTN_BF16 ? 1 : 0;
+  const uint32_t idesc_s = make_idesc(FMT, 128, TK5, 0);
+  const uint32_t idesc_o = make_idesc(FMT, 128, D5, 1);
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+
+  float m_ref = -INFINITY;   // maximum the exponentials refer to
+  float l_run = 0.f;
+  const int prow = s_rowpos[tid];
+  const float cap = p.logit_softcap;
+  uint32_t phase = 0;
+  bool have_o = false;
+
+  if (n_tiles > 0) {
+    make_meta(0);
+    if (n_tiles > 1) make_meta(1);
+    __syncthreads();
+    gather_rows(meta[0].koff, kbase, sK);
+    cp_async_commit();
+  }
+  for (int it = 0; it < n_tiles; ++it) {
+    const Meta5& mt = meta[it % 3];
+    unsigned char* kb = sK + (it & 1) * KT_BYTES;
+    // V of this tile, then K of the next one
+    gather_rows(mt.voff, vbase, sV);
+    cp_async_commit();
+    if (it + 1 < n_tiles) gather_rows(meta[(it + 1) % 3].koff, kbase, sK + ((it + 1) & 1) * KT_BYTES);
+    cp_async_commit();
+    if (it + 2 < n_tiles) make_meta(it + 2);
+    cp_async_wait<2>();   // K of this tile has landed
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // ---- S = Q K^T ----
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t qa = smem_u32(sQ) + (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+        const uint32_t ka = smem_u32(kb) + (kk >> 2) * (TK5 * 128) + (kk & 3) * 32;
+        umma(tmem_s, make_desc(qa, 16, 1024), make_desc(ka, 16, 1024), idesc_s, kk > 0);
+      }
+      umma_commit(mbar_s);
+    }
+    mbar_wait(mbar_s, phase, &s_abort, p.status);
+    __syncwarp();
+    tc_fence_after();
+    // ---- softmax of row `tid` ----
+    float s[TK5];
+    tmem_ld32(tmem_s + lane_base, s);
+    tmem_ld32(tmem_s + lane_base + 32, s + 32);
+    const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < TK5; ++j) {
+      float x = s[j];
+      if (cap > 0.f) x = tanhf(x / cap) * cap;
+      x *= kLog2e;
+      if (!full && !admits(prow, mt.tpos[j], mt.twin[j] != 0, p.window)) x = -INFINITY;
+      s[j] = x;
+      mx = fmaxf(mx, x);
+    }
+    // raise the reference maximum only when needed; O (in TMEM) and l are rescaled together.
+    // tcgen05.ld / st are warp-collective: if any lane of the warp rescales, every lane takes the
+    // branch (lanes that need no change multiply by one).
+    const bool need = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
+    if (__any_sync(0xffffffffu, need)) {
+      const float alpha = !need ? 1.f : (m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx));
+      if (have_o) {
+#pragma unroll
+        for (int c = 0; c < D5; c += 32) {
+          float o[32];
+          tmem_ld32(tmem_o + lane_base + c, o);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= alpha;
+          tmem_st32(tmem_o + lane_base + c, o);
+        }
+      }
+      if (need) {
+        l_run *= alpha;
+        m_ref = mx;
+      }
+    }
+    const float base = m_ref > -INFINITY ? m_ref : 0.f;
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      float e[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        e[j] = exp2f(s[c * 8 + j] - base);
+        sum += e[j];
+      }
+      uint4 w;
+      w.x = pack2<DT>(e[0], e[1]); w.y = pack2<DT>(e[2], e[3]); w.z = pack2<DT>(e[4], e[5]); w.w = pack2<DT>(e[6], e[7]);
+      *reinterpret_cast<uint4*>(sP + sw128(tid, c)) = w;
+    }
+    l_run += sum;
+    cp_async_wait<1>();   // V of this tile has landed
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // ---- O += P V ----
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint32_t pa = smem_u32(sP) + kk * 32;
+        const uint32_t va = smem_u32(sV) + kk * 2048;
+        umma(tmem_o, make_desc(pa, 16, 1024), make_desc(va, TK5 * 128, 1024), idesc_o, (have_o || kk > 0) ? 1u : 0u);
+      }
+      umma_commit(mbar_o);
+    }
+    have_o = true;
+    mbar_wait(mbar_o, phase, &s_abort, p.status);
+    __syncwarp();
+    tc_fence_after();
+    phase ^= 1;
+    if (__syncthreads_or(s_abort)) break;  // leave together if any wait ran out
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  const bool aborted = s_abort != 0;
+
+  // ---- epilogue: O / l -> element type, staged through shared memory, 16-byte stores ----
+  const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll
+  for (int c = 0; c < D5; c += 32) {
+    float o[32];
+    if (have_o && !aborted) {
+      tmem_ld32(tmem_o + lane_base + c, o);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      uint4 w;
+      w.x = pack2<DT>(o[j] * inv, o[j + 1] * inv); w.y = pack2<DT>(o[j + 2] * inv, o[j + 3] * inv);
+      w.z = pack2<DT>(o[j + 4] * inv, o[j + 5] * inv); w.w = pack2<DT>(o[j + 6] * inv, o[j + 7] * inv);
+      const int pc = (c + j) >> 3;
+      *reinterpret_cast<uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(tid, pc & 7)) = w;
+    }
+  }
+  if (p.lse_out && (tid % BQ) < rows_here)
+    p.lse_out[((int64_t)b * p.TQ + row_t0 + tid % BQ) * p.H + h0 + tid / BQ] = l_run > 0.f ? m_ref + log2f(l_run) : -INFINITY;
+  tc_fence_before();
+  __syncthreads();
+  for (int i = tid; i < 128 * 16; i += 128) {
+    const int r = i >> 4, pc = i & 15;
+    if ((r % BQ) < rows_here) {
+      T* op = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_stride_b + (int64_t)(row_t0 + r % BQ) * p.o_stride_t +
+              (int64_t)(h0 + r / BQ) * p.o_stride_h + pc * 8;
+      *reinterpret_cast<uint4*>(op) = *reinterpret_cast<const uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(r, pc & 7));
+    }
+  }
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256u) : "memory");
+  }
+}
+
+template <int DT>
+int launch5(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t stream) {
+  const size_t smem = 1024 + 2 * 128 * 128 + 3 * (2 * TK5 * 128) + 128 * 128 + 3 * sizeof(Meta5);
+  const int NH = 128 / BQ;
+  const int NBLK = cdiv(p.TQ, p.block_size_q);
+  const int64_t grid = (int64_t)p.B * (p.H / NH) * NBLK * n_sub;
+  HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "attention grid of %lld blocks", (long long)grid);
+  auto kern = bsa_tcgen05_kernel<DT>;
+  HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)grid, 128, smem, stream>>>(p, BQ, n_sub);
+  return check_launch("bsa_tcgen05_kernel");
+}
+
+}  // namespace
+
+// Takes 16-bit prefill with head dim 128 and attention blocks of 64 rows (two heads of a KV group that
+// share their key list per CTA) or a multiple of 128 rows.
+int bsa_tcgen05(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled) {
+  *handled = false;
+  if (p.n_splits != 1 || p.dtype == HIPATTN_F32 || p.D != 128 || p.TQ < 64) return HIPATTN_OK;
+  if (((uintptr_t)p.out % 16) || (p.o_stride_b % 8) || (p.o_stride_t % 8) || (p.o_stride_h % 8)) return HIPATTN_OK;
+  const int Gq = p.H / p.HKV;
+  int BQ, n_sub;
+  if (p.block_size_q == 64 && p.heads_share_mask && (Gq % 2) == 0) { BQ = 64; n_sub = 1; }
+  else if (p.block_size_q % 128 == 0) { BQ = 128; n_sub = p.block_size_q / 128; }
+  else return HIPATTN_OK;
+  *handled = true;
+  return p.dtype == HIPATTN_BF16 ? launch5<HIPATTN_BF16>(p, BQ, n_sub, stream) : launch5<HIPATTN_F16>(p, BQ, n_sub, stream);
+}
+
+}  // namespace hipattn

@@ -2,6 +2,7 @@
 // log-sum-exp merge of partial outputs.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -40,6 +41,7 @@ int validate_tokens(const hipattn_tokens_t& t, int elem_bytes, int D, const char
 int bsa_generic(const hipattn_bsa_params_t& p, cudaStream_t stream);
 int bsa_mma(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
 int bsa_decode(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
+int bsa_tcgen05(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
 
 namespace {
 
@@ -96,6 +98,12 @@ extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream
   bool handled = false;
   rc = bsa_decode(*p, (cudaStream_t)stream, &handled);
   if (handled) return rc;
+  // HIPATTN_PREFILL_KERNEL=mma keeps prefill on the warp-level tensor-core kernel (for comparisons)
+  const char* pk = getenv("HIPATTN_PREFILL_KERNEL");
+  if (!(pk && strcmp(pk, "mma") == 0)) {
+    rc = bsa_tcgen05(*p, (cudaStream_t)stream, &handled);
+    if (handled) return rc;
+  }
   rc = bsa_mma(*p, (cudaStream_t)stream, &handled);
   if (handled) return rc;
   return bsa_generic(*p, (cudaStream_t)stream);

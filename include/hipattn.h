@@ -32,6 +32,7 @@ extern "C" {
 /* Bits of the device status word written by the kernels (0 = clean). */
 #define HIPATTN_STATUS_PAGE_RANGE 1u  /* a block-table entry pointed outside the page pool; clamped */
 #define HIPATTN_STATUS_TOKEN_RANGE 2u /* a token index fell outside [0, T); clamped                 */
+#define HIPATTN_STATUS_TIMEOUT 4u     /* a bounded on-chip wait ran out; the launch's output is invalid */
 
 #define HIPATTN_SCORE_INIT (-32000.0f) /* attention_extend.py:2040-2045 */
 #define HIPATTN_INDEX_PAD INT64_MAX    /* attention_extend.py:2913 */

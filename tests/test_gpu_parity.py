@@ -265,3 +265,30 @@ def test_scan_tensor_core_path_is_exact(dtype, monkeypatch):
     assert torch.equal(md_auto.indices, md_strict.indices) and torch.equal(md_auto.ks, md_strict.ks)
     assert torch.equal(md_check.indices, md_strict.indices)
     print(f"scan check {dtype}: keys {keys} fallbacks {fallbacks} ({100 * fallbacks / keys:.2f} %) max ratio {ratio:.4f}")
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("bq,tq,hkv", [(64, 300, 2), (128, 300, 2), (64, 64, 4), (64, 1024, 1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prefill_head_dim_128_matches_oracle(kernel, bq, tq, hkv, dtype, monkeypatch):
+    """Head dim 128 (the shape of the benchmark configs): both tensor-core prefill kernels against the
+    fp64 recompute on the oracle's mask, ragged last block included."""
+    import bench
+    from hip_attention_b200 import hip_attention_impl, read_status
+    monkeypatch.setenv("HIPATTN_PREFILL_KERNEL", kernel)
+    w = dict(bench.WORKLOADS["prefill_128k"], TQ=tq, T=4096, H=8, HKV=hkv, bq=bq, keep=[2048, 1024, 512], sink=64, sw=256,
+             dtype={torch.bfloat16: "bf16", torch.float16: "fp16"}[dtype])
+    q, k, v = bench.make_qkv(w, "cuda")
+    read_status("cuda")
+    out, md, lse = hip_attention_impl(q, k, v, bench.make_args(w), return_lse=True)
+    torch.cuda.synchronize()
+    assert read_status("cuda") == 0
+    cfg = bench.oracle_config(w)
+    pos = (torch.arange(tq) + w["T"] - tq)[None]
+    qc, kc, vc = q.cpu(), k.cpu(), v.cpu()
+    m = O.estimate_mask(qc, O.DenseKV(kc), pos, cfg)
+    assert torch.equal(md.indices.cpu(), m.indices) and torch.equal(md.ks.cpu(), m.ks)
+    ref, lse_ref = O.attention_on_mask(qc, O.DenseKV(kc), O.DenseKV(vc), pos, m, sink=cfg.sink,
+                                       sw=max(cfg.sw, cfg.stages[0].chunk_size), return_lse=True)
+    _check_out(out, ref, dtype)
+    assert (lse.cpu().double() - lse_ref).abs().max().item() < 2e-2
