@@ -19,6 +19,7 @@ struct KeyList {
   int pmax;
   const int64_t* idx;  // selected block starts of this query block
   int block_k, sink, T;
+  int block_k_shift;   // log2(block_k) when it is a power of two, else -1
 };
 
 __device__ __forceinline__ KeyList make_key_list(const hipattn_bsa_params_t& p, int b, int h, int d, int pmin, int pmax) {
@@ -29,6 +30,7 @@ __device__ __forceinline__ KeyList make_key_list(const hipattn_bsa_params_t& p, 
   long long ks = p.ks[n * p.ks_stride_n + (int64_t)d_idx * p.ks_stride_d];
   ks = ks < 0 ? 0 : (ks > p.K ? p.K : ks);
   kl.block_k = p.block_size_k;
+  kl.block_k_shift = (p.block_size_k & (p.block_size_k - 1)) == 0 ? 31 - __clz(p.block_size_k) : -1;
   kl.sink = p.sink;
   kl.T = p.T;
   kl.pmax = pmax;
@@ -48,8 +50,9 @@ __device__ __forceinline__ int key_position(const KeyList& kl, int j, bool* is_w
   if (j < kl.n_sink) return j;
   j -= kl.n_sink;
   if (j < kl.n_sel) {
-    const long long start = kl.idx[j / kl.block_k];
-    const long long t = start + (j % kl.block_k);
+    const int blk = kl.block_k_shift >= 0 ? (j >> kl.block_k_shift) : (j / kl.block_k);
+    const long long start = kl.idx[blk];
+    const long long t = start + (j - blk * kl.block_k);
     if (t < kl.sink || t > kl.pmax || t >= kl.T) return -1;
     return (int)t;
   }

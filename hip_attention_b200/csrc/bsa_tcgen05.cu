@@ -26,7 +26,7 @@ namespace {
 constexpr int TK5 = 64;            // keys per tile
 constexpr int D5 = 128;            // head dimension
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr unsigned long long kWaitNs = 20ull * 1000 * 1000;  // 20 ms: a tile takes microseconds
+constexpr long long kWaitCycles = 40ll * 1000 * 1000;  // about 20 ms of SM clocks: a tile takes microseconds
 constexpr float kRescaleThreshold = 8.f;  // log2 of the growth that triggers a rescale
 
 struct Meta5 {
@@ -78,6 +78,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -97,15 +108,10 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
-  return t;
-}
-// wait on an mbarrier phase for at most kWaitNs; returns false (and raises the abort flag) when time runs out
+// wait on an mbarrier phase for at most kWaitCycles SM clocks; returns false (and raises the abort
+// flag) when time runs out
 __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
-  if (*abort_flag) return false;
-  const unsigned long long t0 = global_ns();
+  const long long t0 = clock64();
   for (;;) {
     uint32_t done;
     asm volatile(
@@ -113,7 +119,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, volati
         : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
     if (done) return true;
     if (*abort_flag) return false;
-    if (global_ns() - t0 > kWaitNs) break;
+    if (clock64() - t0 > kWaitCycles) break;
   }
   *abort_flag = 1;
   atomicOr(status, HIPATTN_STATUS_TIMEOUT);
@@ -250,14 +256,19 @@ __global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_p
       }
     }
   };
-  // rows of a tile: 64 keys x 16 pieces; piece pc belongs to 64-element block pc >> 3
+  // rows of a tile: 64 keys x 16 pieces; piece pc belongs to 64-element block pc >> 3.  Thread tid
+  // always copies piece tid & 15 of rows (tid >> 4) + 8 i, so its destination offsets never change.
+  const int g_pc = tid & 15, g_r0 = tid >> 4;
+  int g_dst[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) g_dst[i] = (g_pc >> 3) * (TK5 * 128) + sw128(g_r0 + 8 * i, g_pc & 7);
   auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst) {
-    for (int i = tid; i < TK5 * 16; i += 128) {
-      const int r = i >> 4, pc = i & 15;
-      const long long o = off[r];
-      unsigned char* a = dst + (pc >> 3) * (TK5 * 128) + sw128(r, pc & 7);
-      if (o >= 0) cp_async16(a, base + o + pc * 16);
-      else *reinterpret_cast<uint4*>(a) = make_uint4(0, 0, 0, 0);
+    const char* src = base + g_pc * 16;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const long long o = off[g_r0 + 8 * i];
+      if (o >= 0) cp_async16(dst + g_dst[i], src + o);
+      else *reinterpret_cast<uint4*>(dst + g_dst[i]) = make_uint4(0, 0, 0, 0);
     }
   };
 
@@ -274,55 +285,95 @@ __global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_p
   uint32_t phase = 0;
   bool have_o = false;
 
+  // descriptors differ only in their start-address field (low word); the high words are constants
+  const uint64_t dk = make_desc(0, 16, 1024);            // K-major operands: Q, K, P
+  const uint64_t dv = make_desc(0, TK5 * 128, 1024);     // MN-major operand: V
+  const uint32_t q_lo = smem_u32(sQ) >> 4, k_lo = smem_u32(sK) >> 4, p_lo = smem_u32(sP) >> 4, v_lo = smem_u32(sV) >> 4;
+  constexpr int kIssuer = 96;  // first lane of warp 3: warps 0 and 1 resolve addresses, keep them free
+  auto issue_s = [&](int tile) {   // S(tile) = Q K(tile)^T, by one thread
+    const uint32_t kb = k_lo + (tile & 1) * (KT_BYTES >> 4);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const uint32_t off = (kk >> 2) * ((128 * 128) >> 4) + (kk & 3) * 2;
+      const uint32_t offk = (kk >> 2) * ((TK5 * 128) >> 4) + (kk & 3) * 2;
+      umma(tmem_s, dk | (uint64_t)((q_lo + off) & 0x3fffu), dk | (uint64_t)((kb + offk) & 0x3fffu), idesc_s, kk > 0);
+    }
+    umma_commit(mbar_s);
+  };
+  auto issue_o = [&](bool accumulate) {   // O (+)= P V, by one thread
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      umma(tmem_o, dk | (uint64_t)((p_lo + kk * 2) & 0x3fffu), dv | (uint64_t)((v_lo + kk * 128) & 0x3fffu), idesc_o,
+           (accumulate || kk > 0) ? 1u : 0u);
+    umma_commit(mbar_o);
+  };
+
+  // Pipeline invariant at the top of iteration `it`: S(it) has been issued; the gathers of V(it) and
+  // K(it + 1) have been issued; PV(it - 1) has completed.
   if (n_tiles > 0) {
     make_meta(0);
     if (n_tiles > 1) make_meta(1);
     __syncthreads();
     gather_rows(meta[0].koff, kbase, sK);
     cp_async_commit();
-  }
-  for (int it = 0; it < n_tiles; ++it) {
-    const Meta5& mt = meta[it % 3];
-    unsigned char* kb = sK + (it & 1) * KT_BYTES;
-    // V of this tile, then K of the next one
-    gather_rows(mt.voff, vbase, sV);
-    cp_async_commit();
-    if (it + 1 < n_tiles) gather_rows(meta[(it + 1) % 3].koff, kbase, sK + ((it + 1) & 1) * KT_BYTES);
-    cp_async_commit();
-    if (it + 2 < n_tiles) make_meta(it + 2);
-    cp_async_wait<2>();   // K of this tile has landed
+    cp_async_wait<0>();
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
-    // ---- S = Q K^T ----
-    if (tid == 0) {
+    if (tid == kIssuer) {
       tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t qa = smem_u32(sQ) + (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-        const uint32_t ka = smem_u32(kb) + (kk >> 2) * (TK5 * 128) + (kk & 3) * 32;
-        umma(tmem_s, make_desc(qa, 16, 1024), make_desc(ka, 16, 1024), idesc_s, kk > 0);
-      }
-      umma_commit(mbar_s);
+      issue_s(0);
     }
+    gather_rows(meta[0].voff, vbase, sV);
+    if (n_tiles > 1) gather_rows(meta[1].koff, kbase, sK + KT_BYTES);
+    cp_async_commit();
+  }
+  // optional cycle breakdown of CTA 0 / thread 0 (part_lse is unused by prefill): wait S, softmax,
+  // wait copies, barrier, issue, wait O, gather issue, meta
+  const bool prof = p.part_lse != nullptr && blockIdx.x == 0 && tid == kIssuer;
+  long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long tprev = clock64();
+  auto lap = [&](int i) { if (prof) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; } };
+  for (int it = 0; it < n_tiles; ++it) {
+    const Meta5& mt = meta[it % 3];
+    if (it + 2 < n_tiles) make_meta(it + 2);
+    lap(7);
+    // ---- softmax of row `tid` on S(it) ----
     mbar_wait(mbar_s, phase, &s_abort, p.status);
     __syncwarp();
     tc_fence_after();
-    // ---- softmax of row `tid` ----
-    float s[TK5];
-    tmem_ld32(tmem_s + lane_base, s);
-    tmem_ld32(tmem_s + lane_base + 32, s + 32);
+    lap(0);
+    // Two passes over the 64 logits of the row, 16 columns at a time, in rolled loops (a compact loop
+    // body keeps the instruction cache warm): pass 1 finds the row maximum, pass 2 exponentiates.
     const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < TK5; ++j) {
-      float x = s[j];
+    auto logit = [&](float x, int j) -> float {
       if (cap > 0.f) x = tanhf(x / cap) * cap;
       x *= kLog2e;
       if (!full && !admits(prow, mt.tpos[j], mt.twin[j] != 0, p.window)) x = -INFINITY;
-      s[j] = x;
-      mx = fmaxf(mx, x);
+      return x;
+    };
+    const bool plain = full && !(cap > 0.f);   // CTA-uniform: every key admitted for every row, no soft-cap
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    if (plain) {
+#pragma unroll 1
+      for (int c = 0; c < TK5 / 32; ++c) {
+        float v[32];
+        tmem_ld32(tmem_s + lane_base + c * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], v[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mx4[j] *= kLog2e;
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < TK5 / 16; ++c) {
+        float v[16];
+        tmem_ld16(tmem_s + lane_base + c * 16, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], logit(v[j], c * 16 + j));
+      }
     }
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     // raise the reference maximum only when needed; O (in TMEM) and l are rescaled together.
     // tcgen05.ld / st are warp-collective: if any lane of the warp rescales, every lane takes the
     // branch (lanes that need no change multiply by one).
@@ -330,7 +381,7 @@ __global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_p
     if (__any_sync(0xffffffffu, need)) {
       const float alpha = !need ? 1.f : (m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx));
       if (have_o) {
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < D5; c += 32) {
           float o[32];
           tmem_ld32(tmem_o + lane_base + c, o);
@@ -345,41 +396,73 @@ __global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_p
       }
     }
     const float base = m_ref > -INFINITY ? m_ref : 0.f;
-    float sum = 0.f;
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (plain) {
+#pragma unroll 1
+      for (int c = 0; c < TK5 / 32; ++c) {
+        float v[32];
+        tmem_ld32(tmem_s + lane_base + c * 32, v);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      float e[8];
+        for (int j = 0; j < 32; ++j) {
+          v[j] = exp2f(fmaf(v[j], kLog2e, -base));
+          sum4[j & 3] += v[j];
+        }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        e[j] = exp2f(s[c * 8 + j] - base);
-        sum += e[j];
+        for (int g8 = 0; g8 < 4; ++g8) {
+          uint4 w;
+          w.x = pack2<DT>(v[g8 * 8 + 0], v[g8 * 8 + 1]); w.y = pack2<DT>(v[g8 * 8 + 2], v[g8 * 8 + 3]);
+          w.z = pack2<DT>(v[g8 * 8 + 4], v[g8 * 8 + 5]); w.w = pack2<DT>(v[g8 * 8 + 6], v[g8 * 8 + 7]);
+          *reinterpret_cast<uint4*>(sP + sw128(tid, c * 4 + g8)) = w;
+        }
       }
-      uint4 w;
-      w.x = pack2<DT>(e[0], e[1]); w.y = pack2<DT>(e[2], e[3]); w.z = pack2<DT>(e[4], e[5]); w.w = pack2<DT>(e[6], e[7]);
-      *reinterpret_cast<uint4*>(sP + sw128(tid, c)) = w;
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < TK5 / 16; ++c) {
+        float v[16];
+        tmem_ld16(tmem_s + lane_base + c * 16, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          v[j] = exp2f(logit(v[j], c * 16 + j) - base);
+          sum4[j & 3] += v[j];
+        }
+        uint4 w0, w1;
+        w0.x = pack2<DT>(v[0], v[1]); w0.y = pack2<DT>(v[2], v[3]); w0.z = pack2<DT>(v[4], v[5]); w0.w = pack2<DT>(v[6], v[7]);
+        w1.x = pack2<DT>(v[8], v[9]); w1.y = pack2<DT>(v[10], v[11]); w1.z = pack2<DT>(v[12], v[13]); w1.w = pack2<DT>(v[14], v[15]);
+        *reinterpret_cast<uint4*>(sP + sw128(tid, c * 2)) = w0;
+        *reinterpret_cast<uint4*>(sP + sw128(tid, c * 2 + 1)) = w1;
+      }
     }
-    l_run += sum;
-    cp_async_wait<1>();   // V of this tile has landed
+    l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+    lap(1);
+    cp_async_wait<0>();   // V(it) and K(it + 1) have landed
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
-    // ---- O += P V ----
-    if (tid == 0) {
+    lap(2);
+    if (__syncthreads_or(s_abort)) break;  // leave together if any wait ran out
+    lap(3);
+    // ---- O += P V(it), then straight on to S(it + 1) ----
+    if (tid == kIssuer) {
       tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const uint32_t pa = smem_u32(sP) + kk * 32;
-        const uint32_t va = smem_u32(sV) + kk * 2048;
-        umma(tmem_o, make_desc(pa, 16, 1024), make_desc(va, TK5 * 128, 1024), idesc_o, (have_o || kk > 0) ? 1u : 0u);
-      }
-      umma_commit(mbar_o);
+      issue_o(have_o);
+      if (it + 1 < n_tiles) issue_s(it + 1);
     }
     have_o = true;
-    mbar_wait(mbar_o, phase, &s_abort, p.status);
+    lap(4);
+    mbar_wait(mbar_o, phase, &s_abort, p.status);   // PV(it) done: sV, sP and sK[it & 1] are free
     __syncwarp();
     tc_fence_after();
+    lap(5);
     phase ^= 1;
-    if (__syncthreads_or(s_abort)) break;  // leave together if any wait ran out
+    if (it + 1 < n_tiles) {
+      gather_rows(meta[(it + 1) % 3].voff, vbase, sV);
+      if (it + 2 < n_tiles) gather_rows(meta[(it + 2) % 3].koff, kbase, sK + (it & 1) * KT_BYTES);
+    }
+    cp_async_commit();
+    lap(6);
+  }
+  if (prof) {
+    for (int i = 0; i < 8; ++i) p.part_lse[i] = (float)pc[i];
+    p.part_lse[8] = (float)n_tiles;
   }
   cp_async_wait<0>();
   __syncthreads();

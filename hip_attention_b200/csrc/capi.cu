@@ -143,4 +143,4 @@ extern "C" float hipattn_decode_score(int32_t code) {
 }
 
 extern "C" const char* hipattn_error_string(void) { return g_error; }
-extern "C" int hipattn_abi_version(void) { return 2; }
+extern "C" int hipattn_abi_version(void) { return 3; }

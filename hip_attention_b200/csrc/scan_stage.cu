@@ -282,6 +282,8 @@ int dispatch_dim(const hipattn_scan_params_t& p, cudaStream_t stream) {
 }  // namespace
 
 int scan_stage_mma(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
+int key_abs_sum(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* out,
+                uint32_t* status, cudaStream_t stream);
 
 }  // namespace hipattn
 
@@ -316,4 +318,14 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
     case HIPATTN_BF16: return dispatch_dim<HIPATTN_BF16>(*p, s);
     default: set_error("scan stage: unknown dtype %d", p->dtype); return HIPATTN_ERR_INVALID;
   }
+}
+
+extern "C" int hipattn_key_abs_sum(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
+                                   float k_scale, float* out, uint32_t* status, void* stream) {
+  using namespace hipattn;
+  HIPATTN_REQUIRE(k && out && status, HIPATTN_ERR_INVALID, "key_abs_sum: null pointer");
+  HIPATTN_REQUIRE(B > 0 && T > 0 && HKV > 0, HIPATTN_ERR_INVALID, "key_abs_sum: bad shape");
+  int rc = validate_tokens(*k, dtype == HIPATTN_F32 ? 4 : 2, D, "k");
+  if (rc) return rc;
+  return key_abs_sum(*k, dtype, D, B, T, HKV, k_scale, out, status, (cudaStream_t)stream);
 }

@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
   if (Rv == 0) return;
   const int pt = max(s_pmin - p.scan_window, 0);
   const float eps_q = kEps * s_qmax;
+  const bool have_abs = p.key_abs != nullptr;
   const int n = p.n_chunks;
   const int64_t row = (int64_t)b * BDST + d;
 
@@ -225,6 +226,10 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
 
     // ---- approximate scores on tensor cores ----
     float xl = -INFINITY, xr = -INFINITY, sl_abs = 0.f, sr_abs = 0.f;
+    if (have_abs && act) {  // precomputed key magnitudes (one per key row of the call)
+      sl_abs = p.key_abs[((int64_t)b * p.T + tl) * p.HKV + hkv];
+      sr_abs = p.key_abs[((int64_t)b * p.T + tr) * p.HKV + hkv];
+    }
     for (int mg = 0; mg < n_mgroups; ++mg) {
       float acc[MT][8][4];
       float sab[8][4];
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
           bf[nt][0] = mul2<DT>(bf[nt][0], kscale2);
           bf[nt][1] = mul2<DT>(bf[nt][1], kscale2);
         }
-        if (mg == 0) {
+        if (mg == 0 && !have_abs) {
 #pragma unroll
           for (int nt = 0; nt < 8; ++nt) mma16816<DT>(sab[nt], ones_frag, bf[nt][0] & 0x7fff7fffu, bf[nt][1] & 0x7fff7fffu);
         }
@@ -288,7 +293,7 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
         if (nt == mynt) {
           xl = fmaxf(xl, cm[nt][0]);
           xr = fmaxf(xr, cm[nt][1]);
-          if (mg == 0) { sl_abs = sab[nt][0]; sr_abs = sab[nt][1]; }
+          if (mg == 0 && !have_abs) { sl_abs = sab[nt][0]; sr_abs = sab[nt][1]; }
         }
       }
     }
@@ -380,7 +385,47 @@ int dispatch_rows(const hipattn_scan_params_t& p, cudaStream_t stream) {
   return launch<DT, D, 4>(p, stream);
 }
 
+template <int DT>
+__global__ void key_abs_sum_kernel(const hipattn_tokens_t k, int D, int B, int T, int HKV, float k_scale, float* out,
+                                   uint32_t* status) {
+  // one row per group of (row bytes / 16) lanes; a 256-byte row takes 16 lanes
+  const int pieces = D * Elem<DT>::bytes / 16;
+  const int rows_per_block = blockDim.x / pieces;
+  const int sub = threadIdx.x / pieces, piece = threadIdx.x % pieces;
+  const int64_t total = (int64_t)B * T * HKV;
+  const uint32_t kscale2 = pack_scalar2<DT>(k_scale);
+  for (int64_t r = (int64_t)blockIdx.x * rows_per_block + sub; r < total; r += (int64_t)gridDim.x * rows_per_block) {
+    const int hkv = (int)(r % HKV);
+    const int64_t bt = r / HKV;
+    const int t = (int)(bt % T), b = (int)(bt / T);
+    const char* row = token_row(k, b, t, hkv, Elem<DT>::bytes, status);
+    const uint4 w = *reinterpret_cast<const uint4*>(row + piece * 16);
+    const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t m = mul2<DT>(v[i], kscale2) & 0x7fff7fffu;
+      s += lo_f32<DT>(m) + hi_f32<DT>(m);
+    }
+    for (int o = pieces >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (piece == 0) out[r] = s;
+  }
+}
+
 }  // namespace
+
+int key_abs_sum(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* out,
+                uint32_t* status, cudaStream_t stream) {
+  HIPATTN_REQUIRE(dtype == HIPATTN_BF16 || dtype == HIPATTN_F16, HIPATTN_ERR_UNSUPPORTED, "key_abs_sum: 16-bit element types only");
+  HIPATTN_REQUIRE(D == 64 || D == 128, HIPATTN_ERR_UNSUPPORTED, "key_abs_sum: head dimension %d is not built (64, 128)", D);
+  const int64_t total = (int64_t)B * T * HKV;
+  const int rows_per_block = 256 / (D * 2 / 16);
+  int64_t grid = (total + rows_per_block - 1) / rows_per_block;
+  if (grid > 148 * 32) grid = 148 * 32;
+  if (dtype == HIPATTN_BF16) key_abs_sum_kernel<HIPATTN_BF16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, out, status);
+  else key_abs_sum_kernel<HIPATTN_F16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, out, status);
+  return check_launch("key_abs_sum_kernel");
+}
 
 // Takes 16-bit prefill shapes (more than one pooled row, a multiple of 16 of them, head dim 64 or
 // 128); anything else stays on the strict kernel.

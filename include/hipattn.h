@@ -88,6 +88,8 @@ typedef struct hipattn_scan_params {
   int32_t* right_out;
   float* score_out;
   uint32_t* status;          /* one word, OR-ed with HIPATTN_STATUS_* */
+  const float* key_abs;      /* optional [B, T, HKV]: sum_d |round(k * k_scale)| per key row (hipattn_key_abs_sum);
+                                lets the tensor-core path skip computing it per round */
   uint64_t* stats;           /* optional, 4 words: keys scored, keys re-scored strictly, wrong shortcuts
                                 (check mode), largest deviation / allowed radius as float bits (check mode) */
   int32_t dtype, D, B, TQ, H, HKV, T;
@@ -101,6 +103,14 @@ typedef struct hipattn_scan_params {
 } hipattn_scan_params_t;
 
 int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);
+
+/*
+ * Per key row, sum over the head dimension of |round_to_dtype(k * k_scale)| as fp32, out [B, T, HKV].
+ * No counterpart in the reference: it is the magnitude from which the tensor-core scan derives the
+ * error radius of its approximate dot products, computed once per call instead of once per round.
+ */
+int hipattn_key_abs_sum(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
+                        float k_scale, float* out, uint32_t* status, void* stream);
 
 /*
  * Initial chunk list of stage 0 (attention_extend.py:2027-2046): left[c] = sink + c * chunk,
