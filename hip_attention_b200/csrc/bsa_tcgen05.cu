@@ -18,6 +18,9 @@
 // more than 2^8, which keeps P within bf16 / fp16 range and makes rescaling rare.
 // Every wait on an mbarrier is bounded; a wait that runs out sets HIPATTN_STATUS_TIMEOUT and the CTA
 // leaves through the normal exit (TMEM freed), so a fault in the pipeline cannot hang the device.
+#include <cstdlib>
+#include <cstring>
+
 #include "bsa_common.cuh"
 
 namespace hipattn {
@@ -506,6 +509,345 @@ __global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_p
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Warp-specialised variant (7 warps): warps 0-3 run the softmax (thread = query row = TMEM lane),
+// warp 4 issues the MMAs, warps 5-6 resolve key addresses and gather K / V rows.
+//   TMEM: S buffers at columns [0, 64) and [64, 128) (S(it) in buffer it & 1), O at [128, 256).
+//   P(it) is written back over the first 32 columns of S(it)'s buffer as packed 16-bit pairs and is
+//   the A operand of O += P V straight from TMEM, so no shared memory is needed for P.
+//   S runs two tiles ahead of the softmax: at the per-tile barrier the issuer launches PV(it) and
+//   S(it + 2), so the tensor pipe computes S(it + 1) / S(it + 2) while the softmax of tile it / it + 1 runs.
+//   K and V tiles are double buffered.
+// One CTA-wide barrier per tile; every mbarrier wait is bounded.
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u));
+}
+
+template <int DT>
+__global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bsa_params_t p, int BQ, int n_sub) {
+  using T = typename Elem<DT>::type;
+  constexpr int NT = 224;
+  constexpr int Q_BYTES = 2 * 128 * 128;
+  constexpr int KT_BYTES = 2 * TK5 * 128;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  unsigned char* sQ = smem;                   // also the output staging area
+  unsigned char* sK = sQ + Q_BYTES;           // 2 buffers
+  unsigned char* sV = sK + 2 * KT_BYTES;      // 2 buffers
+  Meta5* meta = reinterpret_cast<Meta5*>(sV + 2 * KT_BYTES);  // 4 entries
+  __shared__ __align__(8) unsigned long long s_mbar[3];   // S buffer 0 ready, S buffer 1 ready, PV done
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+  __shared__ int s_rowpos[128];
+  __shared__ int s_mm[4];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int Gq = p.H / p.HKV;
+  const int NH = 128 / BQ;
+  const int NBLK = cdiv(p.TQ, p.block_size_q);
+  const int hslots = p.H / NH;
+  int64_t bid = blockIdx.x;
+  const int sub = (int)(bid % n_sub); bid /= n_sub;
+  const int d = (int)(bid % NBLK); bid /= NBLK;
+  const int hs = (int)(bid % hslots); bid /= hslots;
+  const int b = (int)bid;
+  const int h0 = hs * NH;
+  const int hkv = h0 / Gq;
+  const int blk_t0 = d * p.block_size_q;
+  const int blk_rows = min(p.block_size_q, p.TQ - blk_t0);
+  const int row_t0 = blk_t0 + sub * BQ;
+  const int rows_here = max(0, min(BQ, blk_rows - sub * BQ));
+  const uint32_t mbar_s0 = smem_u32(&s_mbar[0]), mbar_o = smem_u32(&s_mbar[2]);
+
+  if (tid == 0) {
+    for (int i = 0; i < 3; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar_s0 + 8 * i));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    s_abort = 0;
+  }
+  if (tid < 4) s_mm[tid] = (tid & 1) ? -1 : 0x7fffffff;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  {
+    int lo = 0x7fffffff, hi = -1;
+    for (int i = tid; i < blk_rows; i += NT) {
+      const long long x = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(blk_t0 + i) * p.pos_stride_t];
+      const int v = (int)(x > 0x7ffffff0LL ? 0x7ffffff0LL : (x < 0 ? 0 : x));
+      lo = min(lo, v); hi = max(hi, v);
+    }
+    if (hi >= 0) { atomicMin(&s_mm[0], lo); atomicMax(&s_mm[1], hi); }
+  }
+  if (tid < 128) {
+    const int i = tid % BQ;
+    int pv = -0x40000000;
+    if (i < rows_here) {
+      const long long x = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(row_t0 + i) * p.pos_stride_t];
+      pv = (int)(x > 0x7ffffff0LL ? 0x7ffffff0LL : (x < 0 ? 0 : x));
+      atomicMin(&s_mm[2], pv);
+      atomicMax(&s_mm[3], pv);
+    }
+    s_rowpos[tid] = pv;
+  }
+  for (int i = tid; i < 128 * 16; i += NT) {
+    const int r = i >> 4, pc = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if ((r % BQ) < rows_here) {
+      const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(row_t0 + r % BQ) * p.q_stride_t +
+                    (int64_t)(h0 + r / BQ) * p.q_stride_h + pc * 8;
+      v = *reinterpret_cast<const uint4*>(qp);
+    }
+    *reinterpret_cast<uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(r, pc & 7)) = v;
+  }
+  fence_async_smem();
+  __syncthreads();
+  const int pmin = s_mm[0], pmax = s_mm[1];
+  const int rmin = s_mm[2], rmax = s_mm[3];
+  const KeyList kl = make_key_list(p, b, h0, d, pmin, pmax);
+  const int n_tiles = cdiv(kl.total, TK5);
+  constexpr int FMT = DT == HIPATTN_BF16 ? 1 : 0;
+  const uint32_t idesc_s = make_idesc(FMT, 128, TK5, 0);
+  const uint32_t idesc_o = make_idesc(FMT, 128, D5, 1);
+  const uint32_t tmem_o = tmem + 128;
+
+  if (warp >= 5) {
+    // ================================ producers: addresses + gathers ================================
+    const int ptid = tid - 160;  // 0..63
+    const char* kbase = (const char*)(p.k.cache ? p.k.cache : p.k.dense);
+    const char* vbase = (const char*)(p.v.cache ? p.v.cache : p.v.dense);
+    auto make_meta = [&](int tile) {
+      Meta5& m = meta[tile & 3];
+      bool w;
+      const int j = tile * TK5 + ptid;
+      const int t = key_position(kl, j, &w);
+      m.tpos[ptid] = t;
+      m.twin[ptid] = (t >= 0 && w) ? 1 : 0;
+      long long ko = -1, vo = -1;
+      if (t >= 0) {
+        ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
+        vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
+      }
+      m.koff[ptid] = ko;
+      m.voff[ptid] = vo;
+      const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
+      const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
+      const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
+      if (lane == 0) {
+        m.far_ok[ptid >> 5] = f;
+        m.win_ok[ptid >> 5] = g;
+      }
+    };
+    // thread ptid copies piece ptid & 15 of rows (ptid >> 4) + 4 i
+    const int g_pc = ptid & 15, g_r0 = ptid >> 4;
+    auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst) {
+      const char* src = base + g_pc * 16;
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const int r = g_r0 + 4 * i;
+        const long long o = off[r];
+        unsigned char* a = dst + (g_pc >> 3) * (TK5 * 128) + sw128(r, g_pc & 7);
+        if (o >= 0) cp_async16(a, src + o);
+        else *reinterpret_cast<uint4*>(a) = make_uint4(0, 0, 0, 0);
+      }
+    };
+    auto producer_sync = [&]() { asm volatile("bar.sync 1, 64;\n" ::: "memory"); };
+    for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t);
+    producer_sync();
+    if (n_tiles > 0) { gather_rows(meta[0].koff, kbase, sK); gather_rows(meta[0].voff, vbase, sV); }
+    if (n_tiles > 1) gather_rows(meta[1].koff, kbase, sK + KT_BYTES);
+    cp_async_commit();
+    cp_async_wait<0>();
+    fence_async_smem();
+    __syncthreads();  // B0: Q, K(0), K(1), V(0) are in place
+    for (int it = 0; it < n_tiles; ++it) {
+      if (it + 3 < n_tiles) make_meta(it + 3);
+      // K(it + 2) goes where K(it) was: wait until S(it) has been computed
+      if (it + 2 < n_tiles) {
+        mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
+        gather_rows(meta[(it + 2) & 3].koff, kbase, sK + (it & 1) * KT_BYTES);
+      }
+      cp_async_commit();
+      // V(it + 1) goes where V(it - 1) was: wait until PV(it - 1) has completed
+      if (it + 1 < n_tiles) {
+        if (it >= 1) mbar_wait(mbar_o, (it - 1) & 1, &s_abort, p.status);
+        gather_rows(meta[(it + 1) & 3].voff, vbase, sV + ((it + 1) & 1) * KT_BYTES);
+      }
+      cp_async_commit();
+      cp_async_wait<1>();   // K(it + 2) and V(it) have landed; V(it + 1) may still be in flight
+      fence_async_smem();
+      if (__syncthreads_or(s_abort)) break;  // B1(it)
+    }
+    cp_async_wait<0>();
+  } else if (warp == 4) {
+    // ================================ MMA issuer ================================
+    const uint64_t dk = make_desc(0, 16, 1024);
+    const uint64_t dv = make_desc(0, TK5 * 128, 1024);
+    const uint32_t q_lo = smem_u32(sQ) >> 4, k_lo = smem_u32(sK) >> 4, v_lo = smem_u32(sV) >> 4;
+    auto issue_s = [&](int tile) {
+      const uint32_t kb = k_lo + (tile & 1) * (KT_BYTES >> 4);
+      const uint32_t ts = tmem + (tile & 1) * 64;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t off = (kk >> 2) * ((128 * 128) >> 4) + (kk & 3) * 2;
+        const uint32_t offk = (kk >> 2) * ((TK5 * 128) >> 4) + (kk & 3) * 2;
+        umma(ts, dk | (uint64_t)((q_lo + off) & 0x3fffu), dk | (uint64_t)((kb + offk) & 0x3fffu), idesc_s, kk > 0);
+      }
+      umma_commit(mbar_s0 + 8 * (tile & 1));
+    };
+    __syncthreads();  // B0
+    if (lane == 0) {
+      tc_fence_after();
+      if (n_tiles > 0) issue_s(0);
+      if (n_tiles > 1) issue_s(1);
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+      if (__syncthreads_or(s_abort)) break;  // B1(it): P(it) is in TMEM, V(it) and K(it + 2) have landed
+      if (lane == 0) {
+        tc_fence_after();
+        const uint32_t tp = tmem + (it & 1) * 64;                        // P(it): 32 columns of packed pairs
+        const uint32_t vb = v_lo + (it & 1) * (KT_BYTES >> 4);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts(tmem_o, tp + kk * 8, dv | (uint64_t)((vb + kk * 128) & 0x3fffu), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(mbar_o);
+        if (it + 2 < n_tiles) issue_s(it + 2);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ================================ softmax: thread = row = TMEM lane ================================
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const int prow = s_rowpos[tid];
+    const float cap = p.logit_softcap;
+    float m_ref = -INFINITY, l_run = 0.f;
+    __syncthreads();  // B0
+    for (int it = 0; it < n_tiles; ++it) {
+      const Meta5& mt = meta[it & 3];
+      const uint32_t ts = tmem + (it & 1) * 64 + lane_base;
+      mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
+      __syncwarp();
+      tc_fence_after();
+      float s[TK5];
+      tmem_ld32(ts, s);
+      tmem_ld32(ts + 32, s + 32);
+      const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
+      if (!(full && !(cap > 0.f))) {   // CTA-uniform slow path: soft-cap and / or per-element admission
+#pragma unroll
+        for (int j = 0; j < TK5; ++j) {
+          float x = s[j];
+          if (cap > 0.f) x = tanhf(x / cap) * cap;
+          if (!full && !admits(prow, mt.tpos[j], mt.twin[j] != 0, p.window)) x = -INFINITY;
+          s[j] = x;
+        }
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < TK5; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kLog2e;
+      const bool need = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, need)) {   // warp-uniform: tcgen05.ld / st are warp-collective
+        const float alpha = !need ? 1.f : (m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx));
+        if (it > 0) {
+          mbar_wait(mbar_o, (it - 1) & 1, &s_abort, p.status);   // O is stable once PV(it - 1) is done
+          __syncwarp();
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < D5; c += 32) {
+            float o[32];
+            tmem_ld32(tmem_o + lane_base + c, o);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] *= alpha;
+            tmem_st32(tmem_o + lane_base + c, o);
+          }
+        }
+        if (need) {
+          l_run *= alpha;
+          m_ref = mx;
+        }
+      }
+      const float base = m_ref > -INFINITY ? m_ref : 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      float pk[32];
+#pragma unroll
+      for (int j = 0; j < TK5; j += 2) {
+        const float e0 = exp2f(fmaf(s[j], kLog2e, -base));
+        const float e1 = exp2f(fmaf(s[j + 1], kLog2e, -base));
+        sum4[(j >> 1) & 3] += e0 + e1;
+        pk[j >> 1] = __uint_as_float(pack2<DT>(e0, e1));
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_st32(ts, pk);        // P(it) over the first half of S(it)
+      tc_fence_before();
+      if (__syncthreads_or(s_abort)) break;  // B1(it)
+    }
+    // ---- epilogue for this thread's row ----
+    bool ok = n_tiles > 0;
+    if (ok) {
+      ok = mbar_wait(mbar_o, (n_tiles - 1) & 1, &s_abort, p.status);
+      __syncwarp();
+      tc_fence_after();
+    }
+    const bool warp_ok = __all_sync(0xffffffffu, ok);
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll 1
+    for (int c = 0; c < D5; c += 32) {
+      float o[32];
+      if (warp_ok) {
+        tmem_ld32(tmem_o + lane_base + c, o);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 w;
+        w.x = pack2<DT>(o[j] * inv, o[j + 1] * inv); w.y = pack2<DT>(o[j + 2] * inv, o[j + 3] * inv);
+        w.z = pack2<DT>(o[j + 4] * inv, o[j + 5] * inv); w.w = pack2<DT>(o[j + 6] * inv, o[j + 7] * inv);
+        const int pc = (c + j) >> 3;
+        *reinterpret_cast<uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(tid, pc & 7)) = w;
+      }
+    }
+    if (p.lse_out && (tid % BQ) < rows_here)
+      p.lse_out[((int64_t)b * p.TQ + row_t0 + tid % BQ) * p.H + h0 + tid / BQ] = l_run > 0.f ? m_ref + log2f(l_run) : -INFINITY;
+    tc_fence_before();
+  }
+  __syncthreads();  // all roles: output rows staged, every TMEM access finished
+  for (int i = tid; i < 128 * 16; i += NT) {
+    const int r = i >> 4, pc = i & 15;
+    if ((r % BQ) < rows_here) {
+      T* op = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_stride_b + (int64_t)(row_t0 + r % BQ) * p.o_stride_t +
+              (int64_t)(h0 + r / BQ) * p.o_stride_h + pc * 8;
+      *reinterpret_cast<uint4*>(op) = *reinterpret_cast<const uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(r, pc & 7));
+    }
+  }
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256u) : "memory");
+  }
+}
+
+template <int DT>
+int launch5_ws(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t stream) {
+  const size_t smem = 1024 + 2 * 128 * 128 + 4 * (2 * TK5 * 128) + 4 * sizeof(Meta5);
+  const int NH = 128 / BQ;
+  const int NBLK = cdiv(p.TQ, p.block_size_q);
+  const int64_t grid = (int64_t)p.B * (p.H / NH) * NBLK * n_sub;
+  HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "attention grid of %lld blocks", (long long)grid);
+  auto kern = bsa_tcgen05_ws_kernel<DT>;
+  HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)grid, 224, smem, stream>>>(p, BQ, n_sub);
+  return check_launch("bsa_tcgen05_ws_kernel");
+}
+
 template <int DT>
 int launch5(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t stream) {
   const size_t smem = 1024 + 2 * 128 * 128 + 3 * (2 * TK5 * 128) + 128 * 128 + 3 * sizeof(Meta5);
@@ -533,7 +875,10 @@ int bsa_tcgen05(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handle
   else if (p.block_size_q % 128 == 0) { BQ = 128; n_sub = p.block_size_q / 128; }
   else return HIPATTN_OK;
   *handled = true;
-  return p.dtype == HIPATTN_BF16 ? launch5<HIPATTN_BF16>(p, BQ, n_sub, stream) : launch5<HIPATTN_F16>(p, BQ, n_sub, stream);
+  const char* pk = getenv("HIPATTN_PREFILL_KERNEL");
+  if (pk && strcmp(pk, "tcgen05") == 0)   // single-warpgroup variant, kept for comparisons
+    return p.dtype == HIPATTN_BF16 ? launch5<HIPATTN_BF16>(p, BQ, n_sub, stream) : launch5<HIPATTN_F16>(p, BQ, n_sub, stream);
+  return p.dtype == HIPATTN_BF16 ? launch5_ws<HIPATTN_BF16>(p, BQ, n_sub, stream) : launch5_ws<HIPATTN_F16>(p, BQ, n_sub, stream);
 }
 
 }  // namespace hipattn

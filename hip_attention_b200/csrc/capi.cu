@@ -98,7 +98,8 @@ extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream
   bool handled = false;
   rc = bsa_decode(*p, (cudaStream_t)stream, &handled);
   if (handled) return rc;
-  // HIPATTN_PREFILL_KERNEL=mma keeps prefill on the warp-level tensor-core kernel (for comparisons)
+  // HIPATTN_PREFILL_KERNEL = tcgen05_ws (default: warp-specialised tcgen05 kernel) | tcgen05 (single
+  // warpgroup) | mma (mma.sync kernel); the last two exist for comparisons
   const char* pk = getenv("HIPATTN_PREFILL_KERNEL");
   if (!(pk && strcmp(pk, "mma") == 0)) {
     rc = bsa_tcgen05(*p, (cudaStream_t)stream, &handled);

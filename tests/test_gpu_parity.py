@@ -267,7 +267,7 @@ def test_scan_tensor_core_path_is_exact(dtype, monkeypatch):
     print(f"scan check {dtype}: keys {keys} fallbacks {fallbacks} ({100 * fallbacks / keys:.2f} %) max ratio {ratio:.4f}")
 
 
-@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_ws", "mma"])
 @pytest.mark.parametrize("bq,tq,hkv", [(64, 300, 2), (128, 300, 2), (64, 64, 4), (64, 1024, 1)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_prefill_head_dim_128_matches_oracle(kernel, bq, tq, hkv, dtype, monkeypatch):
