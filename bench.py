@@ -313,22 +313,48 @@ def main():
     n_scan = sum(1 for kk in phases if kk.startswith("scan"))
 
     # ---- end to end: pinned host inputs in, output back, every step ---------------------------
+    # Three streams (copy in, compute, copy out) and two sets of device buffers: the host-to-device
+    # copy of step i + 1 and the device-to-host copy of step i - 1 overlap the kernels of step i.
     hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
-    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    houts = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(2)]
+    dbuf = [tuple(torch.empty_like(x) for x in (q, k, v)) for _ in range(2)]
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    s_main = torch.cuda.current_stream(dev)
 
-    def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
-        o, _ = hip_attention_impl(dq, dk, dv, args, score_reduce=reduce)
-        hout.copy_(o, non_blocking=True)
+    def e2e_run(n):
+        ev_in = [None, None]      # inputs of buffer set j are on the device
+        ev_free = [None, None]    # kernels that read buffer set j are done
+        ev_out = [None, None]     # result j has been copied out
+        keep = []
+        for i in range(n):
+            j = i & 1
+            with torch.cuda.stream(s_in):
+                if ev_free[j] is not None:
+                    s_in.wait_event(ev_free[j])
+                for dst, src in zip(dbuf[j], (hq, hk, hv)):
+                    dst.copy_(src, non_blocking=True)
+                ev_in[j] = torch.cuda.Event()
+                ev_in[j].record(s_in)
+            s_main.wait_event(ev_in[j])
+            o, _ = hip_attention_impl(*dbuf[j], args, score_reduce=reduce)
+            ev_free[j] = torch.cuda.Event()
+            ev_free[j].record(s_main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_free[j])
+                if ev_out[j] is not None:
+                    s_out.wait_event(ev_out[j])
+                houts[j].copy_(o, non_blocking=True)
+                o.record_stream(s_out)
+                ev_out[j] = torch.cuda.Event()
+                ev_out[j].record(s_out)
+            keep.append(o)
+        s_main.wait_stream(s_in)
+        s_main.wait_stream(s_out)
 
-    e2e_step()
+    e2e_run(2)
     barrier()
     e0.record()
-    for _ in range(a.steps):
-        e2e_step()
+    e2e_run(a.steps)
     e1.record()
     barrier()
     tms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
@@ -336,7 +362,7 @@ def main():
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
     e2e_ms = float(tms.item()) / a.steps
     h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv)) * world
-    d2h = hout.numel() * hout.element_size() * world
+    d2h = houts[0].numel() * houts[0].element_size() * world
 
     if rank == 0:
         peaks = {}
@@ -359,16 +385,21 @@ def main():
             "clocks": clocks,
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": (3 + len(w["chunks"]) + 3 * (len(w["chunks"]) - 1)) * a.steps,
+            "gpu_launches": (4 + len(w["chunks"]) + 3 * (len(w["chunks"]) - 1)) * a.steps,
             "phases_ms": {k_: round(v_, 4) for k_, v_ in phases.items() if k_ != "start"},
-            "roofline": {"kernel": "scan_stage_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+            "roofline": {"kernel": "scan_stage_mma_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak if achieved else None,
                          "traffic": None, "algorithmic_bytes_per_launch": sb / max(1, n_scan),
                          "launch_ms": scan_ms / max(1, n_scan),
-                         "note": "key-row gathers issued by the scan (mostly L2 hits in prefill: K per KV head is 33.5 MB)"},
-            "attention": {"flops": attention_flops(w, heads_local), "ms": phases.get("attention"),
-                          "tflops": attention_flops(w, heads_local) / 1e12 / (phases.get("attention", 0) / 1e3)
-                          if phases.get("attention") else None},
+                         "note": "algorithmic = key-row gathers issued by the three scan launches (mostly L2 hits in "
+                                 "prefill: K per KV head is 33.5 MB); achieved = their bytes / their summed CUDA-event time"},
+            "attention_roofline": {"kernel": "bsa_tcgen05_ws_kernel", "bound": "tensor",
+                                   "achieved": attention_flops(w, heads_local) / 1e12 / (phases.get("attention", 0) / 1e3)
+                                   if phases.get("attention") else None,
+                                   "peak": peaks.get("bf16_tflops"), "unit": "TFLOP/s",
+                                   "frac": (attention_flops(w, heads_local) / 1e12 / (phases.get("attention", 0) / 1e3)) /
+                                   peaks["bf16_tflops"] if phases.get("attention") and "bf16_tflops" in peaks else None,
+                                   "flops_per_launch": attention_flops(w, heads_local), "launch_ms": phases.get("attention")},
         }
         if world == 1 and not a.no_cpu_baseline:
             cores = len(os.sched_getaffinity(0))

@@ -237,7 +237,8 @@ template <int DT, int D, int RT>
 int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
   using G = RowGeom<DT, D>;
   const int R = p.block_size_q / p.stride_q;
-  const int Rpad = cdiv(R, RT) * RT;
+  const int rows = min(R, cdiv(p.TQ, p.stride_q));   // pooled rows that can be valid (1 for decode)
+  const int Rpad = cdiv(rows, RT) * RT;
   const size_t q_bytes = (size_t)Rpad * D * sizeof(float);
   int NW = 4;
   while (NW > 1 && q_bytes + (size_t)NW * 64 * G::kRowStride > 100 * 1024) NW >>= 1;
