@@ -292,3 +292,37 @@ def test_prefill_head_dim_128_matches_oracle(kernel, bq, tq, hkv, dtype, monkeyp
                                        sw=max(cfg.sw, cfg.stages[0].chunk_size), return_lse=True)
     _check_out(out, ref, dtype)
     assert (lse.cpu().double() - lse_ref).abs().max().item() < 2e-2
+
+
+def test_decode_under_cuda_graph_capture():
+    """With position_ids given the operator makes no host synchronisation, so a decode step (mask
+    refresh or cached mask) can be captured in a CUDA graph and replayed on new queries
+    (reference: attention_extend.py:1980-1982, tests/v1_2/test_attention_decode_bsa.py:66-101)."""
+    from hip_attention_b200 import hip_attention_12, read_status
+    q, k, v, pos, c, cfg, _ = case_inputs("decode_fp16", torch.bfloat16)
+    dev = "cuda"
+    k, v, pos = k.to(dev), v.to(dev), pos.to(dev)
+    q_static = q.to(dev).clone()
+    read_status(dev)
+    args = make_args(c, pos)
+    eager_out, eager_md = hip_attention_12(q_static, k, v, args)          # also warms allocations
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        hip_attention_12(q_static, k, v, args)
+        hip_attention_12(q_static, k, v, args, cached_metadata=eager_md)
+    torch.cuda.current_stream().wait_stream(side)
+    g_refresh, g_cached = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_refresh):
+        out_r, md_r = hip_attention_12(q_static, k, v, args)
+    with torch.cuda.graph(g_cached):
+        out_c, _ = hip_attention_12(q_static, k, v, args, cached_metadata=md_r)
+    q2 = torch.roll(q.to(dev), 5, dims=-1).contiguous()
+    q_static.copy_(q2)
+    g_refresh.replay()
+    g_cached.replay()
+    torch.cuda.synchronize()
+    ref_out, ref_md = hip_attention_12(q2, k, v, args)
+    assert torch.equal(md_r.indices, ref_md.indices)
+    assert torch.equal(out_r, ref_out) and torch.equal(out_c, ref_out)
+    assert read_status(dev) == 0
