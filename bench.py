@@ -51,6 +51,9 @@ WORKLOADS = {
                       heavy=0.0, seed=1237, page=64, shards=8, needles=64),
 }
 _DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+# dram__bytes_read.sum + dram__bytes_write.sum per scan launch (mean of the three stages), from the ncu capture
+# summarised in profiles/prefill128k_dram_traffic.md; keyed by (workload, GPUs, queries)
+NCU_DRAM_BYTES_PER_SCAN_LAUNCH = {("prefill_128k", 1, 32768): (568933376 + 581785344 + 359806464) / 3}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -389,7 +392,8 @@ def main():
             "phases_ms": {k_: round(v_, 4) for k_, v_ in phases.items() if k_ != "start"},
             "roofline": {"kernel": "scan_stage_mma_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                         "traffic": None, "algorithmic_bytes_per_launch": sb / max(1, n_scan),
+                         "traffic": NCU_DRAM_BYTES_PER_SCAN_LAUNCH.get((a.workload, world, w["TQ"])),
+                         "algorithmic_bytes_per_launch": sb / max(1, n_scan),
                          "launch_ms": scan_ms / max(1, n_scan),
                          "note": "algorithmic = key-row gathers issued by the three scan launches (mostly L2 hits in "
                                  "prefill: K per KV head is 33.5 MB); achieved = their bytes / their summed CUDA-event time"},
