@@ -64,6 +64,7 @@ SYMBOLS = {
     "hipattn_decode_score": (f32, [i32]),
     "hipattn_decode_scores": (i32, [vp, vp, i64, vp]),
     "hipattn_widen_i32": (i32, [vp, vp, i64, vp]),
+    "hipattn_debug_bounded_wait": (i32, [vp, vp]),
     "hipattn_error_string": (C.c_char_p, []),
     "hipattn_abi_version": (i32, []),
 }

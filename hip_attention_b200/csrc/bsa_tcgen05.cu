@@ -861,7 +861,27 @@ int launch5(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t strea
   return check_launch("bsa_tcgen05_kernel");
 }
 
+// One CTA waits on an mbarrier that nothing ever arrives on, through the same bounded wait the
+// attention kernel uses, and then leaves normally: exercises the time-out path without any fault.
+__global__ void bounded_wait_probe_kernel(uint32_t* status) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bar)));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    abort_flag = 0;
+  }
+  __syncthreads();
+  mbar_wait(smem_u32(&bar), 0, &abort_flag, status);
+  __syncthreads();
+}
+
 }  // namespace
+
+int bounded_wait_probe(uint32_t* status, cudaStream_t stream) {
+  bounded_wait_probe_kernel<<<1, 64, 0, stream>>>(status);
+  return check_launch("bounded_wait_probe_kernel");
+}
 
 // Takes 16-bit prefill with head dim 128 and attention blocks of 64 rows (two heads of a KV group that
 // share their key list per CTA) or a multiple of 128 rows.

@@ -42,6 +42,7 @@ int bsa_generic(const hipattn_bsa_params_t& p, cudaStream_t stream);
 int bsa_mma(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
 int bsa_decode(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
 int bsa_tcgen05(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled);
+int bounded_wait_probe(uint32_t* status, cudaStream_t stream);
 
 namespace {
 
@@ -141,6 +142,11 @@ extern "C" float hipattn_decode_score(int32_t code) {
   float f;
   memcpy(&f, &bits, 4);
   return f;
+}
+
+extern "C" int hipattn_debug_bounded_wait(uint32_t* status, void* stream) {
+  HIPATTN_REQUIRE(status != nullptr, HIPATTN_ERR_INVALID, "debug_bounded_wait: status is null");
+  return bounded_wait_probe(status, (cudaStream_t)stream);
 }
 
 extern "C" const char* hipattn_error_string(void) { return g_error; }

@@ -226,6 +226,13 @@ float hipattn_decode_score(int32_t code);
 int hipattn_decode_scores(const int32_t* codes, float* scores, int64_t count, void* stream);
 int hipattn_widen_i32(const int32_t* src, int64_t* dst, int64_t count, void* stream);
 
+/*
+ * Failure-handling probe (no counterpart in the reference, whose kernels never report errors): one
+ * CTA waits, with the bounded wait of the tcgen05 attention kernel, on a barrier nothing signals; after
+ * about 20 ms it sets HIPATTN_STATUS_TIMEOUT in *status and exits normally.  The context stays usable.
+ */
+int hipattn_debug_bounded_wait(uint32_t* status, void* stream);
+
 const char* hipattn_error_string(void);
 int hipattn_abi_version(void);
 

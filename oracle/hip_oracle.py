@@ -82,6 +82,7 @@ class OracleConfig:
     sw: int
     second_stage_k: int
     block_size_k: int = 64  # BLOCK_CHUNK seed, ``attention_extend.py:1970``
+    softcap: Optional[float] = None  # logit soft-cap of the attention kernels
 
 
 class DenseKV:
@@ -385,11 +386,14 @@ def attended_columns(indices_row: torch.Tensor, ks: int, pos_rows: torch.Tensor,
 
 
 def attention_on_mask(q: torch.Tensor, ksrc, vsrc, pos: torch.Tensor, mask: OracleMask, *, sink: int, sw: int,
-                      bsa_block_q: Optional[int] = None, return_lse: bool = False, dtype=torch.float64):
+                      bsa_block_q: Optional[int] = None, return_lse: bool = False, dtype=torch.float64,
+                      softcap: Optional[float] = None):
     """Masked softmax attention recomputed in high precision on the estimator's mask.
 
     ``sw`` is the attention window (the reference restores ``max(sw, c_0)``, ``attention_extend.py:2901``).
-    Logits are q·k (q pre-scaled), softmax rows with an empty set give 0 (``attention_extend_bsa.py:1623-1625``).
+    Logits are q·k (q pre-scaled), optionally soft-capped as tanh(x / cap) * cap
+    (``attention_extend_bsa.py:389-390, 507-508``); softmax rows with an empty set give 0
+    (``attention_extend_bsa.py:1623-1625``).
     Returns out [B, TQ, H, D] (and the base-2 log-sum-exp [B, TQ, H] when ``return_lse``).
     """
     B, TQ, H, D = q.shape
@@ -408,6 +412,8 @@ def attention_on_mask(q: torch.Tensor, ksrc, vsrc, pos: torch.Tensor, mask: Orac
                 kk = ksrc.rows(b, cols, h // G).to(dtype)
                 vv = vsrc.rows(b, cols, h // G).to(dtype)
                 s = q[b, r0:r1, h].to(dtype) @ kk.T
+                if softcap:
+                    s = torch.tanh(s / softcap) * softcap
                 s = s.masked_fill(~allow, float("-inf"))
                 m = s.max(-1, keepdim=True).values
                 m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
@@ -450,10 +456,10 @@ def hip_attention_oracle(q, k, v, pos, cfg: OracleConfig, *, paged=None, restart
     if mask is None:
         mask = estimate_mask(q, ksrc, pos, cfg, restart=restart, keep_stage_outputs=keep_stage_outputs)
     sw_attn = max(0, cfg.sw - cfg.stages[0].chunk_size) + cfg.stages[0].chunk_size
-    out = attention_on_mask(q, ksrc, vsrc, pos, mask, sink=cfg.sink, sw=sw_attn, dtype=out_dtype)
+    out = attention_on_mask(q, ksrc, vsrc, pos, mask, sink=cfg.sink, sw=sw_attn, dtype=out_dtype, softcap=cfg.softcap)
     return out, mask
 
 
 def config_from_case(c) -> OracleConfig:
     return OracleConfig(stages=[OracleStage(*s) for s in c["stages"]], sink=c["sink"], sw=c["sw"],
-                        second_stage_k=c["second_k"])
+                        second_stage_k=c["second_k"], softcap=c.get("softcap"))

@@ -46,6 +46,15 @@ def _import_reference(ref_root: str):
     torch.cuda.current_device = lambda: 0
     torch.cuda.set_device = lambda d: None
     torch.cuda.get_device_name = lambda *a: "cpu"
+    # the interpreter cannot run libdevice intrinsics: give it tanh (used by the logit soft-cap) in
+    # terms of operations it can run; on a GPU the reference calls the libdevice function
+    import triton.language as tl
+
+    def _tanh(x, _semantic=None):
+        e = tl.exp(2.0 * x)
+        return (e - 1.0) / (e + 1.0)
+
+    tl.extra.cuda.libdevice.tanh = _tanh
     import hip_attn.v1_2.attention_extend as ext
     from hip_attn.v1_2.attention_metadata import HiPAttentionArgs, ScanStage
 
@@ -91,7 +100,7 @@ def main():
                 stages=[ScanStage(stage_block_size_q=bq, stage_block_stride_q=sq, stage_chunk_size=cs,
                                   stage_k=sk, stage_stride=1) for (bq, sq, cs, sk) in c["stages"]],
                 block_sparse_block_size_q=c["stages"][-1][0], using_extend=False, need_apply_rope=False,
-                disable_flashdecode=c.get("disable_flashdecode", False), **kw)
+                disable_flashdecode=c.get("disable_flashdecode", False), logit_softcap=c.get("softcap"), **kw)
 
         t0 = time.time()
         if "page" in c:

@@ -56,7 +56,8 @@ def test_matches_reference_fixture(name):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "decode_fp16", "square_fp16", "oddsink_fp16",
-                                  "shortwin_fp16", "paged_decode_fp16", "shard_nosink_fp16", "positions_fp16"])
+                                  "shortwin_fp16", "paged_decode_fp16", "shard_nosink_fp16", "positions_fp16",
+                                  "softcap_fp16", "softcap_decode_fp16"])
 def test_matches_oracle_all_dtypes(name, dtype):
     q, k, v, pos, c, cfg, paged = case_inputs(name, dtype)
     (ref, m) = _oracle(q, k, v, pos, cfg, paged)
@@ -326,3 +327,41 @@ def test_decode_under_cuda_graph_capture():
     assert torch.equal(md_r.indices, ref_md.indices)
     assert torch.equal(out_r, ref_out) and torch.equal(out_c, ref_out)
     assert read_status(dev) == 0
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05_ws", "tcgen05", "mma"])
+def test_prefill_head_dim_128_softcap(kernel, monkeypatch):
+    """Soft-capped logits on the tensor-core prefill kernels (the capped path also applies the admission
+    rule per element)."""
+    import bench
+    from hip_attention_b200 import hip_attention_impl
+    monkeypatch.setenv("HIPATTN_PREFILL_KERNEL", kernel)
+    w = dict(bench.WORKLOADS["prefill_128k"], TQ=200, T=4096, H=8, HKV=2, keep=[2048, 1024, 512], sink=64, sw=256)
+    q, k, v = bench.make_qkv(w, "cuda")
+    args = bench.make_args(w, logit_softcap=1.5)
+    out, md = hip_attention_impl(q, k, v, args)
+    cfg = bench.oracle_config(w)
+    cfg.softcap = 1.5
+    pos = (torch.arange(200) + w["T"] - 200)[None]
+    ref, m = O.hip_attention_oracle(q.cpu(), k.cpu(), v.cpu(), pos, cfg)
+    assert torch.equal(md.indices.cpu(), m.indices)
+    _check_out(out, ref, torch.bfloat16)
+
+
+def test_bounded_wait_times_out_and_reports():
+    """A wait nothing satisfies ends by itself: the kernel returns, the status word carries the time-out
+    bit, and the device keeps working."""
+    import time
+    from hip_attention_b200 import _lib as L, read_status
+    from hip_attention_b200.operator import status_word
+    lib = L.load()
+    read_status("cuda")
+    t0 = time.perf_counter()
+    L.check(lib.hipattn_debug_bounded_wait(status_word("cuda").data_ptr(), torch.cuda.current_stream().cuda_stream), "probe")
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert read_status("cuda") & L.STATUS_TIMEOUT
+    assert dt < 2.0
+    x = torch.ones(1024, device="cuda")
+    assert float(x.sum()) == 1024.0
+    assert read_status("cuda") == 0

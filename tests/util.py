@@ -13,7 +13,7 @@ def make_args(c, pos=None, **kw):
         stages=[ScanStage(stage_block_size_q=bq, stage_block_stride_q=sq, stage_chunk_size=cs, stage_k=sk, stage_stride=1)
                 for (bq, sq, cs, sk) in c["stages"]],
         block_sparse_block_size_q=c["stages"][-1][0], using_extend=False, need_apply_rope=False,
-        disable_flashdecode=c.get("disable_flashdecode", False), **kw)
+        disable_flashdecode=c.get("disable_flashdecode", False), logit_softcap=c.get("softcap"), **kw)
 
 
 def case_inputs(name, dtype=None):
