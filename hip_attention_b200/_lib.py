@@ -9,10 +9,10 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libhipattn_sm100.so")
 
 F32, F16, BF16 = 0, 1, 2
-STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE, STATUS_TIMEOUT = 1, 2, 4
+STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE, STATUS_TIMEOUT, STATUS_CHUNK_SIZE = 1, 2, 4, 8
 MAX_CHUNKS = 16384
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
-ABI_VERSION = 3
+ABI_VERSION = 4
 SCAN_AUTO, SCAN_STRICT, SCAN_CHECK = 0, 1, 2
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
@@ -30,10 +30,10 @@ class ScanParams(C.Structure):
                 ("pos", vp), ("pos_stride_b", i64), ("pos_stride_t", i64),
                 ("k", Tokens),
                 ("left", vp), ("right", vp), ("score_max", vp),
-                ("left_out", vp), ("right_out", vp), ("score_out", vp), ("status", vp), ("key_abs", vp), ("stats", vp),
+                ("left_out", vp), ("right_out", vp), ("score_out", vp), ("status", vp), ("key_abs", vp), ("k_scaled", vp), ("stats", vp),
                 ("dtype", i32), ("D", i32), ("B", i32), ("TQ", i32), ("H", i32), ("HKV", i32), ("T", i32),
                 ("block_size_q", i32), ("stride_q", i32), ("n_chunks", i32), ("block_chunk", i32),
-                ("scan_window", i32), ("q_scale", f32), ("k_scale", f32), ("mode", i32)]
+                ("scan_window", i32), ("q_scale", f32), ("k_scale", f32), ("mode", i32), ("chunk_size", i32)]
 
 
 class BsaParams(C.Structure):
@@ -54,6 +54,7 @@ class BsaParams(C.Structure):
 SYMBOLS = {
     "hipattn_scan_stage": (i32, [C.POINTER(ScanParams), vp]),
     "hipattn_key_abs_sum": (i32, [C.POINTER(Tokens), i32, i32, i32, i32, i32, f32, vp, vp, vp]),
+    "hipattn_scan_prepare_keys": (i32, [C.POINTER(Tokens), i32, i32, i32, i32, i32, f32, vp, vp, vp, vp]),
     "hipattn_init_chunks": (i32, [vp, vp, vp, i64, i32, i32, i32, i32, i32, vp]),
     "hipattn_select_stage": (i32, [vp, vp, i64, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     "hipattn_finalize_indices": (i32, [vp, vp, i64, i64, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]),

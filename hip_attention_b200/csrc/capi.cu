@@ -150,4 +150,4 @@ extern "C" int hipattn_debug_bounded_wait(uint32_t* status, void* stream) {
 }
 
 extern "C" const char* hipattn_error_string(void) { return g_error; }
-extern "C" int hipattn_abi_version(void) { return 3; }
+extern "C" int hipattn_abi_version(void) { return 4; }

@@ -117,6 +117,17 @@ __device__ __forceinline__ const char* token_row(const hipattn_tokens_t& tk, int
   return (const char*)tk.cache + off * elem_bytes;
 }
 
+// two floats rounded to the 16-bit element type and packed, low half first
+template <int DT>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (DT == HIPATTN_BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));

@@ -75,6 +75,45 @@ __device__ __forceinline__ int block_min_position(const hipattn_scan_params_t& p
   return (int)(m > 0x7fffffffLL ? 0x7fffffffLL : m);
 }
 
+// ---- pieces of the tensor-core scan kernels ----
+
+// Bound on |tensor-core dot - sequential fp32 dot| / (max|q'| * sum_d |k'_d|) used as the radius inside
+// which a rounded score is not trusted (empirical; the check mode measures the observed fraction).
+constexpr float kEps = 1.0f / (1 << 21);
+
+// statistics words (mode 2)
+enum { ST_KEYS = 0, ST_FALLBACK = 1, ST_WRONG = 2, ST_RATIO_BITS = 3 };
+
+// element-wise product of two packed 16-bit pairs, rounded to nearest even (one rounding of the exact product)
+template <int DT>
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+  if (DT == HIPATTN_BF16) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+template <int DT>
+__device__ __forceinline__ float lo_f32(uint32_t w) {
+  if (DT == HIPATTN_BF16) return __uint_as_float(w << 16);
+  return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
+}
+template <int DT>
+__device__ __forceinline__ float hi_f32(uint32_t w) {
+  if (DT == HIPATTN_BF16) return __uint_as_float(w & 0xffff0000u);
+  return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
+}
+template <int DT>
+__device__ __forceinline__ uint32_t pack_scalar2(float x) {
+  if (DT == HIPATTN_BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(x, x);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(x, x);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 // Number of halving rounds of the lane's chunk: while (m >= 1) m /= 2 with m the largest chunk of the
 // lane's group of block_chunk chunks (attention_extend.py:602-606, 736-737).  `wbase` is the first
 // chunk of the warp; the warp's 32 chunks lie in one group when block_chunk is a multiple of 32.

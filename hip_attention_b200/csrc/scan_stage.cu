@@ -283,8 +283,10 @@ int dispatch_dim(const hipattn_scan_params_t& p, cudaStream_t stream) {
 }  // namespace
 
 int scan_stage_mma(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
-int key_abs_sum(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* out,
-                uint32_t* status, cudaStream_t stream);
+int scan_stage_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
+int scan_dense_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
+int scan_prepare_keys(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* key_abs,
+                      void* k_scaled, uint32_t* status, cudaStream_t stream);
 
 }  // namespace hipattn
 
@@ -311,6 +313,10 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
   cudaStream_t s = (cudaStream_t)stream;
   HIPATTN_REQUIRE(p->mode >= HIPATTN_SCAN_AUTO && p->mode <= HIPATTN_SCAN_CHECK, HIPATTN_ERR_INVALID, "scan stage: unknown mode %d", p->mode);
   bool handled = false;
+  rc = scan_dense_tcgen05(*p, s, &handled);
+  if (handled) return rc;
+  rc = scan_stage_tcgen05(*p, s, &handled);
+  if (handled) return rc;
   rc = scan_stage_mma(*p, s, &handled);
   if (handled) return rc;
   switch (p->dtype) {
@@ -328,5 +334,16 @@ extern "C" int hipattn_key_abs_sum(const hipattn_tokens_t* k, int32_t dtype, int
   HIPATTN_REQUIRE(B > 0 && T > 0 && HKV > 0, HIPATTN_ERR_INVALID, "key_abs_sum: bad shape");
   int rc = validate_tokens(*k, dtype == HIPATTN_F32 ? 4 : 2, D, "k");
   if (rc) return rc;
-  return key_abs_sum(*k, dtype, D, B, T, HKV, k_scale, out, status, (cudaStream_t)stream);
+  return scan_prepare_keys(*k, dtype, D, B, T, HKV, k_scale, out, nullptr, status, (cudaStream_t)stream);
+}
+
+extern "C" int hipattn_scan_prepare_keys(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
+                                         float k_scale, float* key_abs, void* k_scaled, uint32_t* status, void* stream) {
+  using namespace hipattn;
+  HIPATTN_REQUIRE(k && status && (key_abs || k_scaled), HIPATTN_ERR_INVALID, "scan_prepare_keys: null pointer");
+  HIPATTN_REQUIRE(B > 0 && T > 0 && HKV > 0, HIPATTN_ERR_INVALID, "scan_prepare_keys: bad shape");
+  HIPATTN_REQUIRE(((uintptr_t)k_scaled % 16) == 0, HIPATTN_ERR_INVALID, "scan_prepare_keys: k_scaled must be 16-byte aligned");
+  int rc = validate_tokens(*k, dtype == HIPATTN_F32 ? 4 : 2, D, "k");
+  if (rc) return rc;
+  return scan_prepare_keys(*k, dtype, D, B, T, HKV, k_scale, key_abs, k_scaled, status, (cudaStream_t)stream);
 }

@@ -24,41 +24,8 @@
 namespace hipattn {
 namespace {
 
-constexpr float kEps = 1.0f / (1 << 21);
 constexpr int kPadBytes = 16;
 
-// element-wise product of two packed 16-bit pairs, rounded to nearest even (one rounding of the exact product)
-template <int DT>
-__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
-  if (DT == HIPATTN_BF16) {
-    __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
-    return *reinterpret_cast<uint32_t*>(&r);
-  }
-  __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-template <int DT>
-__device__ __forceinline__ float lo_f32(uint32_t w) {
-  if (DT == HIPATTN_BF16) return __uint_as_float(w << 16);
-  return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
-}
-template <int DT>
-__device__ __forceinline__ float hi_f32(uint32_t w) {
-  if (DT == HIPATTN_BF16) return __uint_as_float(w & 0xffff0000u);
-  return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
-}
-template <int DT>
-__device__ __forceinline__ uint32_t pack_scalar2(float x) {
-  if (DT == HIPATTN_BF16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(x, x);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-  __half2 v = __floats2half2_rn(x, x);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// statistics words (mode 2)
-enum { ST_KEYS = 0, ST_FALLBACK = 1, ST_WRONG = 2, ST_RATIO_BITS = 3 };
 
 template <int DT, int D, int MT>
 __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int NW, int check) {
@@ -227,8 +194,8 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
     // ---- approximate scores on tensor cores ----
     float xl = -INFINITY, xr = -INFINITY, sl_abs = 0.f, sr_abs = 0.f;
     if (have_abs && act) {  // precomputed key magnitudes (one per key row of the call)
-      sl_abs = p.key_abs[((int64_t)b * p.T + tl) * p.HKV + hkv];
-      sr_abs = p.key_abs[((int64_t)b * p.T + tr) * p.HKV + hkv];
+      sl_abs = p.key_abs[((int64_t)b * p.HKV + hkv) * p.T + tl];
+      sr_abs = p.key_abs[((int64_t)b * p.HKV + hkv) * p.T + tr];
     }
     for (int mg = 0; mg < n_mgroups; ++mg) {
       float acc[MT][8][4];
@@ -385,47 +352,7 @@ int dispatch_rows(const hipattn_scan_params_t& p, cudaStream_t stream) {
   return launch<DT, D, 4>(p, stream);
 }
 
-template <int DT>
-__global__ void key_abs_sum_kernel(const hipattn_tokens_t k, int D, int B, int T, int HKV, float k_scale, float* out,
-                                   uint32_t* status) {
-  // one row per group of (row bytes / 16) lanes; a 256-byte row takes 16 lanes
-  const int pieces = D * Elem<DT>::bytes / 16;
-  const int rows_per_block = blockDim.x / pieces;
-  const int sub = threadIdx.x / pieces, piece = threadIdx.x % pieces;
-  const int64_t total = (int64_t)B * T * HKV;
-  const uint32_t kscale2 = pack_scalar2<DT>(k_scale);
-  for (int64_t r = (int64_t)blockIdx.x * rows_per_block + sub; r < total; r += (int64_t)gridDim.x * rows_per_block) {
-    const int hkv = (int)(r % HKV);
-    const int64_t bt = r / HKV;
-    const int t = (int)(bt % T), b = (int)(bt / T);
-    const char* row = token_row(k, b, t, hkv, Elem<DT>::bytes, status);
-    const uint4 w = *reinterpret_cast<const uint4*>(row + piece * 16);
-    const uint32_t v[4] = {w.x, w.y, w.z, w.w};
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t m = mul2<DT>(v[i], kscale2) & 0x7fff7fffu;
-      s += lo_f32<DT>(m) + hi_f32<DT>(m);
-    }
-    for (int o = pieces >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (piece == 0) out[r] = s;
-  }
-}
-
 }  // namespace
-
-int key_abs_sum(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* out,
-                uint32_t* status, cudaStream_t stream) {
-  HIPATTN_REQUIRE(dtype == HIPATTN_BF16 || dtype == HIPATTN_F16, HIPATTN_ERR_UNSUPPORTED, "key_abs_sum: 16-bit element types only");
-  HIPATTN_REQUIRE(D == 64 || D == 128, HIPATTN_ERR_UNSUPPORTED, "key_abs_sum: head dimension %d is not built (64, 128)", D);
-  const int64_t total = (int64_t)B * T * HKV;
-  const int rows_per_block = 256 / (D * 2 / 16);
-  int64_t grid = (total + rows_per_block - 1) / rows_per_block;
-  if (grid > 148 * 32) grid = 148 * 32;
-  if (dtype == HIPATTN_BF16) key_abs_sum_kernel<HIPATTN_BF16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, out, status);
-  else key_abs_sum_kernel<HIPATTN_F16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, out, status);
-  return check_launch("key_abs_sum_kernel");
-}
 
 // Takes 16-bit prefill shapes (more than one pooled row, a multiple of 16 of them, head dim 64 or
 // 128); anything else stays on the strict kernel.

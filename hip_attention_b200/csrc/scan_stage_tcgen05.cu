@@ -1,0 +1,400 @@
+// Scan stage of the mask estimator for 16-bit prefill on the tcgen05 tensor cores.
+//
+// Same contract as the strict kernel (scan_stage.cu): the score of a candidate key is
+// max over pooled rows of round_to_dtype(dot), the dot product being the sequential fp32 accumulation
+// over the head dimension.  As in the mma.sync kernel (scan_stage_mma.cu) the dot products are first
+// computed approximately on the tensor cores and a key whose rounded score could change within the
+// error radius eps = kEps * max|q'| * sum_d |k'_d| is re-scored by the strict definition, so decisions
+// and stored scores are those of the strict kernel.
+//
+// Layout of one round: a CTA of 128 threads owns 64 chunks; thread t owns ONE candidate key
+// (chunk t / 2, side t % 2).  The 128 candidate rows are gathered with 16-byte cp.async straight into
+// the 128-byte-swizzled K-major operand layout (A, M = 128); the pooled queries sit in shared memory
+// as the B operand (N = 16 / 32 / 64 rows).  D = K Q^T lands in TMEM with lane = key and
+// column = pooled row, so thread t reads its own lane with one tcgen05.ld and takes the row maximum
+// in registers: no shuffles, no ldmatrix, and one MMA issue per 16 head-dim elements for the whole CTA.
+//
+// The keys are read from a per-call copy that is already multiplied by the key scale and rounded
+// (hipattn_scan_prepare_keys), dense and head-major [B, HKV, T, D] whatever the layout of the cache, so the
+// gather needs no page-table lookups and no arithmetic between global and shared memory.
+//
+// Every mbarrier wait is bounded; when one runs out the CTA raises HIPATTN_STATUS_TIMEOUT and leaves
+// through the normal exit, which frees its TMEM columns.
+#include <cstdlib>
+#include <cstring>
+
+#include "scan_common.cuh"
+#include "tcgen05_common.cuh"
+
+namespace hipattn {
+namespace {
+
+template <int DT, int D, int NR>
+__global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int check) {
+  constexpr int ROWB = D * 2;                 // bytes per key / query row
+  constexpr int PIECES = ROWB / 16;
+  constexpr int KB = D / 64;                  // 128-byte K-blocks per row
+  constexpr int K_BLOCK_BYTES = 128 * 128;    // one K-block of the key tile: 128 rows x 128 B
+  constexpr int Q_BLOCK_BYTES = NR * 128;
+  constexpr uint32_t TMEM_COLS = NR < 32 ? 32 : NR;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  unsigned char* sK = smem;                                  // [KB][128 keys][128 B], swizzled
+  unsigned char* sQ = sK + KB * K_BLOCK_BYTES;               // [KB][NR rows][128 B], swizzled
+  float* kf32 = reinterpret_cast<float*>(sQ + KB * Q_BLOCK_BYTES);   // [4 warps][D]: key of a strict re-score
+  __shared__ __align__(8) unsigned long long s_mbar;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+  __shared__ int s_pmin;
+  __shared__ float s_qmax;
+  __shared__ int s_g[2][4];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int Gq = p.H / p.HKV;
+  const int BDST = cdiv(p.TQ, p.block_size_q);
+  int64_t bid = blockIdx.x;
+  const int cblk = (int)(bid % nblk); bid /= nblk;
+  const int g = (int)(bid % Gq); bid /= Gq;
+  const int d = (int)(bid % BDST); bid /= BDST;
+  const int hkv = (int)(bid % p.HKV); bid /= p.HKV;
+  const int b = (int)bid;
+  const int h = hkv * Gq + g;
+
+  const int R = p.block_size_q / p.stride_q;
+  const int t0 = d * p.block_size_q;
+  int Rv = 0;
+  if (t0 < p.TQ) Rv = min(R, (p.TQ - t0 + p.stride_q - 1) / p.stride_q);
+  const uint32_t mbar = smem_u32(&s_mbar);
+
+  // ---- set-up: barrier, TMEM, pooled queries as the B operand ----
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    s_abort = 0;
+    s_qmax = 0.f;
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  float qmax_local = 0.f;
+  for (int i = tid; i < NR * PIECES; i += 128) {
+    const int r = i / PIECES, pc = i % PIECES;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    if (r < Rv) pooled_query_piece<DT>(p, b, h, t0 + r * p.stride_q, pc, v);
+    uint4 w;
+    w.x = pack2<DT>(v[0], v[1]); w.y = pack2<DT>(v[2], v[3]); w.z = pack2<DT>(v[4], v[5]); w.w = pack2<DT>(v[6], v[7]);
+    *reinterpret_cast<uint4*>(sQ + (pc >> 3) * Q_BLOCK_BYTES + sw128(r, pc & 7)) = w;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qmax_local = fmaxf(qmax_local, fabsf(v[e]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) qmax_local = fmaxf(qmax_local, __shfl_xor_sync(0xffffffffu, qmax_local, o));
+  if (lane == 0) atomicMax(reinterpret_cast<int*>(&s_qmax), __float_as_int(qmax_local));  // non-negative floats order as ints
+  if (warp == 0) {
+    const int m = block_min_position(p, b, t0, Rv, lane);
+    if (lane == 0) s_pmin = m;
+  }
+  fence_async_smem();
+  __syncthreads();
+
+  const int pt = max(s_pmin - p.scan_window, 0);
+  const float eps_q = kEps * s_qmax;
+  const int n = p.n_chunks;
+  const int64_t row = (int64_t)b * BDST + d;
+  const char* kbase = reinterpret_cast<const char*>(p.k_scaled);
+  const uint32_t sK_u32 = smem_u32(sK), sQ_u32 = smem_u32(sQ);
+  const uint32_t idesc = make_idesc(DT == HIPATTN_BF16 ? 1 : 0, 128, NR, 0);
+  const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);
+  float* wkf = kf32 + warp * D;
+  const int side = tid & 1;
+  unsigned long long st_keys = 0, st_fb = 0, st_wrong = 0;
+  float st_ratio = 0.f;
+  uint32_t phase = 0;
+
+  // strict dot products of the key staged in row `srow`, by the whole warp (one pooled row per lane);
+  // returns the largest one before rounding (rounding is monotonic, so it commutes with the maximum)
+  auto strict_score = [&](int srow) -> float {
+    __syncwarp();
+    for (int e2 = lane; e2 < D / 2; e2 += 32) {
+      const int pc = e2 >> 2;
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(sK + (pc >> 3) * K_BLOCK_BYTES + sw128(srow, pc & 7) + (e2 & 3) * 4);
+      wkf[2 * e2] = lo_f32<DT>(w);
+      wkf[2 * e2 + 1] = hi_f32<DT>(w);
+    }
+    __syncwarp();
+    float best = -INFINITY;
+    for (int r0 = 0; r0 < Rv; r0 += 32) {
+      const int r = r0 + lane;
+      if (r < Rv) {
+        float acc = 0.f;
+#pragma unroll 4
+        for (int pc = 0; pc < PIECES; ++pc) {
+          const uint4 qw = *reinterpret_cast<const uint4*>(sQ + (pc >> 3) * Q_BLOCK_BYTES + sw128(r, pc & 7));
+          const float4 k0 = *reinterpret_cast<const float4*>(wkf + pc * 8);
+          const float4 k1 = *reinterpret_cast<const float4*>(wkf + pc * 8 + 4);
+          acc = fmaf(lo_f32<DT>(qw.x), k0.x, acc);
+          acc = fmaf(hi_f32<DT>(qw.x), k0.y, acc);
+          acc = fmaf(lo_f32<DT>(qw.y), k0.z, acc);
+          acc = fmaf(hi_f32<DT>(qw.y), k0.w, acc);
+          acc = fmaf(lo_f32<DT>(qw.z), k1.x, acc);
+          acc = fmaf(hi_f32<DT>(qw.z), k1.y, acc);
+          acc = fmaf(lo_f32<DT>(qw.w), k1.z, acc);
+          acc = fmaf(hi_f32<DT>(qw.w), k1.w, acc);
+        }
+        best = fmaxf(best, acc);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+    return best;
+  };
+
+  bool aborted = Rv == 0;
+  int cbi = 0;
+  for (int cb = cblk; cb < nblk_total && !aborted; cb += nblk, ++cbi) {
+    const int c = cb * 64 + (tid >> 1);
+    const bool in_range = c < n;
+    int left = 0, right = 0;
+    if (in_range) {
+      left = p.left[row * n + c];
+      right = p.right[row * n + c];
+    }
+    // halving rounds: fixed by the largest chunk of the reference group of block_chunk chunks that
+    // holds this thread's chunk; a warp covers 16 chunks, the CTA 64
+    {
+      int m = in_range ? right - left : 0;
+      if (p.block_chunk > 64) {
+        const int gbase = (cb * 64 / p.block_chunk) * p.block_chunk;
+        for (int i = tid; i < p.block_chunk; i += 128) {
+          const int cc = gbase + i;
+          if (cc < n) m = max(m, p.right[row * n + cc] - p.left[row * n + cc]);
+        }
+      }
+      m = __reduce_max_sync(0xffffffffu, m);
+      if (lane == 0) s_g[cbi & 1][warp] = m;
+    }
+    __syncthreads();
+    const int cta_max = max(max(s_g[cbi & 1][0], s_g[cbi & 1][1]), max(s_g[cbi & 1][2], s_g[cbi & 1][3]));
+    const int gmax = p.block_chunk >= 64 ? cta_max
+                     : (p.block_chunk == 32 ? max(s_g[cbi & 1][warp], s_g[cbi & 1][warp ^ 1]) : s_g[cbi & 1][warp]);
+    const int my_rounds = gmax >= 1 ? 32 - __clz(gmax) : 0;
+    const int cta_rounds = cta_max >= 1 ? 32 - __clz(cta_max) : 0;
+    float score = HIPATTN_SCORE_INIT;
+
+    for (int it = 0; it < cta_rounds; ++it) {
+      const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
+      tc_fence_before();
+      const int any = __syncthreads_or((act ? 1 : 0) | (*(volatile int*)&s_abort ? 2 : 0));
+      if (any & 2) { aborted = true; break; }
+      if (!(any & 1)) break;
+      const int mid = (left + right) >> 1;
+      int tk = side ? ((mid + right) >> 1) : ((left + mid) >> 1);
+      int idx = -1;
+      if (act) {
+        if (tk < 0 || tk >= p.T) {
+          atomicOr(p.status, HIPATTN_STATUS_TOKEN_RANGE);
+          tk = min(max(tk, 0), p.T - 1);
+        }
+        idx = (b * p.HKV + hkv) * p.T + tk;
+      }
+      // ---- gather this warp's 32 rows: 8 lanes per row, 128 contiguous bytes per row and instruction ----
+#pragma unroll
+      for (int r0 = 0; r0 < 32; r0 += 4) {
+        const int j = r0 + (lane >> 3);
+        const int src = __shfl_sync(0xffffffffu, idx, j);
+        if (src >= 0) {
+          const int srow = warp * 32 + j;
+          const char* gp = kbase + (int64_t)src * ROWB + (lane & 7) * 16;
+          unsigned char* sp = sK + sw128(srow, lane & 7);
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb) cp_async16(sp + kb * K_BLOCK_BYTES, gp + kb * 128);
+        }
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+      fence_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t da = make_desc(sK_u32 + (k >> 2) * K_BLOCK_BYTES + (k & 3) * 32, 16, 1024);
+          const uint64_t db = make_desc(sQ_u32 + (k >> 2) * Q_BLOCK_BYTES + (k & 3) * 32, 16, 1024);
+          umma(tmem, da, db, idesc, k > 0 ? 1u : 0u);
+        }
+        umma_commit(mbar);
+      }
+      __syncwarp();
+      bool ok = mbar_wait(mbar, phase, &s_abort, p.status);
+      phase ^= 1u;
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+      float x = -INFINITY;
+      if (ok) {
+        float v[NR];
+        if (NR == 16) {
+          tmem_ld16(my_tmem, v);
+        } else {
+#pragma unroll
+          for (int c0 = 0; c0 < NR; c0 += 32) tmem_ld32(my_tmem + c0, v + c0);
+        }
+#pragma unroll
+        for (int j = 0; j < NR; ++j)
+          if (j < Rv) x = fmaxf(x, v[j]);
+      }
+      const float s_abs = act ? p.key_abs[idx] : 0.f;
+      const float e_ = eps_q * s_abs * 1.01f;
+      float sc = Elem<DT>::round(x);
+      const bool sure = Elem<DT>::round(x - e_) == Elem<DT>::round(x + e_);
+      unsigned need = __ballot_sync(0xffffffffu, act && ok && (!sure || check));
+      while (need) {
+        const int owner = __ffs(need) - 1;
+        need &= need - 1;
+        const float rawv = strict_score(warp * 32 + owner);
+        const float ex = Elem<DT>::round(rawv);
+        if (lane == owner) {
+          if (check) {
+            if (sure && sc != ex) ++st_wrong;
+            if (e_ > 0.f) st_ratio = fmaxf(st_ratio, fabsf(x - rawv) / e_);
+          }
+          if (!sure) ++st_fb;
+          sc = ex;
+        }
+      }
+      const float other = __shfl_xor_sync(0xffffffffu, sc, 1);   // the other candidate of the same chunk
+      if (act) {
+        st_keys += 1;
+        const float sl = side ? other : sc, sr = side ? sc : other;
+        const bool win = sl > sr;
+        if (win) right = mid; else left = mid;
+        score = fmaxf(score, win ? sl : sr);
+      }
+    }
+
+    if (in_range && side == 0 && !aborted) {
+      if (score > HIPATTN_SCORE_INIT) atomicMax(p.score_max + row * n + c, encode_score(score));
+      const int64_t o = (row * p.H + h) * n + c;
+      if (p.left_out) p.left_out[o] = left;
+      if (p.right_out) p.right_out[o] = right;
+      if (p.score_out) p.score_out[o] = score;
+    }
+  }
+
+  if (p.stats) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      st_keys += __shfl_xor_sync(0xffffffffu, st_keys, o);
+      st_fb += __shfl_xor_sync(0xffffffffu, st_fb, o);
+      st_wrong += __shfl_xor_sync(0xffffffffu, st_wrong, o);
+    }
+    unsigned long long* st = reinterpret_cast<unsigned long long*>(p.stats);
+    if (lane == 0) {
+      atomicAdd(st + ST_KEYS, st_keys);
+      atomicAdd(st + ST_FALLBACK, st_fb);
+      atomicAdd(st + ST_WRONG, st_wrong);
+    }
+    atomicMax(reinterpret_cast<unsigned int*>(p.stats + ST_RATIO_BITS), __float_as_uint(st_ratio));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+template <int DT, int D, int NR>
+int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)(D / 64) * (128 * 128 + NR * 128) + 4 * D * sizeof(float);
+  const int BDST = cdiv(p.TQ, p.block_size_q);
+  const int nblk_total = cdiv(p.n_chunks, 64);
+  const int64_t units = (int64_t)p.B * p.H * BDST;
+  const int nblk = scan_ctas_per_unit(units, nblk_total);
+  const int64_t grid = units * nblk;
+  HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
+  auto kern = scan_stage_tcgen05_kernel<DT, D, NR>;
+  HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)grid, 128, smem, stream>>>(p, nblk, nblk_total, p.mode == HIPATTN_SCAN_CHECK ? 1 : 0);
+  return check_launch("scan_stage_tcgen05_kernel");
+}
+
+template <int DT, int D>
+int dispatch_rows(const hipattn_scan_params_t& p, cudaStream_t stream) {
+  const int R = p.block_size_q / p.stride_q;
+  if (R <= 16) return launch<DT, D, 16>(p, stream);
+  if (R <= 32) return launch<DT, D, 32>(p, stream);
+  return launch<DT, D, 64>(p, stream);
+}
+
+// Scaled copy of the keys and their absolute sums: 16 / 8 lanes per row of 256 / 128 bytes.
+template <int DT>
+__global__ void scan_prepare_keys_kernel(const hipattn_tokens_t k, int D, int B, int T, int HKV, float k_scale, float* key_abs,
+                                         unsigned char* k_scaled, uint32_t* status) {
+  const int pieces = D * 2 / 16;
+  const int rows_per_block = blockDim.x / pieces;
+  const int sub = threadIdx.x / pieces, piece = threadIdx.x % pieces;
+  const int64_t total = (int64_t)B * T * HKV;
+  const uint32_t kscale2 = pack_scalar2<DT>(k_scale);
+  for (int64_t r = (int64_t)blockIdx.x * rows_per_block + sub; r < total; r += (int64_t)gridDim.x * rows_per_block) {
+    const int hkv = (int)(r % HKV);
+    const int64_t bt = r / HKV;
+    const int t = (int)(bt % T), b = (int)(bt / T);
+    const char* src = token_row(k, b, t, hkv, 2, status);
+    const uint4 w = *reinterpret_cast<const uint4*>(src + piece * 16);
+    uint32_t v[4] = {w.x, w.y, w.z, w.w};
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = mul2<DT>(v[i], kscale2);
+      const uint32_t m = v[i] & 0x7fff7fffu;
+      s += lo_f32<DT>(m) + hi_f32<DT>(m);
+    }
+    const int64_t ro = ((int64_t)b * HKV + hkv) * T + t;     // head-major: the tokens of a KV head are contiguous
+    if (k_scaled) *reinterpret_cast<uint4*>(k_scaled + ro * (int64_t)(D * 2) + piece * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+    for (int o = pieces >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (piece == 0 && key_abs) key_abs[ro] = s;
+  }
+}
+
+}  // namespace
+
+int scan_prepare_keys(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* key_abs,
+                      void* k_scaled, uint32_t* status, cudaStream_t stream) {
+  HIPATTN_REQUIRE(dtype == HIPATTN_BF16 || dtype == HIPATTN_F16, HIPATTN_ERR_UNSUPPORTED, "scan_prepare_keys: 16-bit element types only");
+  HIPATTN_REQUIRE(D == 64 || D == 128, HIPATTN_ERR_UNSUPPORTED, "scan_prepare_keys: head dimension %d is not built (64, 128)", D);
+  const int64_t total = (int64_t)B * T * HKV;
+  const int rows_per_block = 256 / (D * 2 / 16);
+  int64_t grid = (total + rows_per_block - 1) / rows_per_block;
+  if (grid > 148 * 32) grid = 148 * 32;
+  if (dtype == HIPATTN_BF16)
+    scan_prepare_keys_kernel<HIPATTN_BF16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, key_abs, (unsigned char*)k_scaled, status);
+  else
+    scan_prepare_keys_kernel<HIPATTN_F16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, key_abs, (unsigned char*)k_scaled, status);
+  return check_launch("scan_prepare_keys_kernel");
+}
+
+// Takes 16-bit prefill shapes (2 to 64 pooled rows in multiples of 16, head dim 64 or 128) when the
+// caller supplies the prepared keys; anything else is left to the other scan kernels.
+int scan_stage_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled) {
+  *handled = false;
+  const int R = p.block_size_q / p.stride_q;
+  const int rows = min(R, cdiv(p.TQ, p.stride_q));
+  if (p.mode == HIPATTN_SCAN_STRICT || p.dtype == HIPATTN_F32 || rows <= 1 || (R % 16) != 0 || R > 64 || (p.D != 64 && p.D != 128)) return HIPATTN_OK;
+  if (p.key_abs == nullptr || p.k_scaled == nullptr) return HIPATTN_OK;
+  if ((int64_t)p.B * p.T * p.HKV >= 0x7fffffffLL) return HIPATTN_OK;
+  const char* v = getenv("HIPATTN_SCAN_KERNEL");
+  if (v && strcmp(v, "mma") == 0) return HIPATTN_OK;
+  *handled = true;
+  if (p.dtype == HIPATTN_BF16) return p.D == 128 ? dispatch_rows<HIPATTN_BF16, 128>(p, stream) : dispatch_rows<HIPATTN_BF16, 64>(p, stream);
+  return p.D == 128 ? dispatch_rows<HIPATTN_F16, 128>(p, stream) : dispatch_rows<HIPATTN_F16, 64>(p, stream);
+}
+
+}  // namespace hipattn

@@ -218,15 +218,17 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
     if n > L.MAX_CHUNKS:
         raise NotImplementedError(f"{n} chunks per query block exceed the on-chip selection limit of {L.MAX_CHUNKS}")
 
-    # key magnitudes for the error radius of the tensor-core scan (16-bit prefill only), once per call
-    key_abs = None
+    # scaled keys and their magnitudes (error radius) for the tensor-core scan (16-bit prefill only), once per call
+    key_abs = k_scaled = None
     R_min = min(bq // s_.stage_block_stride_q for s_ in stages)
     if (q.dtype != torch.float32 and D in (64, 128) and min(TQ, bq) > 1 and _scan_mode() != L.SCAN_STRICT
             and all((bq // s_.stage_block_stride_q) % 16 == 0 for s_ in stages) and R_min >= 16 and n > 0):
         if timer: timer.mark("start")
-        key_abs = torch.empty((B, T, HKV), dtype=torch.float32, device=dev)
-        L.check(lib.hipattn_key_abs_sum(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, _ptr(key_abs),
-                                        status.data_ptr(), st), "key_abs_sum")
+        key_abs = torch.empty((B, HKV, T), dtype=torch.float32, device=dev)
+        if B * T * HKV < 2 ** 31 - 1:
+            k_scaled = torch.empty((B, HKV, T, D), dtype=q.dtype, device=dev)
+        L.check(lib.hipattn_scan_prepare_keys(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, _ptr(key_abs),
+                                              _ptr(k_scaled), status.data_ptr(), st), "scan_prepare_keys")
         if timer: timer.mark("prep")
 
     block_chunk = args.block_size_k
@@ -255,11 +257,13 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         sp.left_out, sp.right_out, sp.score_out = _ptr(left_out), _ptr(right_out), _ptr(score_out)
         sp.status = status.data_ptr()
         sp.key_abs = _ptr(key_abs)
+        sp.k_scaled = _ptr(k_scaled)
         sp.dtype, sp.D, sp.B, sp.TQ, sp.H, sp.HKV, sp.T = _DT[q.dtype], D, B, TQ, H, HKV, T
         sp.block_size_q, sp.stride_q = bq, s_i.stage_block_stride_q
         sp.n_chunks, sp.block_chunk, sp.scan_window = n, block_chunk, scan_window
         sp.q_scale, sp.k_scale = q_scale, k_scale
         sp.mode = _scan_mode()
+        sp.chunk_size = s_i.stage_chunk_size
         if debug is not None and "scan_stats" in debug:
             sp.stats = debug["scan_stats"].data_ptr()
         if timer: timer.mark("start")

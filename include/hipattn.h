@@ -32,6 +32,7 @@ extern "C" {
 /* Bits of the device status word written by the kernels (0 = clean). */
 #define HIPATTN_STATUS_PAGE_RANGE 1u  /* a block-table entry pointed outside the page pool; clamped */
 #define HIPATTN_STATUS_TOKEN_RANGE 2u /* a token index fell outside [0, T); clamped                 */
+#define HIPATTN_STATUS_CHUNK_SIZE 8u  /* a chunk was longer than the chunk size the scan was told; its tail was ignored */
 #define HIPATTN_STATUS_TIMEOUT 4u     /* a bounded on-chip wait ran out; the launch's output is invalid */
 
 #define HIPATTN_SCORE_INIT (-32000.0f) /* attention_extend.py:2040-2045 */
@@ -88,8 +89,10 @@ typedef struct hipattn_scan_params {
   int32_t* right_out;
   float* score_out;
   uint32_t* status;          /* one word, OR-ed with HIPATTN_STATUS_* */
-  const float* key_abs;      /* optional [B, T, HKV]: sum_d |round(k * k_scale)| per key row (hipattn_key_abs_sum);
+  const float* key_abs;      /* optional [B, HKV, T]: sum_d |round(k * k_scale)| per key row (hipattn_key_abs_sum);
                                 lets the tensor-core path skip computing it per round */
+  const void* k_scaled;      /* optional dense [B, HKV, T, D] copy of the keys, element type, already multiplied by k_scale
+                                and rounded (hipattn_scan_prepare_keys); with key_abs it enables the tcgen05 scan */
   uint64_t* stats;           /* optional, 4 words: keys scored, keys re-scored strictly, wrong shortcuts
                                 (check mode), largest deviation / allowed radius as float bits (check mode) */
   int32_t dtype, D, B, TQ, H, HKV, T;
@@ -100,17 +103,29 @@ typedef struct hipattn_scan_params {
   int32_t scan_window;       /* max(0, sliding_window - first chunk size), attention_extend.py:1976-1978 */
   float q_scale, k_scale;    /* already rounded to the element type, attention_extend.py:924-940 */
   int32_t mode;              /* HIPATTN_SCAN_AUTO / _STRICT / _CHECK */
+  int32_t chunk_size;        /* optional: upper bound of right - left (the stage's chunk size), 0 = unknown.  A small
+                                power of two lets the scan score whole chunks once for all heads of a KV head and
+                                replay the search on the scores (same results, fewer key rows gathered) */
 } hipattn_scan_params_t;
 
 int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);
 
 /*
- * Per key row, sum over the head dimension of |round_to_dtype(k * k_scale)| as fp32, out [B, T, HKV].
+ * Per key row, sum over the head dimension of |round_to_dtype(k * k_scale)| as fp32, out [B, HKV, T].
  * No counterpart in the reference: it is the magnitude from which the tensor-core scan derives the
  * error radius of its approximate dot products, computed once per call instead of once per round.
  */
 int hipattn_key_abs_sum(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
                         float k_scale, float* out, uint32_t* status, void* stream);
+
+/*
+ * As hipattn_key_abs_sum, and also writes the scaled keys round_to_dtype(k * k_scale) as a dense
+ * head-major [B, HKV, T, D] array of the element type (either output may be null).  The scan then gathers from
+ * this copy: no page-table lookups and no arithmetic between global and shared memory.  No counterpart
+ * in the reference, which rescales every gathered key inside the scan (attention_extend.py:924-940).
+ */
+int hipattn_scan_prepare_keys(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
+                              float k_scale, float* key_abs, void* k_scaled, uint32_t* status, void* stream);
 
 /*
  * Initial chunk list of stage 0 (attention_extend.py:2027-2046): left[c] = sink + c * chunk,

@@ -245,12 +245,15 @@ def _scan_check_run(dtype, TQ=512, T=16384):
     return stats.cpu(), md, (q, k, v, w)
 
 
+@pytest.mark.parametrize("scan_kernel", ["auto", "dense", "rounds", "mma"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_scan_tensor_core_path_is_exact(dtype, monkeypatch):
-    """The tensor-core scan takes a shortcut only where rounding is certain.  In check mode every key
-    is also scored by the strict definition: no shortcut may be wrong, and the observed deviation must
-    stay well inside the assumed error radius.  Strict and automatic modes give identical masks."""
+def test_scan_tensor_core_path_is_exact(dtype, scan_kernel, monkeypatch):
+    """The tensor-core scans (tcgen05 whole-chunk and round-based, mma.sync) take a shortcut only where rounding is certain.  In
+    check mode every key is also scored by the strict definition: no shortcut may be wrong, and the
+    observed deviation must stay well inside the assumed error radius.  Strict and automatic modes give
+    identical masks."""
     import numpy as np
+    monkeypatch.setenv("HIPATTN_SCAN_KERNEL", scan_kernel)
     monkeypatch.setenv("HIPATTN_SCAN_MODE", "check")
     stats, md_check, _ = _scan_check_run(dtype)
     keys, fallbacks, wrong = int(stats[0]), int(stats[1]), int(stats[2])
@@ -265,7 +268,58 @@ def test_scan_tensor_core_path_is_exact(dtype, monkeypatch):
     _, md_strict, _ = _scan_check_run(dtype)
     assert torch.equal(md_auto.indices, md_strict.indices) and torch.equal(md_auto.ks, md_strict.ks)
     assert torch.equal(md_check.indices, md_strict.indices)
-    print(f"scan check {dtype}: keys {keys} fallbacks {fallbacks} ({100 * fallbacks / keys:.2f} %) max ratio {ratio:.4f}")
+    print(f"scan check {scan_kernel} {dtype}: keys {keys} fallbacks {fallbacks} ({100 * fallbacks / keys:.2f} %) max ratio {ratio:.4f}")
+
+
+@pytest.mark.parametrize("shape", [
+    dict(D=128, H=8, HKV=2, TQ=300, T=8192, strides=[4, 4, 1]),                       # 16 / 16 / 64 pooled rows, ragged block
+    dict(D=64, H=4, HKV=4, TQ=256, T=4096, strides=[2, 2, 1], keep=[2048, 1024, 512]),  # 32 / 32 / 64 rows, head dim 64
+    dict(D=128, H=4, HKV=1, TQ=128, T=1504, strides=[4, 2, 4], keep=[1024, 512, 256]),   # few chunks: groups of 16 and 32
+    dict(D=128, H=4, HKV=2, B=2, TQ=192, T=6000, strides=[1, 4, 2], keep=[4096, 1024, 512], bq=64),
+])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scan_kernels_agree(shape, dtype, monkeypatch):
+    """The scan kernels (tcgen05 whole-chunk scoring, tcgen05 round by round, mma.sync, strict) give
+    identical per-head bounds and scores at every stage, dense and through a permuted page pool."""
+    import bench
+    from cases import make_paged
+    from hip_attention_b200 import hip_attention_impl, read_status
+    w = dict(bench.WORKLOADS["prefill_128k"], keep=[4096, 2048, 1024], **{k_: v_ for k_, v_ in shape.items() if k_ != "keep"})
+    if "keep" in shape:
+        w["keep"] = shape["keep"]
+    w["dtype"] = {torch.bfloat16: "bf16", torch.float16: "fp16"}[dtype]
+    q, k, v = bench.make_qkv(w, "cuda")
+    results = {}
+    for name, env in (("auto", {"HIPATTN_SCAN_KERNEL": "auto", "HIPATTN_SCAN_MODE": "auto"}),
+                      ("dense", {"HIPATTN_SCAN_KERNEL": "dense", "HIPATTN_SCAN_MODE": "auto"}),
+                      ("rounds", {"HIPATTN_SCAN_KERNEL": "rounds", "HIPATTN_SCAN_MODE": "auto"}),
+                      ("mma", {"HIPATTN_SCAN_KERNEL": "mma", "HIPATTN_SCAN_MODE": "auto"}),
+                      ("strict", {"HIPATTN_SCAN_KERNEL": "auto", "HIPATTN_SCAN_MODE": "strict"})):
+        for k_, v_ in env.items():
+            monkeypatch.setenv(k_, v_)
+        dbg = {}
+        read_status("cuda")
+        out, md = hip_attention_impl(q, k, v, bench.make_args(w), debug=dbg)
+        torch.cuda.synchronize()
+        assert read_status("cuda") == 0
+        results[name] = (dbg["stages"], md)
+    # the same problem through a paged cache, default kernel
+    monkeypatch.setenv("HIPATTN_SCAN_MODE", "auto")
+    monkeypatch.setenv("HIPATTN_SCAN_KERNEL", "auto")
+    kc, vc, table = make_paged(k.cpu(), v.cpu(), 16, 7)
+    args = bench.make_args(w, k_cache=kc.cuda(), v_cache=vc.cuda(), block_table=table.cuda().to(torch.int32),
+                           cache_seq_lens=torch.full((w["B"],), w["T"], dtype=torch.int32, device="cuda"),
+                           extend_context_length=w["T"])
+    out_p, md_p = hip_attention_impl(q, None, None, args)
+    ref_st, ref_md = results["strict"]
+    for name in ("auto", "dense", "rounds", "mma"):
+        st, md = results[name]
+        assert len(st) == len(ref_st)
+        for i, (a, b_) in enumerate(zip(st, ref_st)):
+            for key in ("left", "right", "score", "score_max"):
+                assert torch.equal(a[key], b_[key]), f"{name}: stage {i} {key} differs from the strict kernel"
+        assert torch.equal(md.indices, ref_md.indices) and torch.equal(md.ks, ref_md.ks)
+    assert torch.equal(md_p.indices, ref_md.indices) and torch.equal(md_p.ks, ref_md.ks)
 
 
 @pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_ws", "mma"])
