@@ -54,9 +54,10 @@ namespace {
 #endif
 
 constexpr int kDenseThreads = 448;   // 2 x 4 score warps, 1 issuer, 1 producer, 4 search warps
+constexpr int kSearchWarps = 4;
 constexpr int kMaxStages = 6;
-constexpr int kRows = 10;       // row tables in flight (producer -> search warps)
-constexpr int kScr = 6;         // score tables in flight (score warps -> search warps)
+constexpr int kRows = 14;       // row tables in flight (producer -> search warps)
+constexpr int kScr = 10;        // score tables in flight (score warps -> search warps)
 constexpr int kSideRows = 4;    // key rows of uncertain scores kept per tile for the strict re-score
 constexpr int kSidePairs = 12;  // (key, head) pairs per tile served from those rows; the rest re-read the key
 constexpr int kBoundsAhead = 4; // tiles between the request for a tile's chunk bounds and their use
@@ -80,7 +81,7 @@ struct TileScores {
 };
 
 template <int DT, int D, int NR, int HB>
-__global__ void __launch_bounds__(kDenseThreads) scan_dense_tcgen05_kernel(const hipattn_scan_params_t p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap kmap_run,
+__global__ void __launch_bounds__(kDenseThreads, 1) scan_dense_tcgen05_kernel(const hipattn_scan_params_t p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap kmap_run,
                                                                             int c_log2, int n_split, int tiles_total, int n_stages, int check) {
   constexpr int ROWB = D * 2;
   constexpr int PIECES = ROWB / 16;
@@ -98,8 +99,8 @@ __global__ void __launch_bounds__(kDenseThreads) scan_dense_tcgen05_kernel(const
   unsigned char* sK = sQ + KB * Q_BLOCK_BYTES;                       // [n_stages][KB][128 keys][128 B]
   Scr* scrs = reinterpret_cast<Scr*>(sK + (size_t)n_stages * K_TILE_BYTES);   // [kScr]
   TileRows* rows_ring = reinterpret_cast<TileRows*>(scrs + kScr);    // [kRows]
-  unsigned char* kscratch = reinterpret_cast<unsigned char*>(rows_ring + kRows);   // [4 search warps][ROWB]
-  int* s_gmax = reinterpret_cast<int*>(kscratch + 4 * ROWB);         // [groups of block_chunk chunks]
+  unsigned char* kscratch = reinterpret_cast<unsigned char*>(rows_ring + kRows);   // [kSearchWarps][ROWB]
+  int* s_gmax = reinterpret_cast<int*>(kscratch + kSearchWarps * ROWB);         // [groups of block_chunk chunks]
   __shared__ __align__(8) unsigned long long s_full[kMaxStages], s_empty[kMaxStages], s_acc_full[2], s_acc_empty[2];
   __shared__ __align__(8) unsigned long long s_rows_full[kRows], s_rows_empty[kRows], s_scr_full[kScr], s_scr_empty[kScr];
   __shared__ int s_bounds[(kBoundsAhead + 1) * 64];   // ring of prefetched chunk bounds [slot][left | right][chunk]
@@ -319,6 +320,9 @@ __global__ void __launch_bounds__(kDenseThreads) scan_dense_tcgen05_kernel(const
       db0[k] = make_desc(smem_u32(sQ) + (k >> 2) * Q_BLOCK_BYTES + (k & 3) * 32, 16, 1024);
     }
     PROF_DECL(3);
+#ifdef HIPATTN_SCAN_PROFILE
+    long long prof_tm_[2] = {0, 0};
+#endif
     for (int i = 0; i < my_tiles; ++i) {
       const int s = i % n_stages, a = i & 1;
       bool ok = mbar_wait(smem_u32(&s_full[s]), (i / n_stages) & 1, &s_abort, p.status);
@@ -330,15 +334,30 @@ __global__ void __launch_bounds__(kDenseThreads) scan_dense_tcgen05_kernel(const
       tc_fence_after();
       if (lane == 0) {
         const uint64_t soff = (uint64_t)((s * K_TILE_BYTES) >> 4);
+#ifdef HIPATTN_SCAN_PROFILE
+        const long long tm0 = clock64();
+#endif
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma(tmem + a * N, da0[k] + soff, db0[k], idesc, k > 0 ? 1u : 0u);
+#ifdef HIPATTN_SCAN_PROFILE
+        const long long tm1 = clock64();
+#endif
         umma_commit(smem_u32(&s_empty[s]));
         umma_commit(smem_u32(&s_acc_full[a]));
+#ifdef HIPATTN_SCAN_PROFILE
+        prof_tm_[0] += tm1 - tm0; prof_tm_[1] += clock64() - tm1;
+#endif
       }
       __syncwarp();
       PROF_LAP(2);
     }
     PROF_FLUSH(12, 3, lane == 0);
+#ifdef HIPATTN_SCAN_PROFILE
+    if (lane == 0 && p.stats) {
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.stats) + 30, (unsigned long long)prof_tm_[0]);
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.stats) + 31, (unsigned long long)prof_tm_[1]);
+    }
+#endif
   } else if (my_tiles > 0 && warp < 8) {
     // ================================ scores: thread = key = TMEM lane ================================
     // Two groups of four warps; group g takes the tiles of accumulator g (every other tile), so each has
@@ -368,19 +387,25 @@ __global__ void __launch_bounds__(kDenseThreads) scan_dense_tcgen05_kernel(const
       PROF_LAP(1);
       if (!ok) break;
       tc_fence_after();
+      // the accumulator is read in as few TMEM loads as registers allow (64 columns per load and wait)
       float x[HB];
+      constexpr int BW = N < 64 ? N : 64;     // 128 would not fit the register budget of 448 threads
 #pragma unroll
-      for (int hh = 0; hh < HB; ++hh) {
-        float v[NR];
-        const uint32_t ta = my_tmem + a * N + hh * NR;
-        if (NR == 16) tmem_ld16(ta, v);
-        else if (NR == 32) tmem_ld32(ta, v);
-        else tmem_ld64(ta, v);
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four short chains instead of one long one
+      for (int c0 = 0; c0 < N; c0 += BW) {
+        float v[BW];
+        const uint32_t ta = my_tmem + a * N + c0;
+        if (BW == 16) tmem_ld16(ta, v);
+        else if (BW == 32) tmem_ld32(ta, v);
+        else if (BW == 64) tmem_ld64(ta, v);
+        else tmem_ld128(ta, v);
 #pragma unroll
-        for (int j = 0; j < NR; ++j)
-          if (j < Rv) m4[j & 3] = fmaxf(m4[j & 3], v[j]);
-        x[hh] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        for (int h2 = 0; h2 < BW / NR; ++h2) {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four short chains instead of one long one
+#pragma unroll
+          for (int j = 0; j < NR; ++j)
+            if (j < Rv) m4[j & 3] = fmaxf(m4[j & 3], v[h2 * NR + j]);
+          x[c0 / NR + h2] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&s_acc_empty[a]));
@@ -477,12 +502,12 @@ __global__ void __launch_bounds__(kDenseThreads) scan_dense_tcgen05_kernel(const
     constexpr int GS = NR < 32 ? NR : 32;     // lanes per pair
     constexpr int G = 32 / GS;                // pairs side by side in the warp
     constexpr int RP = NR / GS;               // row passes per pair
-    constexpr int PPG = 4 / RP;               // pairs per lane group and batch
+    constexpr int PPG = 2 / RP;               // pairs per lane group and batch (two chains per lane)
     constexpr int BP = G * PPG;
     const int grp = lane / GS, gl_lane = lane % GS;
 
     PROF_DECL(10);
-    for (int i = sw; i < my_tiles; i += 4) {
+    for (int i = sw; i < my_tiles; i += kSearchWarps) {
       const int rr = i % kRows, sr = i % kScr, tile = tile_of(i);
       const TileRows& tr = rows_ring[rr];
       Scr& scr = scrs[sr];
@@ -507,49 +532,57 @@ __global__ void __launch_bounds__(kDenseThreads) scan_dense_tcgen05_kernel(const
         scr.score[hh][key] = ex;
       };
       // Pairs [e0, e0 + cnt) of the tile's list (rows in scr.kraw), or, with `one_row` set, the single pair
-      // (one_key, one_head) whose key row is at one_row.  Pair slot q of lane group g is pair e0 + q * G + g.
+      // (one_key, one_head) whose key row is at one_row.  A lane runs two sequential fp32 chains side by
+      // side, branch-free, with the operands of four 16-byte pieces in registers at a time: a lone warp hides
+      // no latency, so the loop is laid out as straight-line code the scheduler can overlap.
       auto strict_batch = [&](int e0, int cnt, const unsigned char* one_row, int one_key, int one_head) {
-        const int n_chains = ((cnt + G - 1) / G) * RP;    // chains that hold a pair (the same for all lanes)
 #ifdef HIPATTN_SCAN_PROFILE
         const long long tb0 = clock64();
-        prof_[5] += 1; prof_[9] += n_chains;
+        prof_[5] += 1; prof_[9] += cnt;
 #endif
-        uint32_t kp[4];     // shared-space addresses of the chains' key rows
-        int qrow[4];
-        bool valid[4];
-        float acc[4];
+        uint32_t kp[2], qp[2];     // shared-space addresses of the chains' key rows / pooled-query rows
+        bool valid[2];
+        float acc[2] = {0.f, 0.f};
         const uint32_t sQ_s = smem_u32(sQ);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           const int e = (c / RP) * G + grp;
           const int r = (c % RP) * GS + gl_lane;
           valid[c] = e < cnt && r < Rv;
           const int ee = e0 + (e < cnt ? e : 0);
           const int hd = one_row ? one_head : (int)scr.pair_head[ee];
           kp[c] = smem_u32(one_row ? one_row : scr.kraw[scr.pair_slot[ee]]);
-          qrow[c] = hd * NR + (r < NR ? r : 0);
-          acc[c] = 0.f;
+          const int qrow = hd * NR + (r < NR ? r : 0);
+          qp[c] = sQ_s + qrow * 128;
+          valid[c] = valid[c];
         }
+        const uint32_t qx0 = (uint32_t)((qp[0] >> 7) & 7u), qx1 = (uint32_t)((qp[1] >> 7) & 7u);   // swizzle phase of the rows
 #ifdef HIPATTN_SCAN_PROFILE
         const long long tb1 = clock64();
 #endif
-#pragma unroll 2
-        for (int pc = 0; pc < PIECES; ++pc) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            if (c >= n_chains) continue;
-            const uint4 qw = lds128(sQ_s + (pc >> 3) * Q_BLOCK_BYTES + sw128(qrow[c], pc & 7));
-            const uint4 kw = lds128(kp[c] + pc * 16);
-            float a_ = acc[c];
-            a_ = fmaf(lo_f32<DT>(qw.x), lo_f32<DT>(kw.x), a_);
-            a_ = fmaf(hi_f32<DT>(qw.x), hi_f32<DT>(kw.x), a_);
-            a_ = fmaf(lo_f32<DT>(qw.y), lo_f32<DT>(kw.y), a_);
-            a_ = fmaf(hi_f32<DT>(qw.y), hi_f32<DT>(kw.y), a_);
-            a_ = fmaf(lo_f32<DT>(qw.z), lo_f32<DT>(kw.z), a_);
-            a_ = fmaf(hi_f32<DT>(qw.z), hi_f32<DT>(kw.z), a_);
-            a_ = fmaf(lo_f32<DT>(qw.w), lo_f32<DT>(kw.w), a_);
-            a_ = fmaf(hi_f32<DT>(qw.w), hi_f32<DT>(kw.w), a_);
-            acc[c] = a_;
+        for (int pb = 0; pb < PIECES; pb += 4) {
+          uint4 q0[4], q1[4], k0[4], k1[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int pc = pb + j;
+            q0[j] = lds128(qp[0] + (pc >> 3) * Q_BLOCK_BYTES + ((((uint32_t)pc & 7u) ^ qx0) << 4));
+            q1[j] = lds128(qp[1] + (pc >> 3) * Q_BLOCK_BYTES + ((((uint32_t)pc & 7u) ^ qx1) << 4));
+            k0[j] = lds128(kp[0] + pc * 16);
+            k1[j] = lds128(kp[1] + pc * 16);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float a0 = acc[0], a1 = acc[1];
+            a0 = fmaf(lo_f32<DT>(q0[j].x), lo_f32<DT>(k0[j].x), a0);  a1 = fmaf(lo_f32<DT>(q1[j].x), lo_f32<DT>(k1[j].x), a1);
+            a0 = fmaf(hi_f32<DT>(q0[j].x), hi_f32<DT>(k0[j].x), a0);  a1 = fmaf(hi_f32<DT>(q1[j].x), hi_f32<DT>(k1[j].x), a1);
+            a0 = fmaf(lo_f32<DT>(q0[j].y), lo_f32<DT>(k0[j].y), a0);  a1 = fmaf(lo_f32<DT>(q1[j].y), lo_f32<DT>(k1[j].y), a1);
+            a0 = fmaf(hi_f32<DT>(q0[j].y), hi_f32<DT>(k0[j].y), a0);  a1 = fmaf(hi_f32<DT>(q1[j].y), hi_f32<DT>(k1[j].y), a1);
+            a0 = fmaf(lo_f32<DT>(q0[j].z), lo_f32<DT>(k0[j].z), a0);  a1 = fmaf(lo_f32<DT>(q1[j].z), lo_f32<DT>(k1[j].z), a1);
+            a0 = fmaf(hi_f32<DT>(q0[j].z), hi_f32<DT>(k0[j].z), a0);  a1 = fmaf(hi_f32<DT>(q1[j].z), hi_f32<DT>(k1[j].z), a1);
+            a0 = fmaf(lo_f32<DT>(q0[j].w), lo_f32<DT>(k0[j].w), a0);  a1 = fmaf(lo_f32<DT>(q1[j].w), lo_f32<DT>(k1[j].w), a1);
+            a0 = fmaf(hi_f32<DT>(q0[j].w), hi_f32<DT>(k0[j].w), a0);  a1 = fmaf(hi_f32<DT>(q1[j].w), hi_f32<DT>(k1[j].w), a1);
+            acc[0] = a0; acc[1] = a1;
           }
         }
 #ifdef HIPATTN_SCAN_PROFILE
@@ -559,7 +592,7 @@ __global__ void __launch_bounds__(kDenseThreads) scan_dense_tcgen05_kernel(const
 #pragma unroll
         for (int q_ = 0; q_ < PPG; ++q_) best[q_] = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
           if (valid[c]) best[c / RP] = fmaxf(best[c / RP], acc[c]);
 #pragma unroll
         for (int q_ = 0; q_ < PPG; ++q_) {
@@ -711,7 +744,7 @@ int launch(const hipattn_scan_params_t& p, int c_log2, cudaStream_t stream) {
   // shared memory: 1 KB alignment slack, pooled queries, the two table rings, scratch rows, group maxima, then
   // as many key tiles as fit beside ~2 KB of static data
   const size_t fixed = 1024 + (size_t)KB * N * 128 + kScr * sizeof(TileScores<HB, D * 2>) + kRows * sizeof(TileRows) +
-                       4 * D * 2 + (size_t)n_groups * sizeof(int);
+                       kSearchWarps * D * 2 + (size_t)n_groups * sizeof(int);
   const size_t tile_bytes = (size_t)KB * 128 * 128;
   int n_stages = (int)((224 * 1024 - fixed) / tile_bytes);
   n_stages = n_stages > kMaxStages ? kMaxStages : n_stages;
@@ -778,7 +811,9 @@ int scan_dense_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool
   while (HB > 1 && (Gq % HB != 0 || HB * NRp > 256)) HB >>= 1;
   // Whole-chunk scoring gathers fewer rows than the rounds when C <= HB * 2 * (log2 C + 1), but its single
   // producer / issuer warps are not yet faster than the many CTAs of the round-by-round kernel: opt-in only.
-  if (!(v && strcmp(v, "dense") == 0)) return HIPATTN_OK;
+  const char* mc = getenv("HIPATTN_SCAN_DENSE_MAX_CHUNK");   // chunk sizes up to this use whole-chunk scoring (default: none)
+  const int max_chunk = mc ? atoi(mc) : 0;
+  if (!(v && strcmp(v, "dense") == 0) && C > max_chunk) return HIPATTN_OK;
   *handled = true;
   if (p.dtype == HIPATTN_BF16) return p.D == 128 ? dispatch_rows<HIPATTN_BF16, 128>(p, c_log2, HB, stream) : dispatch_rows<HIPATTN_BF16, 64>(p, c_log2, HB, stream);
   return p.D == 128 ? dispatch_rows<HIPATTN_F16, 128>(p, c_log2, HB, stream) : dispatch_rows<HIPATTN_F16, 64>(p, c_log2, HB, stream);

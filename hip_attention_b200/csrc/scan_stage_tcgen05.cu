@@ -241,15 +241,20 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
       float x = -INFINITY;
       if (ok) {
         float v[NR];
-        if (NR == 16) {
-          tmem_ld16(my_tmem, v);
+        if (NR == 16) tmem_ld16(my_tmem, v);
+        else if (NR == 32) tmem_ld32(my_tmem, v);
+        else tmem_ld64(my_tmem, v);
+        // four short maximum chains; the row mask is only paid for by a ragged last query block
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (Rv >= NR) {
+#pragma unroll
+          for (int j = 0; j < NR; ++j) m4[j & 3] = fmaxf(m4[j & 3], v[j]);
         } else {
 #pragma unroll
-          for (int c0 = 0; c0 < NR; c0 += 32) tmem_ld32(my_tmem + c0, v + c0);
+          for (int j = 0; j < NR; ++j)
+            if (j < Rv) m4[j & 3] = fmaxf(m4[j & 3], v[j]);
         }
-#pragma unroll
-        for (int j = 0; j < NR; ++j)
-          if (j < Rv) x = fmaxf(x, v[j]);
+        x = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
       const float s_abs = act ? p.key_abs[idx] : 0.f;
       const float e_ = eps_q * s_abs * 1.01f;
