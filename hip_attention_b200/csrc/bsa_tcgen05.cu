@@ -32,6 +32,16 @@ constexpr int D5 = 128;            // head dimension
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 of the growth that triggers a rescale
 
+// 2^x on the special-function unit alone (ex2.approx: about 2 ulp, flushes denormal results, 2^-inf = 0).
+// The probabilities are rounded to 8 or 11 significant bits right after, so the exact exp2f sequence
+// (range split + rescale around the same instruction) buys nothing here and costs three more instructions
+// per logit in the longest loop of the kernel.
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct Meta5 {
   int tpos[TK5];
   int twin[TK5];
@@ -307,7 +317,7 @@ __global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_p
         tmem_ld32(tmem_s + lane_base + c * 32, v);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          v[j] = exp2f(fmaf(v[j], kLog2e, -base));
+          v[j] = exp2_approx(fmaf(v[j], kLog2e, -base));
           sum4[j & 3] += v[j];
         }
 #pragma unroll
@@ -325,7 +335,7 @@ __global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_p
         tmem_ld16(tmem_s + lane_base + c * 16, v);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          v[j] = exp2f(logit(v[j], c * 16 + j) - base);
+          v[j] = exp2_approx(logit(v[j], c * 16 + j) - base);
           sum4[j & 3] += v[j];
         }
         uint4 w0, w1;
@@ -679,8 +689,8 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       float pk[32];
 #pragma unroll
       for (int j = 0; j < TK5; j += 2) {
-        const float e0 = exp2f(fmaf(s[j], kLog2e, -base));
-        const float e1 = exp2f(fmaf(s[j + 1], kLog2e, -base));
+        const float e0 = exp2_approx(fmaf(s[j], kLog2e, -base));
+        const float e1 = exp2_approx(fmaf(s[j + 1], kLog2e, -base));
         sum4[(j >> 1) & 3] += e0 + e1;
         pk[j >> 1] = __uint_as_float(pack2<DT>(e0, e1));
       }
