@@ -348,12 +348,16 @@ def main():
             with torch.cuda.stream(s_in):
                 if ev_free[j] is not None:
                     s_in.wait_event(ev_free[j])
-                for dst, src in zip(dbuf[j], (hq, hk, hv)):
-                    dst.copy_(src, non_blocking=True)
+                # q and k first: the estimator starts on them while v is still on its way
+                dbuf[j][0].copy_(hq, non_blocking=True)
+                dbuf[j][1].copy_(hk, non_blocking=True)
                 ev_in[j] = torch.cuda.Event()
                 ev_in[j].record(s_in)
+                dbuf[j][2].copy_(hv, non_blocking=True)
+                ev_v = torch.cuda.Event()
+                ev_v.record(s_in)
             s_main.wait_event(ev_in[j])
-            o, _ = hip_attention_impl(*dbuf[j], args, score_reduce=reduce)
+            o, _ = hip_attention_impl(*dbuf[j], args, score_reduce=reduce, v_ready=ev_v)
             ev_free[j] = torch.cuda.Event()
             ev_free[j].record(s_main)
             with torch.cuda.stream(s_out):

@@ -432,12 +432,15 @@ def _check_inputs(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args: HiP
 
 def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args: HiPAttentionArgs,
                        cached_metadata: Optional[HiPAttentionOutputMetadata] = None, *, return_lse: bool = False,
-                       debug: Optional[dict] = None, score_reduce=None, timer: Optional[PhaseTimer] = None):
+                       debug: Optional[dict] = None, score_reduce=None, timer: Optional[PhaseTimer] = None,
+                       v_ready: Optional[torch.cuda.Event] = None):
     """Implementation behind ``hip_attention_12``.
 
     ``return_lse`` adds the base-2 log-sum-exp [B, TQ, H]; ``score_reduce`` is handed to the estimator
     (see ``_estimate_mask``); ``timer`` collects per-phase CUDA-event times; ``debug`` collects the
-    per-head outputs of every scan stage."""
+    per-head outputs of every scan stage.  ``v_ready``: the mask estimator reads only q and k, so a caller
+    that streams its inputs to the device may issue the call as soon as q and k have arrived and pass the
+    event that marks the arrival of v (dense ``v`` or the value cache); the attention launch waits for it."""
     _check_inputs(q, k, v, args)
     _reject_unsupported(args)
     args = args.clone()
@@ -546,6 +549,8 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
             raise NotImplementedError("the sliding_window_size == 777 sentinel of the serving adapter is not built")
         decode = TQ == 1 and not args.disable_flashdecode and os.environ.get("HIP_DISABLE_FLASHDECODE", "0") != "1"
         if timer: timer.mark("start")
+        if v_ready is not None:
+            torch.cuda.current_stream(dev).wait_event(v_ready)
         context, lse = _attention(q_bsa, ktok, vtok, T, HKV, pos, indices, ks, sink=args.sink_token_size, window=sw_attn,
                                   block_size_k=c_last, bsa_block_q=bsa_bq, index_block_q=index_block_q,
                                   heads_share=heads_share, decode=decode, softcap=args.logit_softcap,

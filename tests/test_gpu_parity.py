@@ -349,6 +349,29 @@ def test_prefill_head_dim_128_matches_oracle(kernel, bq, tq, hkv, dtype, monkeyp
     assert (lse.cpu().double() - lse_ref).abs().max().item() < 2e-2
 
 
+def test_values_may_arrive_after_the_call_is_issued():
+    """The estimator reads q and k only: with ``v_ready`` the call is issued before v has been copied in on
+    another stream, and gives the result of the plain call."""
+    import bench
+    from hip_attention_b200 import hip_attention_impl
+    w = dict(bench.WORKLOADS["prefill_128k"], TQ=256, T=8192, H=8, HKV=2, keep=[4096, 2048, 1024])
+    q, k, v = bench.make_qkv(w, "cuda")
+    args = bench.make_args(w)
+    ref, _ = hip_attention_impl(q, k, v, args)
+    torch.cuda.synchronize()
+    hv = v.cpu().pin_memory()
+    dv = torch.zeros_like(v)
+    side = torch.cuda.Stream()
+    ev = torch.cuda.Event()
+    with torch.cuda.stream(side):
+        torch.cuda._sleep(20_000_000)            # the copy starts well after the call below has been issued
+        dv.copy_(hv, non_blocking=True)
+        ev.record(side)
+    out, _ = hip_attention_impl(q, k, dv, args, v_ready=ev)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
+
+
 def test_decode_under_cuda_graph_capture():
     """With position_ids given the operator makes no host synchronisation, so a decode step (mask
     refresh or cached mask) can be captured in a CUDA graph and replayed on new queries
