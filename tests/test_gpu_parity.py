@@ -245,7 +245,7 @@ def _scan_check_run(dtype, TQ=512, T=16384):
     return stats.cpu(), md, (q, k, v, w)
 
 
-@pytest.mark.parametrize("scan_kernel", ["auto", "dense", "rounds", "mma"])
+@pytest.mark.parametrize("scan_kernel", ["auto", "chunks", "dense", "rounds", "mma"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_scan_tensor_core_path_is_exact(dtype, scan_kernel, monkeypatch):
     """The tensor-core scans (tcgen05 whole-chunk and round-based, mma.sync) take a shortcut only where rounding is certain.  In
@@ -291,6 +291,7 @@ def test_scan_kernels_agree(shape, dtype, monkeypatch):
     q, k, v = bench.make_qkv(w, "cuda")
     results = {}
     for name, env in (("auto", {"HIPATTN_SCAN_KERNEL": "auto", "HIPATTN_SCAN_MODE": "auto"}),
+                      ("chunks", {"HIPATTN_SCAN_KERNEL": "chunks", "HIPATTN_SCAN_MODE": "auto"}),
                       ("dense", {"HIPATTN_SCAN_KERNEL": "dense", "HIPATTN_SCAN_MODE": "auto"}),
                       ("rounds", {"HIPATTN_SCAN_KERNEL": "rounds", "HIPATTN_SCAN_MODE": "auto"}),
                       ("mma", {"HIPATTN_SCAN_KERNEL": "mma", "HIPATTN_SCAN_MODE": "auto"}),
@@ -312,7 +313,7 @@ def test_scan_kernels_agree(shape, dtype, monkeypatch):
                            extend_context_length=w["T"])
     out_p, md_p = hip_attention_impl(q, None, None, args)
     ref_st, ref_md = results["strict"]
-    for name in ("auto", "dense", "rounds", "mma"):
+    for name in ("auto", "chunks", "dense", "rounds", "mma"):
         st, md = results[name]
         assert len(st) == len(ref_st)
         for i, (a, b_) in enumerate(zip(st, ref_st)):
