@@ -1,0 +1,300 @@
+// Scan stage of the mask estimator for decode (one pooled query row per head), small chunks, strict
+// arithmetic: every token of every active chunk is fetched ONCE for all query heads of a KV head, scored
+// against each head's query with the strict dot product, and the halving search of the reference
+// (attention_extend.py:413-1249) is replayed on the stored scores.
+//
+// The search of a chunk only ever scores tokens of that chunk, two per round and head.  In decode the key
+// rows come from HBM (the cache of a batch is far larger than L2), so rows fetched are time: for a last
+// stage of chunk 8 and four heads per KV head the rounds fetch 4 x 2 x 4 = 32 rows per chunk, the whole
+// chunk is 8; for chunk 32 it is 48 against 32.  Scores are the strict kernel's (sequential fp32 dot over
+// the head dimension of round(k * k_scale), rounded to the element type), comparisons are the reference's,
+// so bounds and scores are identical to scan_stage_kernel's.
+//
+// Mapping: a warp takes 32 consecutive rows = 32 / chunk whole chunks per pass; lane = token.  The rows
+// are gathered with 16-byte cp.async (through the page table when the keys are paged) into a per-warp
+// staging area, every lane scores its own row against the HB head queries held in shared memory as fp32,
+// the rounded scores go to a per-warp table and the first HB lanes of every chunk walk the search tree.
+// No block-wide barrier after the prologue; six CTAs of four warps per SM keep about 190 KB of rows in flight.
+#include <cstdlib>
+#include <cstring>
+
+#include "scan_common.cuh"
+
+namespace hipattn {
+namespace {
+
+constexpr int kPadS = 16;  // bytes of padding per staged key row: keeps 16-byte lane reads conflict free
+
+template <int DT>
+__device__ __forceinline__ void unpack_scaled_s(const uint4& w, float k_scale, float* out);
+template <>
+__device__ __forceinline__ void unpack_scaled_s<HIPATTN_F32>(const uint4& w, float k_scale, float* out) {
+  out[0] = __fmul_rn(__uint_as_float(w.x), k_scale);
+  out[1] = __fmul_rn(__uint_as_float(w.y), k_scale);
+  out[2] = __fmul_rn(__uint_as_float(w.z), k_scale);
+  out[3] = __fmul_rn(__uint_as_float(w.w), k_scale);
+}
+template <>
+__device__ __forceinline__ void unpack_scaled_s<HIPATTN_BF16>(const uint4& w, float k_scale, float* out) {
+  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = Elem<HIPATTN_BF16>::round(__fmul_rn(__uint_as_float(v[i] << 16), k_scale));
+    out[2 * i + 1] = Elem<HIPATTN_BF16>::round(__fmul_rn(__uint_as_float(v[i] & 0xffff0000u), k_scale));
+  }
+}
+template <>
+__device__ __forceinline__ void unpack_scaled_s<HIPATTN_F16>(const uint4& w, float k_scale, float* out) {
+  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v[i]));
+    out[2 * i] = Elem<HIPATTN_F16>::round(__fmul_rn(f.x, k_scale));
+    out[2 * i + 1] = Elem<HIPATTN_F16>::round(__fmul_rn(f.y, k_scale));
+  }
+}
+
+template <int DT>
+__device__ __forceinline__ float mac_s(float q, float k, float acc) {
+  if (DT == HIPATTN_F32) return __fadd_rn(acc, __fmul_rn(q, k));  // two roundings, reproducible on a CPU
+  return fmaf(q, k, acc);                                         // 16-bit inputs: the product is exact
+}
+
+template <int DT, int D, int HB>
+__global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_scan_params_t p, int c_log2, int n_split, int passes_total) {
+  constexpr int EB = Elem<DT>::bytes;
+  constexpr int ROWB = D * EB;
+  constexpr int STRIDE = ROWB + kPadS;
+  constexpr int PIECES = ROWB / 16;
+  constexpr int VEC = 16 / EB;
+  extern __shared__ __align__(16) unsigned char smem[];
+  float* qtile = reinterpret_cast<float*>(smem);                         // [HB][D]
+  unsigned char* kstage = smem + (size_t)HB * D * sizeof(float);         // [4 warps][32][STRIDE]
+  float* stab = reinterpret_cast<float*>(kstage + (size_t)4 * 32 * STRIDE);   // [4 warps][HB][32]
+  __shared__ int s_pmin;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int Gq = p.H / p.HKV;
+  const int BDST = cdiv(p.TQ, p.block_size_q);
+  const int n_hb = Gq / HB;
+  int64_t bid = blockIdx.x;
+  const int split = (int)(bid % n_split); bid /= n_split;
+  const int hb = (int)(bid % n_hb); bid /= n_hb;
+  const int d = (int)(bid % BDST); bid /= BDST;
+  const int hkv = (int)(bid % p.HKV); bid /= p.HKV;
+  const int b = (int)bid;
+  const int h0 = hkv * Gq + hb * HB;
+  const int t0 = d * p.block_size_q;
+  const bool has_row = t0 < p.TQ;
+
+  // the single pooled query row of every head of the batch
+  for (int i = threadIdx.x; i < HB * PIECES; i += 128) {
+    const int hh = i / PIECES, pc = i % PIECES;
+    float v[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v[e] = 0.f;
+    if (has_row) pooled_query_piece<DT>(p, b, h0 + hh, t0, pc, v);
+#pragma unroll
+    for (int e = 0; e < VEC; e += 4)
+      *reinterpret_cast<float4*>(qtile + hh * D + pc * VEC + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+  }
+  if (warp == 0) {
+    const int m = block_min_position(p, b, t0, has_row ? 1 : 0, lane);
+    if (lane == 0) s_pmin = m;
+  }
+  __syncthreads();
+  if (!has_row) return;
+  const int pt = max(s_pmin - p.scan_window, 0);
+  const int C = 1 << c_log2;
+  const int cpp_log2 = 5 - c_log2;                  // chunks per pass = 32 / C
+  const int n = p.n_chunks;
+  const int64_t row = (int64_t)b * BDST + d;
+  const int32_t* gl = p.left + row * n;
+  const int32_t* gr = p.right + row * n;
+  const int bc_log2 = 31 - __clz(p.block_chunk);
+  unsigned char* wstage = kstage + (size_t)warp * 32 * STRIDE;
+  const unsigned char* my_row = wstage + (size_t)lane * STRIDE;
+  float* wtab = stab + warp * HB * 32;
+  const int grp_base = lane & ~(C - 1);             // first lane of this lane's chunk
+  const int cl = lane >> c_log2;                    // chunk of the pass
+  int cur_group = -1, cur_gmax = 0;
+
+  // passes of this warp: the unit's passes are dealt to the n_split CTAs x 4 warps round-robin
+  for (int ps = split * 4 + warp; ps < passes_total; ps += n_split * 4) {
+    const int c = (ps << cpp_log2) + cl;
+    int l = 0, rt = 0;
+    if (c < n) { l = gl[c]; rt = gr[c]; }
+    if (rt - l > C) atomicOr(p.status, HIPATTN_STATUS_CHUNK_SIZE);
+    // halving rounds: from the largest chunk of the reference group of block_chunk chunks (all chunks of a
+    // pass lie in one group: a pass holds at most 8 chunks, a group at least 16, both powers of two)
+    const int group = (ps << cpp_log2) >> bc_log2;
+    if (group != cur_group) {
+      int m = 0;
+      const int gbase = group << bc_log2;
+      for (int i = lane; i < p.block_chunk; i += 32) {
+        const int cc = gbase + i;
+        if (cc < n) m = max(m, gr[cc] - gl[cc]);
+      }
+      cur_gmax = __reduce_max_sync(0xffffffffu, m);
+      cur_group = group;
+    }
+    const int rounds = cur_gmax >= 1 ? 32 - __clz(cur_gmax) : 0;
+    // this lane's token
+    const bool chunk_act = c < n && l < rt && l <= pt && l >= 0;
+    int tk = l + (lane & (C - 1));
+    const bool valid = chunk_act && tk < rt;
+    const char* src = nullptr;
+    if (valid) {
+      if (p.k.cache == nullptr && tk >= p.T) {
+        atomicOr(p.status, HIPATTN_STATUS_TOKEN_RANGE);
+        tk = p.T - 1;
+      }
+      src = token_row(p.k, b, tk, hkv, EB, p.status);
+    }
+    if (__any_sync(0xffffffffu, valid)) {   // chunks that are not active still report their (unchanged) bounds below
+    // cooperative gather of the pass's 32 rows
+    __syncwarp();
+    if (PIECES <= 32) {
+      constexpr int RPI = 32 / PIECES > 0 ? 32 / PIECES : 1;     // rows per instruction
+      const int sub = lane / PIECES, piece = lane % PIECES;
+#pragma unroll 4
+      for (int r0 = 0; r0 < 32; r0 += RPI) {
+        const int rr = r0 + sub;
+        const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, rr & 31);
+        if (a != 0ull && sub < RPI) cp_async16(wstage + (size_t)rr * STRIDE + piece * 16, (const char*)a + piece * 16);
+      }
+    } else {
+      for (int rr = 0; rr < 32; ++rr) {
+        const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, rr);
+        if (a != 0ull)
+          for (int piece = lane; piece < PIECES; piece += 32) cp_async16(wstage + (size_t)rr * STRIDE + piece * 16, (const char*)a + piece * 16);
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+    // strict scores of this lane's token for the HB heads
+    if (valid) {
+      float acc[HB];
+#pragma unroll
+      for (int hh = 0; hh < HB; ++hh) acc[hh] = 0.f;
+#pragma unroll 2
+      for (int pc = 0; pc < PIECES; ++pc) {
+        float kv[VEC];
+        unpack_scaled_s<DT>(*reinterpret_cast<const uint4*>(my_row + pc * 16), p.k_scale, kv);
+#pragma unroll
+        for (int hh = 0; hh < HB; ++hh) {
+#pragma unroll
+          for (int e4 = 0; e4 < VEC; e4 += 4) {
+            const float4 qv = *reinterpret_cast<const float4*>(qtile + hh * D + pc * VEC + e4);
+            acc[hh] = mac_s<DT>(qv.x, kv[e4 + 0], acc[hh]);
+            acc[hh] = mac_s<DT>(qv.y, kv[e4 + 1], acc[hh]);
+            acc[hh] = mac_s<DT>(qv.z, kv[e4 + 2], acc[hh]);
+            acc[hh] = mac_s<DT>(qv.w, kv[e4 + 3], acc[hh]);
+          }
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < HB; ++hh) wtab[hh * 32 + lane] = Elem<DT>::round(acc[hh]);
+    }
+    __syncwarp();
+    }
+    __syncwarp();
+    // the first HB lanes of every chunk replay the search of one head each
+    const int hh = lane - grp_base;
+    const bool walker = hh < HB && c < n;
+    float score = HIPATTN_SCORE_INIT;
+    if (walker) {
+      int wl = l, wr = rt;
+      const float* sc = wtab + hh * 32 + grp_base;
+      for (int it = 0; it < rounds; ++it) {
+        if (!(wl < wr && wl <= pt && wl >= 0)) break;
+        const int mid = (wl + wr) >> 1;
+        const float sl = sc[min(((wl + mid) >> 1) - l, C - 1)];
+        const float sr = sc[min(((mid + wr) >> 1) - l, C - 1)];
+        const bool win = sl > sr;
+        if (win) wr = mid; else wl = mid;
+        score = fmaxf(score, win ? sl : sr);
+      }
+      const int64_t o = (row * p.H + h0 + hh) * n + c;
+      if (p.left_out) p.left_out[o] = wl;
+      if (p.right_out) p.right_out[o] = wr;
+      if (p.score_out) p.score_out[o] = score;
+    }
+    float best = score;
+#pragma unroll
+    for (int o = 1; o < HB; o <<= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if (walker && hh == 0 && best > HIPATTN_SCORE_INIT) atomicMax(p.score_max + row * n + c, encode_score(best));
+    __syncwarp();
+  }
+}
+
+template <int DT, int D, int HB>
+int launch(const hipattn_scan_params_t& p, int c_log2, cudaStream_t stream) {
+  constexpr int EB = Elem<DT>::bytes;
+  const size_t smem = (size_t)HB * D * sizeof(float) + (size_t)4 * 32 * (D * EB + kPadS) + (size_t)4 * HB * 32 * sizeof(float);
+  HIPATTN_REQUIRE(smem <= 227 * 1024, HIPATTN_ERR_UNSUPPORTED, "chunk scan stage needs %zu bytes of shared memory", smem);
+  const int BDST = cdiv(p.TQ, p.block_size_q);
+  const int Gq = p.H / p.HKV;
+  const int passes_total = cdiv(p.n_chunks, 32 >> c_log2);
+  const int64_t units = (int64_t)p.B * p.HKV * BDST * (Gq / HB);
+  // enough CTAs to fill the GPU about six deep, never more than there are passes for four warps each
+  int64_t want = (148 * 6 * 2 + units - 1) / units;
+  const int64_t most = cdiv(passes_total, 4);
+  int n_split = (int)(want < 1 ? 1 : (want > most ? most : want));
+  if (n_split < 1) n_split = 1;
+  const int64_t grid = units * n_split;
+  HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
+  auto kern = scan_chunks_strict_kernel<DT, D, HB>;
+  HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)grid, 128, smem, stream>>>(p, c_log2, n_split, passes_total);
+  return check_launch("scan_chunks_strict_kernel");
+}
+
+template <int DT, int D>
+int dispatch_heads(const hipattn_scan_params_t& p, int c_log2, int HB, cudaStream_t stream) {
+  switch (HB) {
+    case 4: return launch<DT, D, 4>(p, c_log2, stream);
+    case 2: return launch<DT, D, 2>(p, c_log2, stream);
+    default: return launch<DT, D, 1>(p, c_log2, stream);
+  }
+}
+
+template <int DT>
+int dispatch_dim(const hipattn_scan_params_t& p, int c_log2, int HB, cudaStream_t stream) {
+  switch (p.D) {
+    case 64: return dispatch_heads<DT, 64>(p, c_log2, HB, stream);
+    case 128: return dispatch_heads<DT, 128>(p, c_log2, HB, stream);
+    default: return dispatch_heads<DT, 256>(p, c_log2, HB, stream);
+  }
+}
+
+}  // namespace
+
+// Decode shapes (a single pooled query row) whose chunk size is a known power of two between 4 and 32 and no
+// larger than the number of rows the rounds of the heads sharing the chunk would fetch.
+// HIPATTN_DECODE_SCAN=rounds keeps the round-by-round kernel.
+int scan_chunks_strict(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled) {
+  *handled = false;
+  const int R = p.block_size_q / p.stride_q;
+  const int rows = min(R, cdiv(p.TQ, p.stride_q));
+  if (rows > 1 || (p.D != 64 && p.D != 128 && p.D != 256)) return HIPATTN_OK;
+  const int C = p.chunk_size;
+  if (C < 4 || C > 32 || (C & (C - 1)) != 0) return HIPATTN_OK;
+  const char* v = getenv("HIPATTN_DECODE_SCAN");
+  if (v && strcmp(v, "rounds") == 0) return HIPATTN_OK;
+  int c_log2 = 0;
+  while ((1 << c_log2) < C) ++c_log2;
+  const int Gq = p.H / p.HKV;
+  int HB = 4;
+  while (HB > 1 && Gq % HB != 0) HB >>= 1;
+  if (C > HB * 2 * (c_log2 + 1)) return HIPATTN_OK;
+  *handled = true;
+  switch (p.dtype) {
+    case HIPATTN_F32: return dispatch_dim<HIPATTN_F32>(p, c_log2, HB, stream);
+    case HIPATTN_F16: return dispatch_dim<HIPATTN_F16>(p, c_log2, HB, stream);
+    default: return dispatch_dim<HIPATTN_BF16>(p, c_log2, HB, stream);
+  }
+}
+
+}  // namespace hipattn
