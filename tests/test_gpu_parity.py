@@ -350,6 +350,49 @@ def test_prefill_head_dim_128_matches_oracle(kernel, bq, tq, hkv, dtype, monkeyp
     assert (lse.cpu().double() - lse_ref).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [
+    dict(B=3, H=8, HKV=2, D=128, T=8192),                                  # four heads per KV head: chunk 32 and chunk 8
+    dict(B=2, H=4, HKV=2, D=64, T=4096, keep=[2048, 1024, 512]),           # two heads per KV head: only chunk 8 qualifies
+    dict(B=2, H=3, HKV=3, D=128, T=5000, keep=[4096, 1024, 512]),          # one head per KV head, ragged last chunk
+])
+def test_decode_scan_whole_chunks_equals_rounds(shape, dtype, monkeypatch):
+    """Decode: scoring whole small chunks once per KV head and replaying the search gives the per-head bounds
+    and scores of the round-by-round strict kernel at every stage, dense and paged."""
+    import bench
+    from cases import make_paged
+    from hip_attention_b200 import hip_attention_impl, read_status
+    w = dict(bench.WORKLOADS["decode_128k"], keep=[4096, 2048, 1024], **{k_: v_ for k_, v_ in shape.items() if k_ != "keep"})
+    if "keep" in shape:
+        w["keep"] = shape["keep"]
+    w["dtype"] = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}[dtype]
+    w["kind"] = "prefill"          # dense q / k / v tensors from the generator
+    q, k, v = bench.make_qkv(w, "cuda")
+    results = {}
+    for name in ("chunks", "rounds"):
+        monkeypatch.setenv("HIPATTN_DECODE_SCAN", name)
+        dbg = {}
+        read_status("cuda")
+        out, md = hip_attention_impl(q, k, v, bench.make_args(w), debug=dbg)
+        torch.cuda.synchronize()
+        assert read_status("cuda") == 0
+        results[name] = (dbg["stages"], md, out)
+    for i, (a, b_) in enumerate(zip(results["chunks"][0], results["rounds"][0])):
+        for key in ("left", "right", "score", "score_max"):
+            assert torch.equal(a[key], b_[key]), f"stage {i} {key}"
+    assert torch.equal(results["chunks"][1].indices, results["rounds"][1].indices)
+    assert torch.equal(results["chunks"][2], results["rounds"][2])
+    if w["T"] % 16 == 0:
+        monkeypatch.setenv("HIPATTN_DECODE_SCAN", "chunks")
+        kc, vc, table = make_paged(k.cpu(), v.cpu(), 16, 11)
+        args = bench.make_args(w, k_cache=kc.cuda(), v_cache=vc.cuda(), block_table=table.cuda().to(torch.int32),
+                               cache_seq_lens=torch.full((w["B"],), w["T"], dtype=torch.int32, device="cuda"),
+                               extend_context_length=w["T"])
+        out_p, md_p = hip_attention_impl(q, None, None, args)
+        assert torch.equal(md_p.indices, results["rounds"][1].indices)
+        assert torch.equal(out_p, results["rounds"][2])
+
+
 def test_values_may_arrive_after_the_call_is_issued():
     """The estimator reads q and k only: with ``v_ready`` the call is issued before v has been copied in on
     another stream, and gives the result of the plain call."""
