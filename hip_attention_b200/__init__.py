@@ -6,6 +6,8 @@ same call, same argument and metadata types, CUDA kernels behind a C ABI (``incl
 from .metadata import (EnsembleScoreStage, EvalScoreStage, HiPAttentionArgs, HiPAttentionCacheAccessStatistics,
                        HiPAttentionOutputMetadata, HiPAttentionStageInputCache, NopStage, ScanStage, Stage)
 from .operator import PhaseTimer, hip_attention_12, hip_attention_impl, read_status
+from .serving import (HiPAttentionConfig, HiPAttentionPerLayerConfig, HiPMaskRefreshState, HiPMetadataCache,
+                      forward_paged_hip)
 
 # the names the reference exports for this generation of the operator
 HiPAttentionArgs12 = HiPAttentionArgs
@@ -19,4 +21,5 @@ __all__ = [
     "HiPAttentionArgs", "HiPAttentionArgs12", "HiPAttentionOutputMetadata", "HiPAttentionOutputMetadata12",
     "HiPAttentionCacheAccessStatistics", "HiPAttentionCacheAccessStatistics12", "HiPAttentionStageInputCache",
     "Stage", "ScanStage", "ScanStage12", "NopStage", "EvalScoreStage", "EnsembleScoreStage",
+    "HiPAttentionConfig", "HiPAttentionPerLayerConfig", "HiPMaskRefreshState", "HiPMetadataCache", "forward_paged_hip",
 ]

@@ -545,8 +545,12 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
         bsa_bq = min(bsa_bq, _next_pow2(TQ))
         if bq % bsa_bq:
             raise ValueError("block_sparse_block_size_q must divide stage_block_size_q")
-        if args.sliding_window_size == 777:
-            raise NotImplementedError("the sliding_window_size == 777 sentinel of the serving adapter is not built")
+        if sw_attn == 777:
+            # window sentinel of the serving adapter (attention_extend.py:3070-3076): these queries see
+            # everything the model context has room for beside the sink, the selected keys and their own block
+            sw_attn = args.model_context_length - args.sink_token_size - args.second_stage_k - bsa_bq
+            if sw_attn < 0:
+                raise ValueError("the window sentinel 777 needs model_context_length > sink + second_stage_k + query block")
         decode = TQ == 1 and not args.disable_flashdecode and os.environ.get("HIP_DISABLE_FLASHDECODE", "0") != "1"
         if timer: timer.mark("start")
         if v_ready is not None:

@@ -1,0 +1,245 @@
+"""Serving-side boundary of the operator: layer configuration, the per-stage mask refresh schedule, the
+metadata cache a decode loop keeps between steps, and ``forward_paged_hip`` -- the call an inference
+server makes per attention layer with its token-granular KV pool.
+
+Mirrors the reference's adapter (``hip_attn/v1_2/hip_config.py``, ``mask_refresh_interval.py``,
+``hip_memory_pool.py:235-300`` and ``paged_hip.py:327-500``): same class and field names, same JSON
+keys, same schedule, same split of a prefill chunk into a sparse part and its last 64 queries.  Not
+covered: in-kernel RoPE (``using_extend`` must be false), the host-offload cache, and the compressed
+CUDA-graph buffers of the reference's metadata pool (the cache below keeps the tensors as they are).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import InitVar, dataclass, field
+from typing import List, Optional, Union
+
+import torch
+from torch import Tensor
+
+from .metadata import (HiPAttentionArgs, HiPAttentionOutputMetadata, HiPAttentionStageInputCache, ScanStage)
+from .operator import hip_attention_12
+
+
+def _default_stages() -> List[ScanStage]:
+    """Three stages, chunk 256 / 32 / 8, query block 64 (hip_config.py:7-29)."""
+    return [
+        ScanStage(stage_block_size_q=64, stage_block_stride_q=4, stage_chunk_size=256, stage_k=None, stage_stride=1),
+        ScanStage(stage_block_size_q=64, stage_block_stride_q=4, stage_chunk_size=32, stage_k=32768, stage_stride=1),
+        ScanStage(stage_block_size_q=64, stage_block_stride_q=1, stage_chunk_size=8, stage_k=8192, stage_stride=1),
+    ]
+
+
+@dataclass
+class HiPAttentionPerLayerConfig:
+    """Mask-estimator settings of one kind of layer (hip_config.py:32-63)."""
+    second_stage_k: int = 2048
+    sliding_window_size: int = 1024
+    sink_token_size: int = 256
+    sa_extend_backend: str = "streaming"
+    scan_extend_backend: Optional[str] = None
+    stages: List[ScanStage] = field(default_factory=_default_stages)
+
+    parsed_json: InitVar[Optional[dict]] = None
+
+    def __post_init__(self, parsed_json: Optional[dict]):
+        if parsed_json is None:
+            return
+        rest = dict(parsed_json)
+        for key in ("second_stage_k", "sliding_window_size", "sink_token_size", "sa_extend_backend", "scan_extend_backend"):
+            if key in rest:
+                setattr(self, key, rest.pop(key))
+        if "stages" in rest:
+            self.stages = [ScanStage(**stage) for stage in rest.pop("stages")]
+        if rest:
+            raise ValueError(f"Unknown keys in json: {rest.keys()}")
+
+
+def _default_layers() -> List[HiPAttentionPerLayerConfig]:
+    """Entry 0: dense layers (larger k), entry 1: all other layers (hip_config.py:66-81)."""
+    return [
+        HiPAttentionPerLayerConfig(second_stage_k=4096, sa_extend_backend="streaming", scan_extend_backend="streaming"),
+        HiPAttentionPerLayerConfig(second_stage_k=2048, sa_extend_backend="streaming", scan_extend_backend="relative"),
+    ]
+
+
+@dataclass
+class HiPAttentionConfig:
+    """Model-level configuration, optionally from a JSON string or file (hip_config.py:84-180)."""
+    dense_layers: List[int] = field(default_factory=lambda: [0, 1, 2, 3, 31])
+    block_sparse_block_size_q: int = 64
+    metadata_cache_max_batch_size: int = 32
+    mask_refresh_interval: Union[int, List[int]] = field(default_factory=lambda: [32, 16, 8])
+    using_extend: bool = True
+    layers: List[HiPAttentionPerLayerConfig] = field(default_factory=_default_layers)
+    prefill_layers: List[HiPAttentionPerLayerConfig] = field(default_factory=_default_layers)
+
+    # deprecated switches, kept so that existing configuration files load
+    apply_v_dot: bool = False
+    prefill_always_dense: bool = False
+    decode_always_dense: bool = False
+    force_dense: bool = False
+    prefill_dense_threshold: int = 8192
+
+    json_or_path: InitVar[Optional[str]] = None
+
+    def __post_init__(self, json_or_path: Optional[str]):
+        if json_or_path is None:
+            parsed = {}
+        elif json_or_path.startswith("{"):
+            parsed = json.loads(json_or_path)
+        else:
+            with open(json_or_path, "r") as f:
+                parsed = json.load(f)
+        for key in ("apply_v_dot", "dense_layers", "prefill_always_dense", "decode_always_dense", "force_dense",
+                    "prefill_dense_threshold", "block_sparse_block_size_q", "metadata_cache_max_batch_size", "using_extend"):
+            if key in parsed:
+                setattr(self, key, parsed.pop(key))
+        if "mask_refresh_interval" in parsed:
+            if not isinstance(parsed["mask_refresh_interval"], (int, list)):
+                raise AssertionError("mask_refresh_interval must be an int or a list of ints")
+            self.mask_refresh_interval = parsed.pop("mask_refresh_interval")
+        if "layers" in parsed:
+            self.layers = [HiPAttentionPerLayerConfig(parsed_json=layer) for layer in parsed.pop("layers")]
+        if self.prefill_layers is None:
+            self.prefill_layers = self.layers
+        if "prefill_layers" in parsed:
+            self.prefill_layers = [HiPAttentionPerLayerConfig(parsed_json=layer) for layer in parsed.pop("prefill_layers")]
+        if parsed:
+            raise ValueError(f"Unknown keys in json: {parsed.keys()}")
+        num_stages = len(self.layers[0].stages)
+        for layer_config in self.layers:
+            if len(layer_config.stages) != num_stages:
+                raise AssertionError("all layers must have the same number of stages")
+        if isinstance(self.mask_refresh_interval, int):
+            self.mask_refresh_interval = [self.mask_refresh_interval] * num_stages
+
+    def layer_config(self, layer_id: int, is_decode: bool) -> HiPAttentionPerLayerConfig:
+        """Two entries mean (dense layers, other layers); otherwise one entry per layer (paged_hip.py:358-370)."""
+        table = self.layers if is_decode else self.prefill_layers
+        if len(table) == 2:
+            return table[0 if layer_id in self.dense_layers else 1]
+        return table[layer_id]
+
+
+class HiPMaskRefreshState:
+    """Which part of the mask a decode step re-estimates (mask_refresh_interval.py:4-30).
+
+    ``update()`` returns -1 on the first step (estimate everything, nothing cached yet), the index i of the first
+    stage whose interval divides the step counter (stages before i keep their cached inputs, the estimator restarts
+    at stage i; 0 means from scratch), or None (reuse the cached mask)."""
+
+    def __init__(self, hip_config: HiPAttentionConfig):
+        self.hip_config = hip_config
+        self.decode_index = 0
+
+    def update(self) -> Optional[int]:
+        cached_stages = None
+        intervals = self.hip_config.mask_refresh_interval
+        if intervals is not None:
+            for i_stage, interval in enumerate(intervals):
+                if self.decode_index % interval == 0:
+                    cached_stages = i_stage
+                    break
+        if self.decode_index == 0:
+            cached_stages = -1
+        self.decode_index += 1
+        return cached_stages
+
+
+class HiPMetadataCache:
+    """The metadata of the last estimate of one layer and the view of it a step may reuse
+    (the selection rules of hip_memory_pool.py:239-300, without the pool's preallocated compressed buffers)."""
+
+    def __init__(self, n_stages: int):
+        self.n_stages = n_stages
+        self.metadata: Optional[HiPAttentionOutputMetadata] = None
+
+    def set(self, metadata: HiPAttentionOutputMetadata) -> None:
+        self.metadata = metadata
+
+    def get(self, cached_stages: Optional[int]) -> Optional[HiPAttentionOutputMetadata]:
+        md = self.metadata
+        if cached_stages == -1 or md is None:
+            return None
+        if cached_stages is None or cached_stages == self.n_stages:
+            return HiPAttentionOutputMetadata(indices=md.indices, ks=md.ks, ks_count=md.ks_count, ks_start_end=md.ks_start_end,
+                                              mask_cache_statistics=None, sa_cache_statistics=None, stage_caches=None)
+        if cached_stages == 0:
+            return None     # re-estimate from scratch
+        caches = [HiPAttentionStageInputCache(indices_left=None, indices_right=None, out_scores=None)]
+        caches += list(md.stage_caches[1:cached_stages + 1])
+        return HiPAttentionOutputMetadata(indices=None, ks=None, ks_count=None, ks_start_end=None,
+                                          mask_cache_statistics=None, sa_cache_statistics=None, stage_caches=caches)
+
+
+LAST_DENSE = 64   # queries at the end of a prefill chunk that attend a near-full window (paged_hip.py:462)
+
+
+def forward_paged_hip(query: Tensor, sm_scale: float, batch_size: int, k_cache: Optional[Tensor], v_cache: Optional[Tensor],
+                      positions: Tensor, seq_lens: Tensor, req_to_tokens: Tensor, req_pool_indices: Tensor, layer_id: int,
+                      logit_cap: float, orig_context_len: int, max_context_len: int, hip_config: HiPAttentionConfig,
+                      cached_metadata: Optional[HiPAttentionOutputMetadata] = None, k: Optional[Tensor] = None,
+                      v: Optional[Tensor] = None, is_decode: bool = False, query_for_mask: Optional[Tensor] = None,
+                      offload_cache=None, rope_cos: Optional[Tensor] = None, rope_sin: Optional[Tensor] = None):
+    """One attention layer of a serving step (paged_hip.py:35-131, 327-500).
+
+    ``query`` [N, H, D] holds ``batch_size`` requests of N / batch_size tokens each; ``k_cache`` / ``v_cache``
+    [tokens, HKV, D] are the server's token-granular pools (page size 1) and ``req_to_tokens[req_pool_indices]`` the
+    per-request token tables; ``k`` / ``v`` [B, T, HKV, D] may be given instead (padded to ``max_context_len``).
+    Decode steps and short chunks are one operator call.  A prefill chunk of 128 tokens or more is split: all but
+    the last 64 queries run with the layer's window, the last 64 with the window sentinel 777, which the operator
+    turns into (model context - sink - second_stage_k - query block) so that they see nearly everything.
+    Returns (context [B, tokens, H, D], metadata of the last call)."""
+    if offload_cache is not None:
+        raise NotImplementedError("the host-offload cache is not built")
+    if hip_config.using_extend:
+        raise NotImplementedError("in-kernel RoPE (using_extend) is not built: configure using_extend = false")
+    N, num_heads, hidden = query.shape
+    if N % batch_size:
+        raise ValueError(f"{N} query tokens are not a multiple of the batch size {batch_size}")
+    dst_len = N // batch_size
+    if is_decode and dst_len != 1:
+        raise ValueError("a decode step has one query token per request")
+    layer = hip_config.layer_config(layer_id, is_decode)
+    query = query.view(batch_size, dst_len, num_heads, hidden)
+    if query_for_mask is not None:
+        query_for_mask = query_for_mask.view(batch_size, -1, num_heads, hidden)
+    if k is not None and k.shape[1] != max_context_len:
+        pad_k = torch.zeros((k.shape[0], max_context_len, k.shape[2], k.shape[3]), dtype=k.dtype, device=k.device)
+        pad_v = torch.zeros_like(pad_k)
+        pad_k[:, :k.shape[1]] = k
+        pad_v[:, :v.shape[1]] = v
+        k, v = pad_k, pad_v
+    if k_cache is not None:
+        if v_cache.shape != k_cache.shape or k_cache.shape[-1] != hidden:
+            raise ValueError("k_cache and v_cache must be [tokens, kv_heads, head_dim] pools of q's head_dim")
+        k_cache = k_cache.view(k_cache.shape[0], 1, k_cache.shape[1], hidden)
+        v_cache = v_cache.view(v_cache.shape[0], 1, v_cache.shape[1], hidden)
+    block_table = req_to_tokens.index_select(0, req_pool_indices)
+    if block_table.shape[0] != batch_size:
+        raise ValueError("req_pool_indices must name one request per batch entry")
+    head_dim = k_cache.shape[-1] if k_cache is not None else k.shape[-1]
+
+    def make_args(position_ids: Tensor, window: int) -> HiPAttentionArgs:
+        return HiPAttentionArgs(
+            k_cache=k_cache, v_cache=v_cache, block_table=block_table, cache_seq_lens=seq_lens, position_ids=position_ids,
+            block_size_k=32 if head_dim > 128 else 64, sliding_window_size=window, sink_token_size=layer.sink_token_size,
+            using_extend=False, need_apply_rope=False, logit_softcap=logit_cap if logit_cap != 0.0 else None,
+            second_stage_k=layer.second_stage_k, stages=layer.stages, model_context_length=orig_context_len,
+            extend_context_length=max_context_len, block_sparse_block_size_q=hip_config.block_sparse_block_size_q,
+            sa_extend_backend=layer.sa_extend_backend, require_cache_statistics=False, disable_flashdecode=not is_decode,
+            q_mask=(query_for_mask * sm_scale).to(query.dtype) if query_for_mask is not None else None, layer_id=layer_id)
+
+    pos = positions.view(batch_size, dst_len)
+    if is_decode or dst_len < 2 * LAST_DENSE:
+        context, metadata = hip_attention_12((query * sm_scale).to(query.dtype), k, v, args=make_args(pos, layer.sliding_window_size),
+                                             cached_metadata=cached_metadata)
+        return context.to(query.dtype), metadata
+    if query_for_mask is not None:
+        raise ValueError("query_for_mask cannot be combined with the split of a prefill chunk")
+    sparse, _ = hip_attention_12((query[:, :-LAST_DENSE] * sm_scale).to(query.dtype), k, v,
+                                 args=make_args(pos[:, :-LAST_DENSE], layer.sliding_window_size), cached_metadata=cached_metadata)
+    dense, metadata = hip_attention_12((query[:, -LAST_DENSE:] * sm_scale).to(query.dtype), k, v,
+                                       args=make_args(pos[:, -LAST_DENSE:], 777), cached_metadata=cached_metadata)
+    return torch.cat([sparse.to(query.dtype), dense.to(query.dtype)], dim=1), metadata
