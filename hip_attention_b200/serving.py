@@ -156,6 +156,13 @@ class HiPMetadataCache:
         self.metadata: Optional[HiPAttentionOutputMetadata] = None
 
     def set(self, metadata: HiPAttentionOutputMetadata) -> None:
+        """Store the metadata a call returned.  A call on a cached mask returns no stage inputs: the ones already
+        stored stay (the reference's pool keeps one buffer per stage and only overwrites what was recomputed)."""
+        if metadata.stage_caches is None and self.metadata is not None:
+            metadata = HiPAttentionOutputMetadata(
+                indices=metadata.indices, ks=metadata.ks, ks_count=metadata.ks_count, ks_start_end=metadata.ks_start_end,
+                mask_cache_statistics=metadata.mask_cache_statistics, sa_cache_statistics=metadata.sa_cache_statistics,
+                stage_caches=self.metadata.stage_caches)
         self.metadata = metadata
 
     def get(self, cached_stages: Optional[int]) -> Optional[HiPAttentionOutputMetadata]:

@@ -78,6 +78,10 @@ def test_metadata_cache_rules():
     assert part.indices is None and len(part.stage_caches) == 2
     assert part.stage_caches[0].indices_left is None and part.stage_caches[1] is caches[1]
     assert len(c.get(2).stage_caches) == 3
+    # a call on the cached mask returns no stage inputs: the stored ones stay usable
+    c.set(HiPAttentionOutputMetadata(indices=t(7), ks=t(2), ks_count=t(3), ks_start_end=t(4), mask_cache_statistics=None,
+                                     sa_cache_statistics=None, stage_caches=None))
+    assert c.get(None).indices.item() == 7 and c.get(1).stage_caches[1] is caches[1]
 
 
 @pytest.mark.gpu
