@@ -76,7 +76,6 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
   extern __shared__ __align__(16) unsigned char smem[];
   float* qtile = reinterpret_cast<float*>(smem);                         // [HB][D]
   unsigned char* kstage = smem + (size_t)HB * D * sizeof(float);         // [4 warps][32][STRIDE]
-  float* stab = reinterpret_cast<float*>(kstage + (size_t)4 * 32 * STRIDE);   // [4 warps][HB][32]
   __shared__ int s_pmin;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,7 +119,7 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
   const int bc_log2 = 31 - __clz(p.block_chunk);
   unsigned char* wstage = kstage + (size_t)warp * 32 * STRIDE;
   const unsigned char* my_row = wstage + (size_t)lane * STRIDE;
-  float* wtab = stab + warp * HB * 32;
+  float* wtab = reinterpret_cast<float*>(wstage);   // [HB][32] rounded scores: reuses the staging area once every lane has scored its row
   const int grp_base = lane & ~(C - 1);             // first lane of this lane's chunk
   const int cl = lane >> c_log2;                    // chunk of the pass
   int cur_group = -1, cur_gmax = 0;
@@ -180,10 +179,10 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
     cp_async_wait<0>();
     __syncwarp();
     // strict scores of this lane's token for the HB heads
-    if (valid) {
-      float acc[HB];
+    float acc[HB];
 #pragma unroll
-      for (int hh = 0; hh < HB; ++hh) acc[hh] = 0.f;
+    for (int hh = 0; hh < HB; ++hh) acc[hh] = 0.f;
+    if (valid) {
 #pragma unroll 2
       for (int pc = 0; pc < PIECES; ++pc) {
         float kv[VEC];
@@ -200,6 +199,9 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
           }
         }
       }
+    }
+    __syncwarp();     // every lane is done with its staged row: the area now holds the score table
+    if (valid) {
 #pragma unroll
       for (int hh = 0; hh < HB; ++hh) wtab[hh * 32 + lane] = Elem<DT>::round(acc[hh]);
     }
@@ -238,7 +240,7 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
 template <int DT, int D, int HB>
 int launch(const hipattn_scan_params_t& p, int c_log2, cudaStream_t stream) {
   constexpr int EB = Elem<DT>::bytes;
-  const size_t smem = (size_t)HB * D * sizeof(float) + (size_t)4 * 32 * (D * EB + kPadS) + (size_t)4 * HB * 32 * sizeof(float);
+  const size_t smem = (size_t)HB * D * sizeof(float) + (size_t)4 * 32 * (D * EB + kPadS);
   HIPATTN_REQUIRE(smem <= 227 * 1024, HIPATTN_ERR_UNSUPPORTED, "chunk scan stage needs %zu bytes of shared memory", smem);
   const int BDST = cdiv(p.TQ, p.block_size_q);
   const int Gq = p.H / p.HKV;
