@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Default workload (``prefill_128k``, BASELINE config 2): one Llama-3.1-8B-shaped layer, bf16, the last
+Default workload (``prefill_128k``, benchmark configuration 2): one Llama-3.1-8B-shaped layer, bf16, the last
 32768 queries against 131072 keys, 32 / 8 heads, head dim 128, three scan stages
 (chunks 256 / 32 / 8 keeping 32768 / 8192 / 2048 tokens), sink 256, window 1024.  A step is one
 ``hip_attention_12`` call (mask estimation + block-sparse attention).  With N > 1 the KV heads are
@@ -33,19 +33,19 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE.json configs[1]
+    # benchmark configuration 2
     "prefill_128k": dict(kind="prefill", B=1, TQ=32768, T=131072, H=32, HKV=8, D=128, dtype="bf16", theta=5e5,
                          bq=64, chunks=[256, 32, 8], keep=[32768, 8192, 2048], strides=[4, 4, 1], sink=256, sw=1024,
                          heavy=0.01, seed=1235),
-    # BASELINE.json configs[0] (fp32, CPU-runnable)
+    # benchmark configuration 1 (fp32, CPU-runnable)
     "prefill_4k_fp32": dict(kind="prefill", B=1, TQ=4096, T=4096, H=8, HKV=2, D=64, dtype="fp32", theta=1e4,
                             bq=64, chunks=[32, 8], keep=[1024, 512], strides=[4, 1], sink=64, sw=256, heavy=0.0,
                             seed=1234),
-    # BASELINE.json configs[2]: batched decode over a paged cache, mask refreshed every 8 steps
+    # benchmark configuration 3: batched decode over a paged cache, mask refreshed every 8 steps
     "decode_128k": dict(kind="decode", B=32, TQ=1, T=131072, H=32, HKV=8, D=128, dtype="bf16", theta=5e5,
                         bq=64, chunks=[256, 32, 8], keep=[32768, 8192, 2048], strides=[4, 4, 1], sink=256, sw=1024,
                         heavy=0.01, seed=1236, page=64, refresh=8),
-    # BASELINE.json configs[3]: million-token decode in 8 logical sequence shards
+    # benchmark configuration 4: million-token decode in 8 logical sequence shards
     "decode_1m": dict(kind="decode_sharded", B=1, TQ=1, T=1048576, H=32, HKV=8, D=128, dtype="bf16", theta=5e5,
                       bq=64, chunks=[256, 32, 8], keep=[32768, 8192, 512], strides=[4, 4, 1], sink=256, sw=1024,
                       heavy=0.0, seed=1237, page=64, shards=8, needles=64),
@@ -408,7 +408,7 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": (4 + len(w["chunks"]) + 3 * (len(w["chunks"]) - 1)) * a.steps,
             "phases_ms": {k_: round(v_, 4) for k_, v_ in phases.items() if k_ != "start"},
-            # The scan gathers SURVEY-defined "scan bytes" of key rows; in prefill nearly all of them are L2 hits
+            # `algorithmic` counts the key rows the rounds of the scan gather; in prefill nearly all of them are L2 hits
             # (one KV head's keys, 33.5 MB, are swept by all its query blocks), so `achieved` can exceed the HBM
             # copy peak: `traffic` (measured DRAM bytes per launch) is the part that reaches HBM.  The tensor-core
             # side of the same launches is given beside it.

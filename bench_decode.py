@@ -1,4 +1,4 @@
-"""Decode workloads of bench.py (BASELINE configs 3 and 4); selected with ``bench.py --workload decode_128k | decode_1m``.
+"""Decode workloads of bench.py (benchmark configurations 3 and 4); selected with ``bench.py --workload decode_128k | decode_1m``.
 
 ``decode_128k``: 32 sequences of 131072 tokens in a paged cache (page 64, permuted page table); one step
 is one ``hip_attention_12`` call with one query row per sequence; the mask is re-estimated every 8th
@@ -218,7 +218,7 @@ def run(a, w):
                     "d2h_bytes_per_step": qs[0].numel() * 2},
             "gpu_launches": None,
             "phases_ms": {"refresh_step": ph_refresh, "cached_step": ph_cached},
-            # `algorithmic` is the survey's figure: the key rows the reference's rounds fetch.  The stages with small
+            # `algorithmic` counts the key rows the reference's rounds fetch.  The stages with small
             # chunks fetch every chunk once for the heads of a KV head instead (same results, fewer rows): the rows
             # actually requested are `fetched_bytes_per_refresh`, and `fetched_gbs` is the bandwidth they came at.
             "roofline": {"kernel": "scan_stage_kernel + scan_chunks_strict_kernel (refresh steps)", "bound": "hbm",

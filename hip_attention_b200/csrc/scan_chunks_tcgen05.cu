@@ -397,7 +397,7 @@ int dispatch_rows(const hipattn_scan_params_t& p, int c_log2, int HB, cudaStream
 
 // Takes the shapes of the round-based tcgen05 scan when the stage's chunk size is a known power of two
 // between 4 and `HIPATTN_SCAN_CHUNKS_MAX`, or for every such stage with HIPATTN_SCAN_KERNEL=chunks.
-// Off by default (limit 0): on BASELINE config 2 it equals the round-by-round kernel on the last stage
+// Off by default (limit 0): on benchmark configuration 2 it equals the round-by-round kernel on the last stage
 // (chunk 8: 4.42 against 4.37 ms, with a quarter of the key rows gathered) and loses on chunk 32 (6.9
 // against 4.8 ms): a tile is one long dependent chain per CTA and only two CTAs fit beside the pooled
 // queries of four heads.

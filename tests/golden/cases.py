@@ -57,7 +57,7 @@ CASES = {
                          second_k=128, stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=22, softcap=1.5),
     "softcap_decode_fp16": dict(B=2, TQ=1, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128,
                                 second_k=128, stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=23, softcap=1.5),
-    # BASELINE config 1 shape (fp32, 4096 x 4096, 8/2 heads, D 64)
+    # benchmark configuration 1 shape (fp32, 4096 x 4096, 8/2 heads, D 64)
     "config1_fp32": dict(B=1, TQ=4096, T=4096, H=8, HKV=2, D=64, dtype="fp32", sink=64, sw=256,
                          second_k=512, stages=[(64, 4, 32, None), (64, 1, 8, 1024)], seed=101,
                          rope_theta=10000.0, out_row_stride=16),

@@ -63,7 +63,7 @@ def _import_reference(ref_root: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of DeepAuto-AI/hip-attention")
     ap.add_argument("--native-ties", action="store_true", help="keep torch's own order among equal scores")
     ap.add_argument("--out", default=HERE)
     ap.add_argument("cases", nargs="*")

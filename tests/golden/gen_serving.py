@@ -80,7 +80,7 @@ def config_record(cfg):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of DeepAuto-AI/hip-attention")
     ap.add_argument("--out", default=HERE)
     ap.add_argument("--skip-paged", action="store_true")
     a = ap.parse_args()

@@ -85,7 +85,7 @@ def test_scan_stage_outputs(name, dtype):
 
 
 def test_config1_fixture():
-    """BASELINE config 1 (fp32 4096 x 4096, 8/2 heads, D 64) against the recorded reference run."""
+    """benchmark configuration 1 (fp32 4096 x 4096, 8/2 heads, D 64) against the recorded reference run."""
     path = os.path.join(GOLD, "config1_fp32.npz")
     if not os.path.exists(path):
         pytest.skip("fixture not generated")

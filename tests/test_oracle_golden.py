@@ -49,7 +49,7 @@ def test_oracle_matches_reference(name):
 
 
 def test_oracle_matches_reference_config1():
-    """BASELINE config 1 (fp32, 4096 x 4096); the reference took minutes through the interpreter."""
+    """benchmark configuration 1 (fp32, 4096 x 4096); the reference took minutes through the interpreter."""
     if not os.path.exists(os.path.join(GOLD, "config1_fp32.npz")):
         pytest.skip("fixture not generated")
     check_against_golden("config1_fp32")
