@@ -42,16 +42,23 @@ __device__ __forceinline__ KeyList make_key_list(const hipattn_bsa_params_t& p, 
   return kl;
 }
 
+// Index into kl.idx of the selected block that holds entry j, or -1 when j is not a selected entry.
+__device__ __forceinline__ int selected_block_of(const KeyList& kl, int j) {
+  j -= kl.n_sink;
+  if (j < 0 || j >= kl.n_sel) return -1;
+  return kl.block_k_shift >= 0 ? (j >> kl.block_k_shift) : (j / kl.block_k);
+}
+
 // Position of entry j of the virtual list, or -1 when the entry admits no row.  *is_window tells
-// which admission rule applies.
-__device__ __forceinline__ int key_position(const KeyList& kl, int j, bool* is_window) {
+// which admission rule applies.  `start` is kl.idx[selected_block_of(kl, j)] for a selected entry (unused otherwise);
+// callers that fetched it ahead of time pass it in, so that no global load sits in this function.
+__device__ __forceinline__ int key_position_at(const KeyList& kl, int j, long long start, bool* is_window) {
   *is_window = false;
   if (j < 0 || j >= kl.total) return -1;
   if (j < kl.n_sink) return j;
   j -= kl.n_sink;
   if (j < kl.n_sel) {
     const int blk = kl.block_k_shift >= 0 ? (j >> kl.block_k_shift) : (j / kl.block_k);
-    const long long start = kl.idx[blk];
     const long long t = start + (j - blk * kl.block_k);
     if (t < kl.sink || t > kl.pmax || t >= kl.T) return -1;
     return (int)t;
@@ -59,6 +66,11 @@ __device__ __forceinline__ int key_position(const KeyList& kl, int j, bool* is_w
   j -= kl.n_sel;
   *is_window = true;
   return kl.w_start + j;
+}
+
+__device__ __forceinline__ int key_position(const KeyList& kl, int j, bool* is_window) {
+  const int blk = selected_block_of(kl, j);
+  return key_position_at(kl, j, blk >= 0 ? kl.idx[blk] : 0, is_window);
 }
 
 __device__ __forceinline__ bool admits(int p_row, int t, bool is_window, int window) {

@@ -18,6 +18,7 @@
 // more than 2^8, which keeps P within bf16 / fp16 range and makes rescaling rare.
 // Every wait on an mbarrier is bounded; a wait that runs out sets HIPATTN_STATUS_TIMEOUT and the CTA
 // leaves through the normal exit (TMEM freed), so a fault in the pipeline cannot hang the device.
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -42,11 +43,22 @@ __device__ __forceinline__ float exp2_approx(float x) {
   return y;
 }
 
+// Optional cycle accounting of one CTA's roles, printed from the device; compiled in with
+// -DHIPATTN_ATTN_PROFILE for experiments only.
+#ifdef HIPATTN_ATTN_PROFILE
+#define APROF_DECL(n) long long ap_[n] = {}; long long ap_t_ = clock64()
+#define APROF_LAP(k) do { const long long t_ = clock64(); ap_[k] += t_ - ap_t_; ap_t_ = t_; } while (0)
+#else
+#define APROF_DECL(n)
+#define APROF_LAP(k)
+#endif
+
 struct Meta5 {
   int tpos[TK5];
   int twin[TK5];
   long long koff[TK5];
   long long voff[TK5];
+  long long start[TK5];   // warp-specialised kernel: block starts of the tile's selected entries, fetched a tile ahead
   int far_ok[2];
   int win_ok[2];
 };
@@ -534,11 +546,19 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     const int ptid = tid - 160;  // 0..63
     const char* kbase = (const char*)(p.k.cache ? p.k.cache : p.k.dense);
     const char* vbase = (const char*)(p.v.cache ? p.v.cache : p.v.dense);
-    auto make_meta = [&](int tile) {
+    // requests the block start of this thread's entry of `tile` (if it is a selected entry) into the tile's record;
+    // the copy joins the thread's next commit group
+    auto prefetch_start = [&](int tile) {
+      if (tile >= n_tiles) return;
+      const int blk = selected_block_of(kl, tile * TK5 + ptid);
+      if (blk >= 0)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_u32(&meta[tile & 3].start[ptid])), "l"(kl.idx + blk));
+    };
+    auto make_meta = [&](int tile, bool prefetched) {
       Meta5& m = meta[tile & 3];
       bool w;
       const int j = tile * TK5 + ptid;
-      const int t = key_position(kl, j, &w);
+      const int t = prefetched ? key_position_at(kl, j, m.start[ptid], &w) : key_position(kl, j, &w);
       m.tpos[ptid] = t;
       m.twin[ptid] = (t >= 0 && w) ? 1 : 0;
       long long ko = -1, vo = -1;
@@ -570,7 +590,8 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
     };
     auto producer_sync = [&]() { asm volatile("bar.sync 1, 64;\n" ::: "memory"); };
-    for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t);
+    for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t, false);
+    prefetch_start(3);
     producer_sync();
     if (n_tiles > 0) { gather_rows(meta[0].koff, kbase, sK); gather_rows(meta[0].voff, vbase, sV); }
     if (n_tiles > 1) gather_rows(meta[1].koff, kbase, sK + KT_BYTES);
@@ -578,25 +599,40 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     cp_async_wait<0>();
     fence_async_smem();
     __syncthreads();  // B0: Q, K(0), K(1), V(0) are in place
+    APROF_DECL(6);
     for (int it = 0; it < n_tiles; ++it) {
-      if (it + 3 < n_tiles) make_meta(it + 3);
+      // the block starts of tile it + 3 were requested one tile ago and have landed (every tile ends with a wait
+      // for all of this thread's copies); those of tile it + 4 are requested now
+      if (it + 3 < n_tiles) make_meta(it + 3, true);
+      prefetch_start(it + 4);
+      APROF_LAP(0);
       // K(it + 2) goes where K(it) was: wait until S(it) has been computed
       if (it + 2 < n_tiles) {
         mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
+        APROF_LAP(1);
         gather_rows(meta[(it + 2) & 3].koff, kbase, sK + (it & 1) * KT_BYTES);
       }
-      cp_async_commit();
+      cp_async_commit();   // K(it + 2) and the block starts of tile it + 4
+      APROF_LAP(2);
       // V(it + 1) goes where V(it - 1) was: wait until PV(it - 1) has completed
       if (it + 1 < n_tiles) {
         if (it >= 1) mbar_wait(mbar_o, (it - 1) & 1, &s_abort, p.status);
         gather_rows(meta[(it + 1) & 3].voff, vbase, sV + ((it + 1) & 1) * KT_BYTES);
       }
       cp_async_commit();
-      cp_async_wait<1>();   // K(it + 2) and V(it) have landed; V(it + 1) may still be in flight
+      APROF_LAP(3);
+      cp_async_wait<1>();   // K(it + 2), the block starts and V(it) have landed; V(it + 1) may still be in flight
       fence_async_smem();
+      APROF_LAP(4);
       if (__syncthreads_or(s_abort)) break;  // B1(it)
+      APROF_LAP(5);
     }
     cp_async_wait<0>();
+#ifdef HIPATTN_ATTN_PROFILE
+    if (blockIdx.x == gridDim.x / 2 && ptid == 0)
+      printf("producer/tile: meta %lld  waitS %lld  gatherK %lld  waitPV+gatherV %lld  cpwait %lld  barrier %lld (tiles %d)\n",
+             ap_[0] / n_tiles, ap_[1] / n_tiles, ap_[2] / n_tiles, ap_[3] / n_tiles, ap_[4] / n_tiles, ap_[5] / n_tiles, n_tiles);
+#endif
   } else if (warp == 4) {
     // ================================ MMA issuer ================================
     const uint64_t dk = make_desc(0, 16, 1024);
@@ -619,8 +655,10 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       if (n_tiles > 0) issue_s(0);
       if (n_tiles > 1) issue_s(1);
     }
+    APROF_DECL(3);
     for (int it = 0; it < n_tiles; ++it) {
       if (__syncthreads_or(s_abort)) break;  // B1(it): P(it) is in TMEM, V(it) and K(it + 2) have landed
+      APROF_LAP(0);
       if (lane == 0) {
         tc_fence_after();
         const uint32_t tp = tmem + (it & 1) * 64;                        // P(it): 32 columns of packed pairs
@@ -629,10 +667,16 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(tmem_o, tp + kk * 8, dv | (uint64_t)((vb + kk * 128) & 0x3fffu), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(mbar_o);
+        APROF_LAP(1);
         if (it + 2 < n_tiles) issue_s(it + 2);
+        APROF_LAP(2);
       }
       __syncwarp();
     }
+#ifdef HIPATTN_ATTN_PROFILE
+    if (blockIdx.x == gridDim.x / 2 && lane == 0)
+      printf("issuer/tile: barrier %lld  PV issue %lld  S issue %lld\n", ap_[0] / n_tiles, ap_[1] / n_tiles, ap_[2] / n_tiles);
+#endif
   } else {
     // ================================ softmax: thread = row = TMEM lane ================================
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
@@ -640,15 +684,18 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     const float cap = p.logit_softcap;
     float m_ref = -INFINITY, l_run = 0.f;
     __syncthreads();  // B0
+    APROF_DECL(5);
     for (int it = 0; it < n_tiles; ++it) {
       const Meta5& mt = meta[it & 3];
       const uint32_t ts = tmem + (it & 1) * 64 + lane_base;
       mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
       __syncwarp();
       tc_fence_after();
+      APROF_LAP(0);
       float s[TK5];
       tmem_ld32(ts, s);
       tmem_ld32(ts + 32, s + 32);
+      APROF_LAP(1);
       const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
       if (!(full && !(cap > 0.f))) {   // CTA-uniform slow path: soft-cap and / or per-element admission
 #pragma unroll
@@ -695,10 +742,18 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         pk[j >> 1] = __uint_as_float(pack2<DT>(e0, e1));
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      APROF_LAP(2);
       tmem_st32(ts, pk);        // P(it) over the first half of S(it)
       tc_fence_before();
+      APROF_LAP(3);
       if (__syncthreads_or(s_abort)) break;  // B1(it)
+      APROF_LAP(4);
     }
+#ifdef HIPATTN_ATTN_PROFILE
+    if (blockIdx.x == gridDim.x / 2 && tid == 0)
+      printf("softmax/tile: waitS %lld  ld %lld  max+exp+pack %lld  st %lld  barrier %lld\n", ap_[0] / n_tiles, ap_[1] / n_tiles,
+             ap_[2] / n_tiles, ap_[3] / n_tiles, ap_[4] / n_tiles);
+#endif
     // ---- epilogue for this thread's row ----
     bool ok = n_tiles > 0;
     if (ok) {
