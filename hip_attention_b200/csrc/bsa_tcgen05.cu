@@ -541,41 +541,43 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   const uint32_t idesc_o = make_idesc(FMT, 128, D5, 1);
   const uint32_t tmem_o = tmem + 128;
 
+  const char* kbase = (const char*)(p.k.cache ? p.k.cache : p.k.dense);
+  const char* vbase = (const char*)(p.v.cache ? p.v.cache : p.v.dense);
+  // requests the block start of entry e of `tile` (if it is a selected entry) into the tile's record; the copy joins
+  // the calling thread's next commit group and must be consumed by the same thread
+  auto prefetch_start = [&](int tile, int e) {
+    if (tile >= n_tiles) return;
+    const int blk = selected_block_of(kl, tile * TK5 + e);
+    if (blk >= 0)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_u32(&meta[tile & 3].start[e])), "l"(kl.idx + blk));
+  };
+  // position, addresses and admission summary of entry e of `tile`; all 32 lanes of a warp call it with e = 32 h + lane
+  auto make_meta = [&](int tile, int e, bool prefetched) {
+    Meta5& m = meta[tile & 3];
+    bool w;
+    const int j = tile * TK5 + e;
+    const int t = prefetched ? key_position_at(kl, j, m.start[e], &w) : key_position(kl, j, &w);
+    m.tpos[e] = t;
+    m.twin[e] = (t >= 0 && w) ? 1 : 0;
+    long long ko = -1, vo = -1;
+    if (t >= 0) {
+      ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
+      vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
+    }
+    m.koff[e] = ko;
+    m.voff[e] = vo;
+    const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
+    const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
+    const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
+    if (lane == 0) {
+      m.far_ok[e >> 5] = f;
+      m.win_ok[e >> 5] = g;
+    }
+  };
+
   if (warp >= 5) {
     // ================================ producers: addresses + gathers ================================
     const int ptid = tid - 160;  // 0..63
-    const char* kbase = (const char*)(p.k.cache ? p.k.cache : p.k.dense);
-    const char* vbase = (const char*)(p.v.cache ? p.v.cache : p.v.dense);
-    // requests the block start of this thread's entry of `tile` (if it is a selected entry) into the tile's record;
-    // the copy joins the thread's next commit group
-    auto prefetch_start = [&](int tile) {
-      if (tile >= n_tiles) return;
-      const int blk = selected_block_of(kl, tile * TK5 + ptid);
-      if (blk >= 0)
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_u32(&meta[tile & 3].start[ptid])), "l"(kl.idx + blk));
-    };
-    auto make_meta = [&](int tile, bool prefetched) {
-      Meta5& m = meta[tile & 3];
-      bool w;
-      const int j = tile * TK5 + ptid;
-      const int t = prefetched ? key_position_at(kl, j, m.start[ptid], &w) : key_position(kl, j, &w);
-      m.tpos[ptid] = t;
-      m.twin[ptid] = (t >= 0 && w) ? 1 : 0;
-      long long ko = -1, vo = -1;
-      if (t >= 0) {
-        ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
-        vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
-      }
-      m.koff[ptid] = ko;
-      m.voff[ptid] = vo;
-      const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
-      const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
-      const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
-      if (lane == 0) {
-        m.far_ok[ptid >> 5] = f;
-        m.win_ok[ptid >> 5] = g;
-      }
-    };
     // thread ptid copies piece ptid & 15 of rows (ptid >> 4) + 4 i
     const int g_pc = ptid & 15, g_r0 = ptid >> 4;
     auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst) {
@@ -590,8 +592,7 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
     };
     auto producer_sync = [&]() { asm volatile("bar.sync 1, 64;\n" ::: "memory"); };
-    for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t, false);
-    prefetch_start(3);
+    for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t, ptid, false);
     producer_sync();
     if (n_tiles > 0) { gather_rows(meta[0].koff, kbase, sK); gather_rows(meta[0].voff, vbase, sV); }
     if (n_tiles > 1) gather_rows(meta[1].koff, kbase, sK + KT_BYTES);
@@ -601,10 +602,6 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     __syncthreads();  // B0: Q, K(0), K(1), V(0) are in place
     APROF_DECL(6);
     for (int it = 0; it < n_tiles; ++it) {
-      // the block starts of tile it + 3 were requested one tile ago and have landed (every tile ends with a wait
-      // for all of this thread's copies); those of tile it + 4 are requested now
-      if (it + 3 < n_tiles) make_meta(it + 3, true);
-      prefetch_start(it + 4);
       APROF_LAP(0);
       // K(it + 2) goes where K(it) was: wait until S(it) has been computed
       if (it + 2 < n_tiles) {
@@ -612,7 +609,7 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         APROF_LAP(1);
         gather_rows(meta[(it + 2) & 3].koff, kbase, sK + (it & 1) * KT_BYTES);
       }
-      cp_async_commit();   // K(it + 2) and the block starts of tile it + 4
+      cp_async_commit();
       APROF_LAP(2);
       // V(it + 1) goes where V(it - 1) was: wait until PV(it - 1) has completed
       if (it + 1 < n_tiles) {
@@ -621,7 +618,7 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
       cp_async_commit();
       APROF_LAP(3);
-      cp_async_wait<1>();   // K(it + 2), the block starts and V(it) have landed; V(it + 1) may still be in flight
+      cp_async_wait<1>();   // K(it + 2) and V(it) have landed; V(it + 1) may still be in flight
       fence_async_smem();
       APROF_LAP(4);
       if (__syncthreads_or(s_abort)) break;  // B1(it)
@@ -649,6 +646,12 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
       umma_commit(mbar_s0 + 8 * (tile & 1));
     };
+    // This warp is idle most of a tile (one lane issues a dozen MMAs): its lanes also resolve the key positions and
+    // addresses of tile it + 3, two entries per lane, with the block starts fetched one tile ahead.
+    prefetch_start(3, lane);
+    prefetch_start(3, lane + 32);
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();  // B0
     if (lane == 0) {
       tc_fence_after();
@@ -657,6 +660,14 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     }
     APROF_DECL(3);
     for (int it = 0; it < n_tiles; ++it) {
+      if (it + 3 < n_tiles) {
+        make_meta(it + 3, lane, true);
+        make_meta(it + 3, lane + 32, true);
+      }
+      prefetch_start(it + 4, lane);
+      prefetch_start(it + 4, lane + 32);
+      cp_async_commit();
+      cp_async_wait<0>();     // the block starts of tile it + 4 are in place before the barrier
       if (__syncthreads_or(s_abort)) break;  // B1(it): P(it) is in TMEM, V(it) and K(it + 2) have landed
       APROF_LAP(0);
       if (lane == 0) {
