@@ -7,7 +7,7 @@ from .metadata import (EnsembleScoreStage, EvalScoreStage, HiPAttentionArgs, HiP
                        HiPAttentionOutputMetadata, HiPAttentionStageInputCache, NopStage, ScanStage, Stage)
 from .operator import PhaseTimer, hip_attention_12, hip_attention_impl, read_status
 from .serving import (HiPAttentionConfig, HiPAttentionPerLayerConfig, HiPMaskRefreshState, HiPMetadataCache,
-                      forward_paged_hip)
+                      HiPMetadataCachePool, forward_paged_hip)
 
 # the names the reference exports for this generation of the operator
 HiPAttentionArgs12 = HiPAttentionArgs
@@ -21,5 +21,6 @@ __all__ = [
     "HiPAttentionArgs", "HiPAttentionArgs12", "HiPAttentionOutputMetadata", "HiPAttentionOutputMetadata12",
     "HiPAttentionCacheAccessStatistics", "HiPAttentionCacheAccessStatistics12", "HiPAttentionStageInputCache",
     "Stage", "ScanStage", "ScanStage12", "NopStage", "EvalScoreStage", "EnsembleScoreStage",
-    "HiPAttentionConfig", "HiPAttentionPerLayerConfig", "HiPMaskRefreshState", "HiPMetadataCache", "forward_paged_hip",
+    "HiPAttentionConfig", "HiPAttentionPerLayerConfig", "HiPMaskRefreshState", "HiPMetadataCache", "HiPMetadataCachePool",
+    "forward_paged_hip",
 ]

@@ -1,18 +1,18 @@
 """Serving-side boundary of the operator: layer configuration, the per-stage mask refresh schedule, the
-metadata cache a decode loop keeps between steps, and ``forward_paged_hip`` -- the call an inference
-server makes per attention layer with its token-granular KV pool.
+metadata a decode loop keeps between steps (as plain tensors, or in the preallocated compressed buffers
+of ``HiPMetadataCachePool``), and ``forward_paged_hip`` -- the call an inference server makes per attention
+layer with its token-granular KV pool.
 
 Mirrors the reference's adapter (``hip_attn/v1_2/hip_config.py``, ``mask_refresh_interval.py``,
-``hip_memory_pool.py:235-300`` and ``paged_hip.py:327-500``): same class and field names, same JSON
-keys, same schedule, same split of a prefill chunk into a sparse part and its last 64 queries.  Not
-covered: in-kernel RoPE (``using_extend`` must be false), the host-offload cache, and the compressed
-CUDA-graph buffers of the reference's metadata pool (the cache below keeps the tensors as they are).
+``hip_memory_pool.py`` and ``paged_hip.py:327-500``): same class and field names, same JSON keys, same
+schedule, same split of a prefill chunk into a sparse part and its last 64 queries.  Not covered:
+in-kernel RoPE (``using_extend`` must be false) and the host-offload cache.
 """
 from __future__ import annotations
 
 import json
 from dataclasses import InitVar, dataclass, field
-from typing import List, Optional, Union
+from typing import Dict, List, Optional, Sequence, Union
 
 import torch
 from torch import Tensor
@@ -178,6 +178,148 @@ class HiPMetadataCache:
         caches += list(md.stage_caches[1:cached_stages + 1])
         return HiPAttentionOutputMetadata(indices=None, ks=None, ks_count=None, ks_start_end=None,
                                           mask_cache_statistics=None, sa_cache_statistics=None, stage_caches=caches)
+
+
+class _PoolBuffer:
+    """One preallocated buffer of the metadata pool (hip_memory_pool.py:20-53): ``per_head`` buffers are
+    [max_batch * heads, ...] and sliced by batch * heads rows, the others are [max_batch, 1, heads, ...]; values are
+    stored in ``store`` and handed back as fresh tensors of ``dtype``."""
+
+    def __init__(self, max_batch: int, heads: int, tail: Sequence[int], dtype: torch.dtype, per_head: bool, store: Optional[torch.dtype],
+                 device) -> None:
+        lead = (max_batch * heads,) if per_head else (max_batch, 1, heads)
+        self.buffer = torch.zeros((*lead, *tail), dtype=store or dtype, device=device)
+        self.dtype, self.per_head = dtype, per_head
+
+    def _check(self, rows: int, what: str) -> None:
+        if self.buffer.shape[0] < rows:
+            raise ValueError(f"the metadata pool holds {self.buffer.shape[0]} rows, {what} needs {rows}: lower the CUDA-graph batch size or "
+                             'raise "metadata_cache_max_batch_size" in the attention configuration')
+
+    def get(self, batch_size: int, heads: int) -> Tensor:
+        # (the reference compares the batch size with the row count even where rows are batch x head, and then hands
+        # back a silently truncated slice; here a batch beyond the configured maximum is an error in both layouts)
+        self._check(batch_size * heads if self.per_head else batch_size, "the requested batch")
+        view = self.buffer[:batch_size * heads] if self.per_head else self.buffer[:batch_size, :, :heads]
+        return view.to(self.dtype, copy=True)
+
+    def set(self, value: Tensor) -> None:
+        self._check(value.shape[0], "the stored value")
+        dst = self.buffer[:value.shape[0]] if self.per_head else self.buffer[:value.shape[0], :, :value.shape[2]]
+        dst.copy_(value.to(self.buffer.dtype))
+
+
+class HiPMetadataCachePool:
+    """Preallocated per-layer buffers that carry the mask and the stage inputs of decode steps from one step to the
+    next at fixed addresses, so that a captured CUDA graph can replay them (hip_memory_pool.py:55-433).
+
+    Block indices and chunk bounds are stored as uint32 and the stage scores as bfloat16, as the reference stores
+    them: a mask that went through the pool has its INT64_MAX padding replaced by 2^32 - 1 (still beyond every
+    token, and ``ks`` bounds the entries that count), and an estimator restart sees scores rounded to bfloat16.
+    ``set_hip_metadata_cache`` / ``get_hip_metadata_cache`` take the same arguments as the reference's.  The
+    research switches that enlarge or delay the buffers (HIP_DEBUG_UNION_HEAD, HIP_DIAG_INFO,
+    HIP_DEBUG_ADD_DELAY_WINDOW, HIP_DEBUG_DELAYED_STAGE0) are not built."""
+
+    _COUNTERS = ("access_count", "unique_access_count", "cache_miss_count")
+
+    def __init__(self, max_total_num_tokens: int, query_head_num: int, layer_num: int, context_length: int, device,
+                 hip_config: HiPAttentionConfig) -> None:
+        self.hip_config, self.layer_num, self.head_num, self.device = hip_config, layer_num, query_head_num, device
+        self.max_batch_size = hip_config.metadata_cache_max_batch_size
+        self.layer_configs = {i: hip_config.layer_config(i, is_decode=True) for i in range(layer_num)}
+        self.cache: List[Dict[str, _PoolBuffer]] = []
+        for i in range(layer_num):
+            layer = self.layer_configs[i]
+
+            def buf(tail, dtype, per_head=True, store=None):
+                return _PoolBuffer(self.max_batch_size, self.head_num, tail, dtype, per_head, store, device)
+
+            n_blocks = -(-layer.second_stage_k // layer.stages[-1].stage_chunk_size)
+            bufs = {"indices": buf([1, n_blocks], torch.int64, store=torch.uint32), "ks": buf([1], torch.int64),
+                    "ks_count": buf([1, 1], torch.int64), "ks_start_end": buf([1, 2], torch.int64)}
+            for prefix in ("mask", "sa"):
+                for c in self._COUNTERS:
+                    bufs[f"{prefix}_{c}"] = buf([1], torch.int64)
+            reach = context_length - layer.sliding_window_size - layer.sink_token_size
+            for i_stage, stage in enumerate(layer.stages):
+                if i_stage == 0:
+                    continue
+                n = min(stage.stage_k, reach) // stage.stage_chunk_size
+                bufs[f"stage_{i_stage}_indices_left"] = buf([n], torch.int64, per_head=False, store=torch.uint32)
+                bufs[f"stage_{i_stage}_indices_right"] = buf([n], torch.int64, per_head=False, store=torch.uint32)
+                bufs[f"stage_{i_stage}_out_scores"] = buf([n], torch.float32, per_head=False, store=torch.bfloat16)
+            self.cache.append(bufs)
+        self.allocated_gpu_bytes = self.compute_allocated_bytes()
+
+    def reset_decode_phase(self) -> None:
+        """Called by the server when a decode phase starts; only the delayed-stage research mode keeps state there."""
+
+    def compute_allocated_bytes(self) -> int:
+        return sum(b.buffer.numel() * b.buffer.element_size() for layer in self.cache for b in layer.values())
+
+    def _buffer(self, layer_idx: int, name: str) -> _PoolBuffer:
+        if layer_idx not in range(len(self.cache)):
+            raise IndexError(f"layer {layer_idx} is not in range({len(self.cache)})")
+        if name not in self.cache[layer_idx]:
+            raise KeyError(f"{name} is not one of {sorted(self.cache[layer_idx])}")
+        return self.cache[layer_idx][name]
+
+    def get_buffer(self, layer_idx: int, name: str, batch_size: int) -> Tensor:
+        return self._buffer(layer_idx, name).get(batch_size, self.head_num)
+
+    def set_buffer(self, layer_idx: int, name: str, value: Tensor) -> None:
+        self._buffer(layer_idx, name).set(value)
+
+    def get_hip_metadata_cache(self, layer_id: int, size: int, batch_size: int,
+                               cached_stages: Optional[int]) -> Optional[HiPAttentionOutputMetadata]:
+        """What a step may reuse: the mask (``cached_stages`` None or the number of stages), nothing (0, or -1 for the
+        first step), or the inputs of stages 1 .. cached_stages, from which the estimator restarts."""
+        if size != batch_size:
+            raise ValueError("the pool serves decode steps: one query token per request")
+        n_stages = len(self.layer_configs[layer_id].stages)
+        if cached_stages is None or cached_stages == n_stages:
+            return HiPAttentionOutputMetadata(
+                indices=self.get_buffer(layer_id, "indices", batch_size), ks=self.get_buffer(layer_id, "ks", batch_size),
+                ks_count=self.get_buffer(layer_id, "ks_count", batch_size), ks_start_end=self.get_buffer(layer_id, "ks_start_end", batch_size),
+                mask_cache_statistics=None, sa_cache_statistics=None, stage_caches=None)
+        if cached_stages <= 0:
+            return None
+        caches = [HiPAttentionStageInputCache(indices_left=None, indices_right=None, out_scores=None)]
+        for i_stage in range(1, cached_stages + 1):
+            caches.append(HiPAttentionStageInputCache(
+                indices_left=self.get_buffer(layer_id, f"stage_{i_stage}_indices_left", batch_size),
+                indices_right=self.get_buffer(layer_id, f"stage_{i_stage}_indices_right", batch_size),
+                out_scores=self.get_buffer(layer_id, f"stage_{i_stage}_out_scores", batch_size)))
+        return HiPAttentionOutputMetadata(indices=None, ks=None, ks_count=None, ks_start_end=None, mask_cache_statistics=None,
+                                          sa_cache_statistics=None, stage_caches=caches)
+
+    def set_hip_metadata_cache(self, layer_id: int, size: int, batch_size: int, metadata: HiPAttentionOutputMetadata) -> None:
+        """Store what a step returned.  Stage inputs are only overwritten when the step recomputed them."""
+        if size != batch_size:
+            raise ValueError("the pool serves decode steps: one query token per request")
+        for name in ("indices", "ks", "ks_count", "ks_start_end"):
+            self.set_buffer(layer_id, name, getattr(metadata, name))
+        for prefix, stats in (("sa", metadata.sa_cache_statistics), ("mask", metadata.mask_cache_statistics)):
+            counts = stats.compute_statistics() if stats is not None else {}
+            for c in self._COUNTERS:
+                v = counts.get(c)
+                v = torch.zeros((1,), dtype=torch.int64, device=self.device) if v is None else v
+                self.set_buffer(layer_id, f"{prefix}_{c}", v.view(1, 1).expand(self.max_batch_size, 1))
+        for i_stage, cache in enumerate(metadata.stage_caches or []):
+            if i_stage == 0:
+                continue
+            self.set_buffer(layer_id, f"stage_{i_stage}_indices_left", cache.indices_left)
+            self.set_buffer(layer_id, f"stage_{i_stage}_indices_right", cache.indices_right)
+            self.set_buffer(layer_id, f"stage_{i_stage}_out_scores", cache.out_scores)
+
+    def compute_cache_statistics(self, batch_size: int) -> dict:
+        """Access / miss totals over all layers and the hit ratio (0 / 0 when the steps gathered no statistics)."""
+        result = {}
+        for prefix in ("sa", "mask"):
+            access = sum(self.get_buffer(i, f"{prefix}_access_count", batch_size).sum() for i in range(self.layer_num))
+            miss = sum(self.get_buffer(i, f"{prefix}_cache_miss_count", batch_size).sum() for i in range(self.layer_num))
+            result.update({f"{prefix}_access": access, f"{prefix}_miss": miss, f"{prefix}_hit_ratio": 1 - (miss / access)})
+        return result
 
 
 LAST_DENSE = 64   # queries at the end of a prefill chunk that attend a near-full window (paged_hip.py:462)

@@ -8,7 +8,9 @@ Writes ``serving_config.json`` (parsed configurations and mask-refresh schedules
 ``hip_attn/v1_2/hip_config.py`` and ``mask_refresh_interval.py``) and ``serving_paged.npz`` (outputs of
 ``hip_attn/v1_2/paged_hip.py::forward_paged_hip`` on a small token-granular KV pool: a prefill chunk long enough
 to be split into a sparse part and its last 64 queries, a decode step that estimates everything, one that restarts
-at stage 1 from the cached stage inputs and one that reuses the cached mask).  The reference runs on the CPU
+at stage 1 from the cached stage inputs and one that reuses the cached mask) and ``serving_pool.npz`` (the metadata
+of the first decode step stored into and read back from ``hip_memory_pool.py::HiPMetadataCachePool``, and two decode
+steps fed from the pool's compressed buffers).  The reference runs on the CPU
 through ``TRITON_INTERPRET=1`` with the same shims and tie rule as ``gen_golden.py``.
 """
 from __future__ import annotations
@@ -163,6 +165,39 @@ def main():
     save["decode2_out"] = out2.float().numpy()
     np.savez_compressed(os.path.join(a.out, "serving_paged.npz"), **save)
     print("wrote serving_paged.npz")
+
+    # ---- the metadata pool: store the first decode step, read it back in the three ways a step can ask for it ----
+    pm = importlib.import_module("hip_attn.v1_2.hip_memory_pool")
+    pool = pm.HiPMetadataCachePool(max_total_num_tokens=T + 77, query_head_num=c["H"], layer_num=c["layer_id"] + 1, context_length=T,
+                                   device="cpu", hip_config=cfg)
+    ps = {"allocated_bytes": np.int64(pool.compute_allocated_bytes())}
+    ps["in_indices"], ps["in_ks"], ps["in_ks_count"], ps["in_ks_start_end"] = (md0.indices.numpy(), md0.ks.numpy(), md0.ks_count.numpy(),
+                                                                               md0.ks_start_end.numpy())
+    ps["in_stage1_left"], ps["in_stage1_right"], ps["in_stage1_scores"] = (md0.stage_caches[1].indices_left.numpy(),
+                                                                           md0.stage_caches[1].indices_right.numpy(),
+                                                                           md0.stage_caches[1].out_scores.float().numpy())
+    pool.set_hip_metadata_cache(c["layer_id"], 1, 1, md0)
+    got = pool.get_hip_metadata_cache(c["layer_id"], 1, 1, None)
+    ps["mask_indices"], ps["mask_ks"], ps["mask_ks_count"], ps["mask_ks_start_end"] = (got.indices.numpy(), got.ks.numpy(), got.ks_count.numpy(),
+                                                                                       got.ks_start_end.numpy())
+    assert pool.get_hip_metadata_cache(c["layer_id"], 1, 1, 0) is None
+    got1 = pool.get_hip_metadata_cache(c["layer_id"], 1, 1, 1)
+    assert got1.indices is None and len(got1.stage_caches) == 2 and got1.stage_caches[0].indices_left is None
+    ps["stage1_left"], ps["stage1_right"], ps["stage1_scores"] = (got1.stage_caches[1].indices_left.numpy(), got1.stage_caches[1].indices_right.numpy(),
+                                                                  got1.stage_caches[1].out_scores.numpy())
+    # decode step 1 restarted from the pool's stage inputs (scores rounded to bfloat16), then step 2 on the pooled mask
+    outp1, mdp1 = call(x["q_decode"][1], torch.tensor([T - 2], dtype=torch.int64), T - 1, True, got1)
+    ps["decode1_out"], ps["decode1_indices"], ps["decode1_ks"] = outp1.float().numpy(), mdp1.indices.numpy(), mdp1.ks.numpy()
+    pool.set_hip_metadata_cache(c["layer_id"], 1, 1, mdp1)
+    outp2, _ = call(x["q_decode"][2], torch.tensor([T - 1], dtype=torch.int64), T, True, pool.get_hip_metadata_cache(c["layer_id"], 1, 1, None))
+    ps["decode2_out"] = outp2.float().numpy()
+    try:
+        pool.get_buffer(c["layer_id"], "ks", cfg.metadata_cache_max_batch_size + 1)
+        ps["too_large"] = np.array("none")
+    except Exception as e:      # noqa: BLE001 - the exception type is what is recorded
+        ps["too_large"] = np.array(type(e).__name__)
+    np.savez_compressed(os.path.join(a.out, "serving_pool.npz"), **ps)
+    print("wrote serving_pool.npz")
 
 
 if __name__ == "__main__":

@@ -117,3 +117,112 @@ def test_forward_paged_hip_matches_the_reference():
     assert np.abs(out1.float().cpu().numpy() - g["decode1_out"]).max() < tol
     out2, _ = call(x["q_decode"][2], torch.tensor([T - 1]), T, True, cache.get(None))
     assert np.abs(out2.float().cpu().numpy() - g["decode2_out"]).max() < tol
+
+
+def _pool(device):
+    from hip_attention_b200 import HiPAttentionConfig, HiPMetadataCachePool
+    c = G.PAGED
+    cfg = HiPAttentionConfig(json_or_path=G.CONFIG_JSONS["custom_layers"])
+    return HiPMetadataCachePool(max_total_num_tokens=c["T"] + 77, query_head_num=c["H"], layer_num=c["layer_id"] + 1,
+                                context_length=c["T"], device=device, hip_config=cfg), cfg
+
+
+def test_metadata_pool_stores_and_returns_like_the_reference():
+    """The metadata of a decode step goes into the preallocated buffers and comes back as the reference's pool
+    returns it: block indices through uint32 (the INT64_MAX padding becomes 2^32 - 1), stage scores through
+    bfloat16, fresh tensors on every read, the same buffer sizes."""
+    from hip_attention_b200 import HiPAttentionOutputMetadata, HiPAttentionStageInputCache
+    g = np.load(os.path.join(GOLD, "serving_pool.npz"))
+    pool, cfg = _pool("cpu")
+    lid = G.PAGED["layer_id"]
+    assert pool.compute_allocated_bytes() == int(g["allocated_bytes"]) == pool.allocated_gpu_bytes
+    t = torch.from_numpy
+    md = HiPAttentionOutputMetadata(
+        indices=t(g["in_indices"]), ks=t(g["in_ks"]), ks_count=t(g["in_ks_count"]), ks_start_end=t(g["in_ks_start_end"]),
+        mask_cache_statistics=None, sa_cache_statistics=None,
+        stage_caches=[HiPAttentionStageInputCache(None, None, None),
+                      HiPAttentionStageInputCache(t(g["in_stage1_left"]), t(g["in_stage1_right"]), t(g["in_stage1_scores"]))])
+    assert pool.get_hip_metadata_cache(lid, 1, 1, -1) is None
+    pool.set_hip_metadata_cache(lid, 1, 1, md)
+    for cached in (None, 2):
+        got = pool.get_hip_metadata_cache(lid, 1, 1, cached)
+        assert got.stage_caches is None
+        for name in ("indices", "ks", "ks_count", "ks_start_end"):
+            v = getattr(got, name)
+            assert v.dtype == torch.int64 and np.array_equal(v.numpy(), g["mask_" + name]), name
+    # padding entries (INT64_MAX) come back as 2^32 - 1
+    padded = md.indices.clone()
+    padded[:, :, -3:] = torch.iinfo(torch.int64).max
+    pool.set_buffer(lid, "indices", padded)
+    back = pool.get_buffer(lid, "indices", 1)
+    assert torch.equal(back[:, :, :-3], padded[:, :, :-3]) and bool((back[:, :, -3:] == 2 ** 32 - 1).all())
+    pool.set_buffer(lid, "indices", md.indices)
+    assert pool.get_hip_metadata_cache(lid, 1, 1, 0) is None
+    part = pool.get_hip_metadata_cache(lid, 1, 1, 1)
+    assert part.indices is None and part.ks is None and len(part.stage_caches) == 2 and part.stage_caches[0].indices_left is None
+    s1 = part.stage_caches[1]
+    assert np.array_equal(s1.indices_left.numpy(), g["stage1_left"]) and np.array_equal(s1.indices_right.numpy(), g["stage1_right"])
+    assert s1.out_scores.dtype == torch.float32 and np.array_equal(s1.out_scores.numpy(), g["stage1_scores"])
+    # reads are copies: writing into one does not change the pool
+    s1.out_scores.zero_()
+    assert np.array_equal(pool.get_hip_metadata_cache(lid, 1, 1, 1).stage_caches[1].out_scores.numpy(), g["stage1_scores"])
+    # a step on the cached mask returns no stage inputs: the stored ones stay
+    pool.set_hip_metadata_cache(lid, 1, 1, HiPAttentionOutputMetadata(md.indices, md.ks, md.ks_count, md.ks_start_end, None, None, None))
+    assert np.array_equal(pool.get_hip_metadata_cache(lid, 1, 1, 1).stage_caches[1].indices_left.numpy(), g["stage1_left"])
+
+
+def test_metadata_pool_limits_and_errors():
+    pool, cfg = _pool("cpu")
+    lid = G.PAGED["layer_id"]
+    g = np.load(os.path.join(GOLD, "serving_pool.npz"))
+    # the reference returns a truncated slice for a per-head buffer read beyond the configured batch (recorded as
+    # "none"); the pool here refuses it, as both do for the per-batch buffers
+    assert str(g["too_large"]) == "none"
+    with pytest.raises(ValueError):
+        pool.get_buffer(lid, "ks", cfg.metadata_cache_max_batch_size + 1)
+    with pytest.raises(ValueError):
+        pool.get_buffer(lid, "stage_1_out_scores", cfg.metadata_cache_max_batch_size + 1)
+    assert pool.get_buffer(lid, "ks", cfg.metadata_cache_max_batch_size).shape[0] == cfg.metadata_cache_max_batch_size * G.PAGED["H"]
+    with pytest.raises(ValueError):
+        pool.set_buffer(lid, "ks", torch.zeros((cfg.metadata_cache_max_batch_size * G.PAGED["H"] + 1, 1), dtype=torch.int64))
+    with pytest.raises(KeyError):
+        pool.get_buffer(lid, "stage_0_indices_left", 1)
+    with pytest.raises(IndexError):
+        pool.get_buffer(lid + 1, "ks", 1)
+    with pytest.raises(ValueError):
+        pool.get_hip_metadata_cache(lid, 2, 1, None)
+    # dense layers size their buffers from their own configuration (entry 0 of a two-entry layer table)
+    assert pool.cache[0]["indices"].buffer.shape[-1] == 256 // 8 and pool.cache[lid]["indices"].buffer.shape[-1] == 128 // 8
+    stats = pool.compute_cache_statistics(1)
+    assert int(stats["sa_access"]) == 0 and int(stats["mask_miss"]) == 0
+    pool.reset_decode_phase()
+
+
+@pytest.mark.gpu
+def test_decode_steps_through_the_metadata_pool_match_the_reference():
+    """Decode steps whose cached metadata travels through the pool's compressed buffers: the restart at stage 1 sees
+    bfloat16-rounded scores and uint32 bounds, the step after it reads the pooled mask; masks identical to the
+    reference run through its own pool, outputs within fp16 tolerance."""
+    from hip_attention_b200 import forward_paged_hip
+    g = np.load(os.path.join(GOLD, "serving_pool.npz"))
+    c = G.PAGED
+    x = {k_: v_.cuda() for k_, v_ in G.paged_inputs().items()}
+    pool, cfg = _pool("cuda")
+    T, lid = c["T"], c["layer_id"]
+
+    def call(q, position, seq_len, cached):
+        return forward_paged_hip(q, c["sm_scale"], 1, x["k_pool"], x["v_pool"], torch.tensor([position], device="cuda"),
+                                 torch.tensor([seq_len], device="cuda"), x["req_to_tokens"], x["req_pool_indices"], lid, 0.0,
+                                 c["model_context"], T, cfg, cached_metadata=cached, is_decode=True)
+
+    tol = 3e-3
+    out0, md0 = call(x["q_decode"][0], T - 3, T - 2, pool.get_hip_metadata_cache(lid, 1, 1, -1))
+    pool.set_hip_metadata_cache(lid, 1, 1, md0)
+    assert np.array_equal(pool.get_hip_metadata_cache(lid, 1, 1, None).indices.cpu().numpy(), g["mask_indices"])
+    assert np.array_equal(pool.get_hip_metadata_cache(lid, 1, 1, 1).stage_caches[1].out_scores.cpu().numpy(), g["stage1_scores"])
+    out1, md1 = call(x["q_decode"][1], T - 2, T - 1, pool.get_hip_metadata_cache(lid, 1, 1, 1))
+    pool.set_hip_metadata_cache(lid, 1, 1, md1)
+    assert np.array_equal(md1.indices.cpu().numpy(), g["decode1_indices"]) and np.array_equal(md1.ks.cpu().numpy(), g["decode1_ks"])
+    assert np.abs(out1.float().cpu().numpy() - g["decode1_out"]).max() < tol
+    out2, _ = call(x["q_decode"][2], T - 1, T, pool.get_hip_metadata_cache(lid, 1, 1, None))
+    assert np.abs(out2.float().cpu().numpy() - g["decode2_out"]).max() < tol
