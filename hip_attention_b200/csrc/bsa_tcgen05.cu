@@ -580,15 +580,19 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     const int ptid = tid - 160;  // 0..63
     // thread ptid copies piece ptid & 15 of rows (ptid >> 4) + 4 i
     const int g_pc = ptid & 15, g_r0 = ptid >> 4;
+    // All sixteen offsets are read first and the copies follow without a branch between them: a row that no
+    // query admits (offset -1) is a copy of zero source bytes, which fills its sixteen bytes with zeros.
     auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst) {
       const char* src = base + g_pc * 16;
-#pragma unroll 4
+      const uint32_t d0 = smem_u32(dst) + (g_pc >> 3) * (TK5 * 128);
+      long long o[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) o[i] = off[g_r0 + 4 * i];
+#pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const int r = g_r0 + 4 * i;
-        const long long o = off[r];
-        unsigned char* a = dst + (g_pc >> 3) * (TK5 * 128) + sw128(r, g_pc & 7);
-        if (o >= 0) cp_async16(a, src + o);
-        else *reinterpret_cast<uint4*>(a) = make_uint4(0, 0, 0, 0);
+        const bool live = o[i] >= 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d0 + sw128(g_r0 + 4 * i, g_pc & 7)), "l"(src + (live ? o[i] : 0)),
+                     "r"(live ? 16 : 0));
       }
     };
     auto producer_sync = [&]() { asm volatile("bar.sync 1, 64;\n" ::: "memory"); };
@@ -596,11 +600,12 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     producer_sync();
     if (n_tiles > 0) { gather_rows(meta[0].koff, kbase, sK); gather_rows(meta[0].voff, vbase, sV); }
     if (n_tiles > 1) gather_rows(meta[1].koff, kbase, sK + KT_BYTES);
+    prefetch_start(3, ptid);
     cp_async_commit();
     cp_async_wait<0>();
     fence_async_smem();
     __syncthreads();  // B0: Q, K(0), K(1), V(0) are in place
-    APROF_DECL(6);
+    APROF_DECL(7);
     for (int it = 0; it < n_tiles; ++it) {
       APROF_LAP(0);
       // K(it + 2) goes where K(it) was: wait until S(it) has been computed
@@ -609,6 +614,7 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         APROF_LAP(1);
         gather_rows(meta[(it + 2) & 3].koff, kbase, sK + (it & 1) * KT_BYTES);
       }
+      prefetch_start(it + 4, ptid);   // block start of this thread's entry of tile it + 4, used one tile from now
       cp_async_commit();
       APROF_LAP(2);
       // V(it + 1) goes where V(it - 1) was: wait until PV(it - 1) has completed
@@ -618,6 +624,10 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
       cp_async_commit();
       APROF_LAP(3);
+      // with both copies of this tile on their way, resolve the key positions and addresses of tile it + 3
+      // (one entry per thread; its block start arrived with the copies of the previous tile)
+      if (it + 3 < n_tiles) make_meta(it + 3, ptid, true);
+      APROF_LAP(6);
       cp_async_wait<1>();   // K(it + 2) and V(it) have landed; V(it + 1) may still be in flight
       fence_async_smem();
       APROF_LAP(4);
@@ -627,8 +637,8 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     cp_async_wait<0>();
 #ifdef HIPATTN_ATTN_PROFILE
     if (blockIdx.x == gridDim.x / 2 && ptid == 0)
-      printf("producer/tile: meta %lld  waitS %lld  gatherK %lld  waitPV+gatherV %lld  cpwait %lld  barrier %lld (tiles %d)\n",
-             ap_[0] / n_tiles, ap_[1] / n_tiles, ap_[2] / n_tiles, ap_[3] / n_tiles, ap_[4] / n_tiles, ap_[5] / n_tiles, n_tiles);
+      printf("producer/tile: top %lld  waitS %lld  gatherK %lld  waitPV+gatherV %lld  records %lld  cpwait %lld  barrier %lld (tiles %d)\n",
+             ap_[0] / n_tiles, ap_[1] / n_tiles, ap_[2] / n_tiles, ap_[3] / n_tiles, ap_[6] / n_tiles, ap_[4] / n_tiles, ap_[5] / n_tiles, n_tiles);
 #endif
   } else if (warp == 4) {
     // ================================ MMA issuer ================================
@@ -646,12 +656,6 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
       umma_commit(mbar_s0 + 8 * (tile & 1));
     };
-    // This warp is idle most of a tile (one lane issues a dozen MMAs): its lanes also resolve the key positions and
-    // addresses of tile it + 3, two entries per lane, with the block starts fetched one tile ahead.
-    prefetch_start(3, lane);
-    prefetch_start(3, lane + 32);
-    cp_async_commit();
-    cp_async_wait<0>();
     __syncthreads();  // B0
     if (lane == 0) {
       tc_fence_after();
@@ -660,14 +664,6 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     }
     APROF_DECL(3);
     for (int it = 0; it < n_tiles; ++it) {
-      if (it + 3 < n_tiles) {
-        make_meta(it + 3, lane, true);
-        make_meta(it + 3, lane + 32, true);
-      }
-      prefetch_start(it + 4, lane);
-      prefetch_start(it + 4, lane + 32);
-      cp_async_commit();
-      cp_async_wait<0>();     // the block starts of tile it + 4 are in place before the barrier
       if (__syncthreads_or(s_abort)) break;  // B1(it): P(it) is in TMEM, V(it) and K(it + 2) have landed
       APROF_LAP(0);
       if (lane == 0) {
