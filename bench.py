@@ -273,7 +273,7 @@ def main():
         return bench_decode.run(a, w)
 
     import torch.distributed as dist
-    from hip_attention_b200 import PhaseTimer, hip_attention_impl
+    from hip_attention_b200 import PhaseTimer, hip_attention_impl, read_status
     from hip_attention_b200.sharded import kv_head_slice, make_score_reduce
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -298,9 +298,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def check_status(where: str):
+        # a kernel that gave up on a bounded on-chip wait, or clamped a bad index, says so in the device status word:
+        # a number measured on such a run is not a measurement
+        st = read_status(dev)
+        if st != 0:
+            raise SystemExit(f"bench.py: device status word {st:#x} after {where}; the run is invalid")
+
+    read_status(dev)
     for _ in range(max(a.warmup, 3)):
         out, md = step()
     barrier()
+    check_status("the warm-up steps")
 
     # ---- device-resident timing -------------------------------------------------------------
     sampler = ClockSampler(local)
@@ -317,6 +326,7 @@ def main():
     e1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
+    check_status("the timed steps")
     ms_total = e0.elapsed_time(e1)
     tms = torch.tensor([ms_total], device=dev, dtype=torch.float64)
     if world > 1:
@@ -378,6 +388,7 @@ def main():
     e2e_run(a.steps)
     e1.record()
     barrier()
+    check_status("the end-to-end steps")
     tms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)

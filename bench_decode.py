@@ -70,6 +70,12 @@ def _queries(w, dev, steps, heads=None):
 
 
 def _emit(a, w, line):
+    # a kernel that gave up on a bounded on-chip wait, or clamped a bad index, says so in the device status word:
+    # a number measured on such a run is not a measurement
+    from hip_attention_b200 import read_status
+    st = read_status(torch.device("cuda", torch.cuda.current_device()))
+    if st != 0:
+        raise SystemExit(f"bench_decode.py: device status word {st:#x} after the measured steps; the run is invalid")
     print(json.dumps(line), flush=True)
 
 
