@@ -328,16 +328,24 @@ __global__ void __launch_bounds__(128) bsa_decode_mma_kernel(const hipattn_bsa_p
     const DecodeMeta& m = meta[tile % (kStages + 1)];
     unsigned char* kb = sK + (tile % kStages) * TILE_BYTES;
     unsigned char* vb = sV + (tile % kStages) * TILE_BYTES;
-    for (int i = tid; i < TKD * PIECES; i += 128) {
-      const int r = i / PIECES, pc = i % PIECES;
-      const long long ko = m.koff[r], vo = m.voff[r];
-      if (ko >= 0) {
-        cp_async16(kb + swz<D>(r, pc), kbase + ko + pc * 16);
-        cp_async16(vb + swz<D>(r, pc), vbase + vo + pc * 16);
-      } else {
-        *reinterpret_cast<uint4*>(kb + swz<D>(r, pc)) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(vb + swz<D>(r, pc)) = make_uint4(0, 0, 0, 0);
-      }
+    // the offsets of this thread's rows are read first and the copies follow without a branch between them: a row that
+    // the query does not admit (offset -1) is a copy of zero source bytes, which fills its sixteen bytes with zeros
+    constexpr int N = TKD * PIECES / 128;
+    static_assert(TKD * PIECES % 128 == 0, "a tile is a whole number of copies per thread");
+    long long ko[N], vo[N];
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+      const int r = (tid + n * 128) / PIECES;
+      ko[n] = m.koff[r];
+      vo[n] = m.voff[r];
+    }
+    const uint32_t kb_s = (uint32_t)__cvta_generic_to_shared(kb), vb_s = (uint32_t)__cvta_generic_to_shared(vb);
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+      const int i = tid + n * 128, r = i / PIECES, pc = i % PIECES;
+      const bool live = ko[n] >= 0;
+      cp_async16_zfill(kb_s + swz<D>(r, pc), kbase + (live ? ko[n] : 0) + pc * 16, live);
+      cp_async16_zfill(vb_s + swz<D>(r, pc), vbase + (live ? vo[n] : 0) + pc * 16, live);
     }
   };
 

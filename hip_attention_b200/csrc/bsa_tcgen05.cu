@@ -591,8 +591,7 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const bool live = o[i] >= 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d0 + sw128(g_r0 + 4 * i, g_pc & 7)), "l"(src + (live ? o[i] : 0)),
-                     "r"(live ? 16 : 0));
+        cp_async16_zfill(d0 + sw128(g_r0 + 4 * i, g_pc & 7), src + (live ? o[i] : 0), live);
       }
     };
     auto producer_sync = [&]() { asm volatile("bar.sync 1, 64;\n" ::: "memory"); };

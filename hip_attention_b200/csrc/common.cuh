@@ -132,6 +132,11 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
 }
+// The same copy to a shared-memory address, or sixteen zero bytes when `live` is false: a copy of zero source bytes
+// fills its destination with zeros and reads nothing, so a loop of copies needs no branch around masked rows.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t smem_addr, const void* gmem, bool live) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem), "r"(live ? 16 : 0));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

@@ -211,13 +211,12 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
       for (int r0 = 0; r0 < 32; r0 += 4) {
         const int j = r0 + (lane >> 3);
         const int src = __shfl_sync(0xffffffffu, idx, j);
-        if (src >= 0) {
-          const int srow = warp * 32 + j;
-          const char* gp = kbase + (int64_t)src * ROWB + (lane & 7) * 16;
-          unsigned char* sp = sK + sw128(srow, lane & 7);
+        // no branch between the copies: the row of an inactive candidate is a copy of zero source bytes (zero fill)
+        const bool live = src >= 0;
+        const char* gp = kbase + (int64_t)(live ? src : 0) * ROWB + (lane & 7) * 16;
+        const uint32_t sp = sK_u32 + sw128(warp * 32 + j, lane & 7);
 #pragma unroll
-          for (int kb = 0; kb < KB; ++kb) cp_async16(sp + kb * K_BLOCK_BYTES, gp + kb * 128);
-        }
+        for (int kb = 0; kb < KB; ++kb) cp_async16_zfill(sp + kb * K_BLOCK_BYTES, gp + kb * 128, live);
       }
       cp_async_commit();
       cp_async_wait<0>();
