@@ -206,6 +206,8 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
         }
         idx = (b * p.HKV + hkv) * p.T + tk;
       }
+      // the key's magnitude is needed only after the MMA: requested here, its latency hides behind the row copies
+      const float s_abs = act ? __ldg(p.key_abs + idx) : 0.f;
       // ---- gather this warp's 32 rows: 8 lanes per row, 128 contiguous bytes per row and instruction ----
 #pragma unroll
       for (int r0 = 0; r0 < 32; r0 += 4) {
@@ -255,7 +257,6 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
         }
         x = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
-      const float s_abs = act ? p.key_abs[idx] : 0.f;
       const float e_ = eps_q * s_abs * 1.01f;
       float sc = Elem<DT>::round(x);
       const bool sure = Elem<DT>::round(x - e_) == Elem<DT>::round(x + e_);
