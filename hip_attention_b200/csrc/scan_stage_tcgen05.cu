@@ -29,6 +29,17 @@
 namespace hipattn {
 namespace {
 
+// the CTA's small shared variables (behind the operand tiles in dynamic shared memory)
+struct ScanShared {
+  unsigned long long mbar;
+  uint32_t tmem;
+  int abort;
+  int pmin;
+  float qmax;
+  int g[2][4];
+};
+constexpr uint32_t kScanSlack = 896;   // padding reserved in front of the tiles
+
 template <int DT, int D, int NR>
 __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int check) {
   constexpr int ROWB = D * 2;                 // bytes per key / query row
@@ -37,18 +48,20 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
   constexpr int K_BLOCK_BYTES = 128 * 128;    // one K-block of the key tile: 128 rows x 128 B
   constexpr int Q_BLOCK_BYTES = NR * 128;
   constexpr uint32_t TMEM_COLS = NR < 32 ? 32 : NR;
-  extern __shared__ unsigned char smem_raw[];
+  // All shared memory is dynamic and the small variables sit behind the operand tiles, so that nothing precedes the
+  // tiles in the CTA's window: the tiles then need no padding to their 1024-byte alignment and six CTAs of the
+  // 16-row variant fit an SM (kScanSlack covers a window that is only 128-byte aligned).
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
+  unsigned char* smem = smem_raw + pad;
   unsigned char* sK = smem;                                  // [KB][128 keys][128 B], swizzled
   unsigned char* sQ = sK + KB * K_BLOCK_BYTES;               // [KB][NR rows][128 B], swizzled
-  float* kf32 = reinterpret_cast<float*>(sQ + KB * Q_BLOCK_BYTES);   // [4 warps][D]: key of a strict re-score
-  __shared__ __align__(8) unsigned long long s_mbar;
-  __shared__ uint32_t s_tmem;
-  __shared__ int s_abort;
-  __shared__ int s_pmin;
-  __shared__ float s_qmax;
-  __shared__ int s_g[2][4];
+  ScanShared& sh = *reinterpret_cast<ScanShared*>(sQ + KB * Q_BLOCK_BYTES);
+  if (pad > kScanSlack) {   // never expected: the launch reserved less padding than this window needs
+    if (threadIdx.x == 0) atomicOr(p.status, HIPATTN_STATUS_TIMEOUT);
+    return;
+  }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int Gq = p.H / p.HKV;
@@ -65,23 +78,23 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
   const int t0 = d * p.block_size_q;
   int Rv = 0;
   if (t0 < p.TQ) Rv = min(R, (p.TQ - t0 + p.stride_q - 1) / p.stride_q);
-  const uint32_t mbar = smem_u32(&s_mbar);
+  const uint32_t mbar = smem_u32(&sh.mbar);
 
   // ---- set-up: barrier, TMEM, pooled queries as the B operand ----
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar));
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    s_abort = 0;
-    s_qmax = 0.f;
+    sh.abort = 0;
+    sh.qmax = 0.f;
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = s_tmem;
+  const uint32_t tmem = sh.tmem;
 
   float qmax_local = 0.f;
   for (int i = tid; i < NR * PIECES; i += 128) {
@@ -98,60 +111,51 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) qmax_local = fmaxf(qmax_local, __shfl_xor_sync(0xffffffffu, qmax_local, o));
-  if (lane == 0) atomicMax(reinterpret_cast<int*>(&s_qmax), __float_as_int(qmax_local));  // non-negative floats order as ints
+  if (lane == 0) atomicMax(reinterpret_cast<int*>(&sh.qmax), __float_as_int(qmax_local));  // non-negative floats order as ints
   if (warp == 0) {
     const int m = block_min_position(p, b, t0, Rv, lane);
-    if (lane == 0) s_pmin = m;
+    if (lane == 0) sh.pmin = m;
   }
   fence_async_smem();
   __syncthreads();
 
-  const int pt = max(s_pmin - p.scan_window, 0);
-  const float eps_q = kEps * s_qmax;
+  const int pt = max(sh.pmin - p.scan_window, 0);
+  const float eps_q = kEps * sh.qmax;
   const int n = p.n_chunks;
   const int64_t row = (int64_t)b * BDST + d;
   const char* kbase = reinterpret_cast<const char*>(p.k_scaled);
   const uint32_t sK_u32 = smem_u32(sK), sQ_u32 = smem_u32(sQ);
   const uint32_t idesc = make_idesc(DT == HIPATTN_BF16 ? 1 : 0, 128, NR, 0);
   const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);
-  float* wkf = kf32 + warp * D;
   const int side = tid & 1;
   unsigned long long st_keys = 0, st_fb = 0, st_wrong = 0;
   float st_ratio = 0.f;
   uint32_t phase = 0;
 
   // strict dot products of the key staged in row `srow`, by the whole warp (one pooled row per lane);
-  // returns the largest one before rounding (rounding is monotonic, so it commutes with the maximum)
+  // returns the largest one before rounding (rounding is monotonic, so it commutes with the maximum).
+  // The key is read piece by piece from the operand tile (every lane the same address: a broadcast) and the loop is
+  // unrolled over the whole row, so that the loads run ahead of the one chain of fused multiply-adds per lane.
   auto strict_score = [&](int srow) -> float {
-    __syncwarp();
-    for (int e2 = lane; e2 < D / 2; e2 += 32) {
-      const int pc = e2 >> 2;
-      const uint32_t w = *reinterpret_cast<const uint32_t*>(sK + (pc >> 3) * K_BLOCK_BYTES + sw128(srow, pc & 7) + (e2 & 3) * 4);
-      wkf[2 * e2] = lo_f32<DT>(w);
-      wkf[2 * e2 + 1] = hi_f32<DT>(w);
-    }
-    __syncwarp();
     float best = -INFINITY;
     for (int r0 = 0; r0 < Rv; r0 += 32) {
       const int r = r0 + lane;
-      if (r < Rv) {
-        float acc = 0.f;
-#pragma unroll 4
-        for (int pc = 0; pc < PIECES; ++pc) {
-          const uint4 qw = *reinterpret_cast<const uint4*>(sQ + (pc >> 3) * Q_BLOCK_BYTES + sw128(r, pc & 7));
-          const float4 k0 = *reinterpret_cast<const float4*>(wkf + pc * 8);
-          const float4 k1 = *reinterpret_cast<const float4*>(wkf + pc * 8 + 4);
-          acc = fmaf(lo_f32<DT>(qw.x), k0.x, acc);
-          acc = fmaf(hi_f32<DT>(qw.x), k0.y, acc);
-          acc = fmaf(lo_f32<DT>(qw.y), k0.z, acc);
-          acc = fmaf(hi_f32<DT>(qw.y), k0.w, acc);
-          acc = fmaf(lo_f32<DT>(qw.z), k1.x, acc);
-          acc = fmaf(hi_f32<DT>(qw.z), k1.y, acc);
-          acc = fmaf(lo_f32<DT>(qw.w), k1.z, acc);
-          acc = fmaf(hi_f32<DT>(qw.w), k1.w, acc);
-        }
-        best = fmaxf(best, acc);
+      const int rr = r < Rv ? r : 0;
+      float acc = 0.f;
+#pragma unroll
+      for (int pc = 0; pc < PIECES; ++pc) {
+        const uint4 qw = lds128(sQ_u32 + (pc >> 3) * Q_BLOCK_BYTES + sw128(rr, pc & 7));
+        const uint4 kw = lds128(sK_u32 + (pc >> 3) * K_BLOCK_BYTES + sw128(srow, pc & 7));
+        acc = fmaf(lo_f32<DT>(qw.x), lo_f32<DT>(kw.x), acc);
+        acc = fmaf(hi_f32<DT>(qw.x), hi_f32<DT>(kw.x), acc);
+        acc = fmaf(lo_f32<DT>(qw.y), lo_f32<DT>(kw.y), acc);
+        acc = fmaf(hi_f32<DT>(qw.y), hi_f32<DT>(kw.y), acc);
+        acc = fmaf(lo_f32<DT>(qw.z), lo_f32<DT>(kw.z), acc);
+        acc = fmaf(hi_f32<DT>(qw.z), hi_f32<DT>(kw.z), acc);
+        acc = fmaf(lo_f32<DT>(qw.w), lo_f32<DT>(kw.w), acc);
+        acc = fmaf(hi_f32<DT>(qw.w), hi_f32<DT>(kw.w), acc);
       }
+      if (r < Rv) best = fmaxf(best, acc);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
@@ -180,12 +184,12 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
         }
       }
       m = __reduce_max_sync(0xffffffffu, m);
-      if (lane == 0) s_g[cbi & 1][warp] = m;
+      if (lane == 0) sh.g[cbi & 1][warp] = m;
     }
     __syncthreads();
-    const int cta_max = max(max(s_g[cbi & 1][0], s_g[cbi & 1][1]), max(s_g[cbi & 1][2], s_g[cbi & 1][3]));
+    const int cta_max = max(max(sh.g[cbi & 1][0], sh.g[cbi & 1][1]), max(sh.g[cbi & 1][2], sh.g[cbi & 1][3]));
     const int gmax = p.block_chunk >= 64 ? cta_max
-                     : (p.block_chunk == 32 ? max(s_g[cbi & 1][warp], s_g[cbi & 1][warp ^ 1]) : s_g[cbi & 1][warp]);
+                     : (p.block_chunk == 32 ? max(sh.g[cbi & 1][warp], sh.g[cbi & 1][warp ^ 1]) : sh.g[cbi & 1][warp]);
     const int my_rounds = gmax >= 1 ? 32 - __clz(gmax) : 0;
     const int cta_rounds = cta_max >= 1 ? 32 - __clz(cta_max) : 0;
     float score = HIPATTN_SCORE_INIT;
@@ -193,7 +197,7 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
     for (int it = 0; it < cta_rounds; ++it) {
       const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
       tc_fence_before();
-      const int any = __syncthreads_or((act ? 1 : 0) | (*(volatile int*)&s_abort ? 2 : 0));
+      const int any = __syncthreads_or((act ? 1 : 0) | (*(volatile int*)&sh.abort ? 2 : 0));
       if (any & 2) { aborted = true; break; }
       if (!(any & 1)) break;
       const int mid = (left + right) >> 1;
@@ -235,7 +239,7 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
         umma_commit(mbar);
       }
       __syncwarp();
-      bool ok = mbar_wait(mbar, phase, &s_abort, p.status);
+      bool ok = mbar_wait(mbar, phase, &sh.abort, p.status);
       phase ^= 1u;
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
@@ -318,7 +322,7 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
 
 template <int DT, int D, int NR>
 int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
-  const size_t smem = 1024 + (size_t)(D / 64) * (128 * 128 + NR * 128) + 4 * D * sizeof(float);
+  const size_t smem = kScanSlack + (size_t)(D / 64) * (128 * 128 + NR * 128) + sizeof(ScanShared);
   const int BDST = cdiv(p.TQ, p.block_size_q);
   const int nblk_total = cdiv(p.n_chunks, 64);
   const int64_t units = (int64_t)p.B * p.H * BDST;
