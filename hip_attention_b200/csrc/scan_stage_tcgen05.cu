@@ -195,11 +195,10 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
     float score = HIPATTN_SCORE_INIT;
 
     for (int it = 0; it < cta_rounds; ++it) {
+      // A warp goes straight from its decisions to the copies of its next 32 rows: those rows are its own (only this
+      // warp re-reads them for a strict re-score) and the MMA that read the tile has completed for every warp.  The one
+      // CTA-wide barrier of a round sits between the copies and the MMA; it also carries "is anybody still searching".
       const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
-      tc_fence_before();
-      const int any = __syncthreads_or((act ? 1 : 0) | (*(volatile int*)&sh.abort ? 2 : 0));
-      if (any & 2) { aborted = true; break; }
-      if (!(any & 1)) break;
       const int mid = (left + right) >> 1;
       int tk = side ? ((mid + right) >> 1) : ((left + mid) >> 1);
       int idx = -1;
@@ -227,7 +226,10 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
       cp_async_commit();
       cp_async_wait<0>();
       fence_async_smem();
-      __syncthreads();
+      tc_fence_before();
+      const int any = __syncthreads_or((act ? 1 : 0) | (*(volatile int*)&sh.abort ? 2 : 0));
+      if (any & 2) { aborted = true; break; }
+      if (!(any & 1)) break;
       if (tid == 0) {
         tc_fence_after();
 #pragma unroll
