@@ -164,13 +164,23 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
 
   bool aborted = Rv == 0;
   int cbi = 0;
+  // the bounds of a thread's chunk are requested one chunk block ahead, so that their latency is not part of the chain
+  int next_left = 0, next_right = 0;
+  if (cblk < nblk_total && cblk * 64 + (tid >> 1) < n) {
+    next_left = __ldg(p.left + row * n + cblk * 64 + (tid >> 1));
+    next_right = __ldg(p.right + row * n + cblk * 64 + (tid >> 1));
+  }
   for (int cb = cblk; cb < nblk_total && !aborted; cb += nblk, ++cbi) {
     const int c = cb * 64 + (tid >> 1);
     const bool in_range = c < n;
-    int left = 0, right = 0;
-    if (in_range) {
-      left = p.left[row * n + c];
-      right = p.right[row * n + c];
+    int left = next_left, right = next_right;
+    next_left = next_right = 0;
+    {
+      const int cn = c + nblk * 64;
+      if (cb + nblk < nblk_total && cn < n) {
+        next_left = __ldg(p.left + row * n + cn);
+        next_right = __ldg(p.right + row * n + cn);
+      }
     }
     // halving rounds: fixed by the largest chunk of the reference group of block_chunk chunks that
     // holds this thread's chunk; a warp covers 16 chunks, the CTA 64
