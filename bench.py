@@ -53,7 +53,7 @@ WORKLOADS = {
 _DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 # dram__bytes_read.sum + dram__bytes_write.sum per scan launch (mean of the three stages), from the ncu capture
 # summarised in profiles/prefill128k_dram_traffic.md; keyed by (workload, GPUs, queries)
-NCU_DRAM_BYTES_PER_SCAN_LAUNCH = {("prefill_128k", 1, 32768): (578108160 + 594838272 + 359103488) / 3}
+NCU_DRAM_BYTES_PER_SCAN_LAUNCH = {("prefill_128k", 1, 32768): (563160320 + 582162688 + 357693696) / 3}
 
 
 # ----------------------------------------------------------------------------------------------
