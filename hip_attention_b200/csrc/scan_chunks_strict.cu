@@ -124,12 +124,40 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
   const int cl = lane >> c_log2;                    // chunk of the pass
   int cur_group = -1, cur_gmax = 0;
 
-  // passes of this warp: the unit's passes are dealt to the n_split CTAs x 4 warps round-robin
-  for (int ps = split * 4 + warp; ps < passes_total; ps += n_split * 4) {
+  // What a pass needs before its rows can be requested: this lane's chunk bounds and the address of its token's row
+  // (two dependent global reads: the bounds, then the page table).  Resolved one pass ahead, while the rows of the
+  // current pass are on their way, so that neither read is part of a pass's chain.
+  struct PassInput {
+    int l, rt;
+    bool valid;
+    const char* src;
+  };
+  auto resolve_pass = [&](int ps) {
+    PassInput in{0, 0, false, nullptr};
+    if (ps >= passes_total) return in;
     const int c = (ps << cpp_log2) + cl;
-    int l = 0, rt = 0;
-    if (c < n) { l = gl[c]; rt = gr[c]; }
-    if (rt - l > C) atomicOr(p.status, HIPATTN_STATUS_CHUNK_SIZE);
+    if (c < n) { in.l = __ldg(gl + c); in.rt = __ldg(gr + c); }
+    if (in.rt - in.l > C) atomicOr(p.status, HIPATTN_STATUS_CHUNK_SIZE);
+    const bool chunk_act = c < n && in.l < in.rt && in.l <= pt && in.l >= 0;
+    int tk = in.l + (lane & (C - 1));
+    in.valid = chunk_act && tk < in.rt;
+    if (in.valid) {
+      if (p.k.cache == nullptr && tk >= p.T) {
+        atomicOr(p.status, HIPATTN_STATUS_TOKEN_RANGE);
+        tk = p.T - 1;
+      }
+      in.src = token_row(p.k, b, tk, hkv, EB, p.status);
+    }
+    return in;
+  };
+
+  // passes of this warp: the unit's passes are dealt to the n_split CTAs x 4 warps round-robin
+  const int ps_step = n_split * 4;
+  PassInput next_in = resolve_pass(split * 4 + warp);
+  for (int ps = split * 4 + warp; ps < passes_total; ps += ps_step) {
+    const int c = (ps << cpp_log2) + cl;
+    const PassInput in = next_in;
+    const int l = in.l, rt = in.rt;
     // halving rounds: from the largest chunk of the reference group of block_chunk chunks (all chunks of a
     // pass lie in one group: a pass holds at most 8 chunks, a group at least 16, both powers of two)
     const int group = (ps << cpp_log2) >> bc_log2;
@@ -144,19 +172,11 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
       cur_group = group;
     }
     const int rounds = cur_gmax >= 1 ? 32 - __clz(cur_gmax) : 0;
-    // this lane's token
-    const bool chunk_act = c < n && l < rt && l <= pt && l >= 0;
-    int tk = l + (lane & (C - 1));
-    const bool valid = chunk_act && tk < rt;
-    const char* src = nullptr;
-    if (valid) {
-      if (p.k.cache == nullptr && tk >= p.T) {
-        atomicOr(p.status, HIPATTN_STATUS_TOKEN_RANGE);
-        tk = p.T - 1;
-      }
-      src = token_row(p.k, b, tk, hkv, EB, p.status);
-    }
-    if (__any_sync(0xffffffffu, valid)) {   // chunks that are not active still report their (unchanged) bounds below
+    const bool valid = in.valid;
+    const char* src = in.src;
+    const bool any_valid = __any_sync(0xffffffffu, valid);
+    if (!any_valid) next_in = resolve_pass(ps + ps_step);
+    if (any_valid) {   // chunks that are not active still report their (unchanged) bounds below
     // cooperative gather of the pass's 32 rows
     __syncwarp();
     if (PIECES <= 32) {
@@ -176,6 +196,7 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
       }
     }
     cp_async_commit();
+    next_in = resolve_pass(ps + ps_step);   // the next pass's bounds and row address travel with this pass's rows
     cp_async_wait<0>();
     __syncwarp();
     // strict scores of this lane's token for the HB heads
