@@ -43,6 +43,26 @@ __device__ __forceinline__ float exp2_approx(float x) {
   return y;
 }
 
+// two-wide fp32 arithmetic (one instruction for a pair of lanes' values): the softmax is bound by instruction issue
+__device__ __forceinline__ unsigned long long f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f32x2_split(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 // Optional cycle accounting of one CTA's roles, printed from the device; compiled in with
 // -DHIPATTN_ATTN_PROFILE for experiments only.
 #ifdef HIPATTN_ATTN_PROFILE
@@ -738,16 +758,24 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         }
       }
       const float base = m_ref > -INFINITY ? m_ref : 0.f;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // the scaling and the row sum run two values per instruction
+      const unsigned long long scale2 = f32x2(kLog2e, kLog2e), nbase2 = f32x2(-base, -base);
+      unsigned long long sum2[4] = {0ull, 0ull, 0ull, 0ull};
       float pk[32];
 #pragma unroll
       for (int j = 0; j < TK5; j += 2) {
-        const float e0 = exp2_approx(fmaf(s[j], kLog2e, -base));
-        const float e1 = exp2_approx(fmaf(s[j + 1], kLog2e, -base));
-        sum4[(j >> 1) & 3] += e0 + e1;
+        float x0, x1;
+        f32x2_split(fma_f32x2(f32x2(s[j], s[j + 1]), scale2, nbase2), x0, x1);
+        const float e0 = exp2_approx(x0), e1 = exp2_approx(x1);
+        sum2[(j >> 1) & 3] = add_f32x2(sum2[(j >> 1) & 3], f32x2(e0, e1));
         pk[j >> 1] = __uint_as_float(pack2<DT>(e0, e1));
       }
-      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      {
+        float a0, a1, b0, b1;
+        f32x2_split(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), a0, a1);
+        (void)b0; (void)b1;
+        l_run += a0 + a1;
+      }
       APROF_LAP(2);
       tmem_st32(ts, pk);        // P(it) over the first half of S(it)
       tc_fence_before();
