@@ -11,6 +11,7 @@ partials are all-gathered.
 """
 from __future__ import annotations
 
+import hashlib
 import json
 import os
 import time
@@ -69,14 +70,13 @@ def _queries(w, dev, steps, heads=None):
     return q
 
 
-def _emit(a, w, line):
+def _check_status(dev):
     # a kernel that gave up on a bounded on-chip wait, or clamped a bad index, says so in the device status word:
     # a number measured on such a run is not a measurement
     from hip_attention_b200 import read_status
-    st = read_status(torch.device("cuda", torch.cuda.current_device()))
+    st = read_status(dev)
     if st != 0:
         raise SystemExit(f"bench_decode.py: device status word {st:#x} after the measured steps; the run is invalid")
-    print(json.dumps(line), flush=True)
 
 
 def fetched_scan_bytes(w, heads):
@@ -99,17 +99,13 @@ def fetched_scan_bytes(w, heads):
     return total
 
 
-def run(a, w):
+def run(a, w, dev, rank, world, triton=False):
+    """Runs a decode workload on this rank; returns the JSON record on rank 0 (None elsewhere)."""
     import torch.distributed as dist
-    from hip_attention_b200 import PhaseTimer, hip_attention_impl
+    from hip_attention_b200 import PhaseTimer, _lib, hip_attention_impl
     from hip_attention_b200.sharded import hip_attention_12_sequence_sharded
-
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    local = dev.index
     steps = a.steps if a.steps != 5 else 64
     B, T, H, HKV, D = w["B"], w["T"], w["H"], w["HKV"], w["D"]
     peaks = {}
@@ -151,16 +147,18 @@ def run(a, w):
                     timers.append(t)
             return out
 
-        run_steps(max(a.warmup, 3) * refresh // refresh + refresh)  # at least one refresh + cached steps
+        run_steps(max(a.warmup, 3) + refresh)  # at least one refresh + cached steps
         barrier()
         sampler = bench.ClockSampler(local)
         sampler.start()
         timers = []
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = lib.hipattn_launch_count()
         e0.record()
         run_steps(steps, timers)
         e1.record()
         barrier()
+        launches = lib.hipattn_launch_count() - launches0
         clocks = sampler.stop()
         ms_step = e0.elapsed_time(e1) / steps
         ph_refresh, ph_cached, n_r, n_c = {}, {}, 0, 0
@@ -207,42 +205,56 @@ def run(a, w):
         e1.record()
         barrier()
         graph_ms = e0.elapsed_time(e1) / steps
-        sb = bench.scan_bytes(w, H)
+        _check_status(dev)
+        fetched = fetched_scan_bytes(w, H)
         scan_ms = sum(v_ for k_, v_ in ph_refresh.items() if k_.startswith("scan"))
         att_bytes = B * HKV * (w["keep"][-1] + w["sink"] + w["sw"]) * D * 2 * 2
         att_ms = ph_cached.get("attention", 0.0)
+        scan_gbs = fetched / 1e9 / (scan_ms / 1e3) if scan_ms else None
         line = {
             "metric": "hip_decode_ms_per_step", "value": graph_ms, "unit": "ms/step", "n_gpus": 1, "steps": steps,
             "warmup": max(a.warmup, 3), "ms_per_step": graph_ms, "eager_ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "weak",
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-            "config": {"workload": a.workload, "B": B, "TQ": 1, "T": T, "H": H, "HKV": HKV, "D": D, "page": w["page"],
-                       "mask_refresh_every": refresh, "l2": "page pool of 2 x 8.6 GB exceeds the 126 MB L2",
+            "config": {**bench.config_of(a, w, 1), "l2": "page pool of 2 x 8.6 GB exceeds the 126 MB L2",
                        "launch": "value: two CUDA graphs (refresh step, cached-mask step) replayed; eager_ms_per_step: plain calls"},
             "clocks": clocks,
             "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": qs[0].numel() * 2,
                     "d2h_bytes_per_step": qs[0].numel() * 2},
-            "gpu_launches": None,
+            "gpu_launches": int(launches), "gpu_launches_counted_by": "hipattn_launch_count() around the eager timed steps",
             "phases_ms": {"refresh_step": ph_refresh, "cached_step": ph_cached},
-            # `algorithmic` counts the key rows the reference's rounds fetch.  The stages with small
-            # chunks fetch every chunk once for the heads of a KV head instead (same results, fewer rows): the rows
-            # actually requested are `fetched_bytes_per_refresh`, and `fetched_gbs` is the bandwidth they came at.
+            # The bytes counted are the key rows the scan kernels request: the stages with small chunks fetch every
+            # token of an active chunk once for the heads of a KV head, the others two rows per chunk, head and round.
             "roofline": {"kernel": "scan_stage_kernel + scan_chunks_strict_kernel (refresh steps)", "bound": "hbm",
-                         "achieved": sb / 1e9 / (scan_ms / 1e3) if scan_ms else None, "peak": peak, "peak_source": peak_src,
-                         "unit": "GB/s", "frac": (sb / 1e9 / (scan_ms / 1e3)) / peak if scan_ms else None, "traffic": None,
-                         "algorithmic_bytes_per_refresh": sb,
-                         "fetched_bytes_per_refresh": fetched_scan_bytes(w, H),
-                         "fetched_gbs": fetched_scan_bytes(w, H) / 1e9 / (scan_ms / 1e3) if scan_ms else None},
+                         "achieved": scan_gbs, "peak": peak, "peak_source": peak_src,
+                         "unit": "GB/s", "frac": scan_gbs / peak if scan_gbs else None, "traffic": None,
+                         "algorithmic_bytes_per_refresh": fetched,
+                         "bytes_if_every_head_gathered_two_rows_per_round": bench.scan_bytes(w, H), "scan_ms_per_refresh": scan_ms},
             "attention_roofline": {"kernel": "bsa_decode_mma_kernel (split-KV decode)", "bound": "hbm",
                                    "achieved": att_bytes / 1e9 / (att_ms / 1e3) if att_ms else None, "peak": peak,
                                    "unit": "GB/s", "frac": (att_bytes / 1e9 / (att_ms / 1e3)) / peak if att_ms else None,
                                    "algorithmic_bytes_per_step": att_bytes},
         }
-        n_launch_refresh = 3 + len(w["chunks"]) + 3 * (len(w["chunks"]) - 1) + 1
-        line["gpu_launches"] = n_r * n_launch_refresh + n_c * 2
         if not a.no_cpu_baseline:
-            line["cpu_baseline"] = _cpu_decode(w)
-        return _emit(a, w, line)
+            # one sequence through the CPU oracle on the GPU's own tensors: the baseline, and the parity check
+            k0 = kc[table[0].long()].reshape(1, T, HKV, D).cpu()
+            v0 = vc[table[0].long()].reshape(1, T, HKV, D).cpu()
+            out0, md0_ = hip_attention_impl(qs[0][:1], None, None, bench.make_args(
+                w, k_cache=kc, v_cache=vc, block_table=table[:1], cache_seq_lens=seq[:1], position_ids=pos[:1],
+                extend_context_length=T))
+            rec, ref_out, m = _cpu_decode(w, qs[0][:1].cpu(), k0, v0)
+            line["cpu_baseline"] = rec
+            mask_equal = bool(torch.equal(md0_.indices.cpu(), m.indices) and torch.equal(md0_.ks.cpu(), m.ks))
+            err = (out0.float().cpu() - ref_out.float()).abs()
+            line["parity"] = {"sequences": 1, "mask_equal": mask_equal, "out_max_abs": float(err.max()),
+                              "out_mean_abs": float(err.mean()), "tolerance": {"max_abs": 2e-2, "mean_abs": 2e-3},
+                              "against": "CPU oracle on the same tensors (sequence 0, de-paged)"}
+            if not mask_equal or err.max().item() > 2e-2 or err.mean().item() > 2e-3:
+                print(json.dumps(line), flush=True)
+                raise SystemExit("bench_decode.py: the GPU result differs from the CPU oracle on the sampled sequence")
+        if triton:
+            line["triton_reference"] = _triton_decode(w, kc, vc, table, qs, steps)
+        return line
 
     # ---- sequence-sharded million-token decode -----------------------------------------------------
     S = w["shards"]
@@ -250,11 +262,11 @@ def run(a, w):
         raise SystemExit(f"{S} shards cannot be split over {world} ranks")
     per = S // world
     L = T // S
-    shard_kv = []
-    for j in range(per):
-        s = rank * per + j
-        kc, vc, table = _paged_pool(w, dev, t0=s * L, t1=(s + 1) * L)
-        shard_kv.append((kc, vc, table, torch.full((B,), L, dtype=torch.int32, device=dev)))
+    # one page pool per rank holding its shards; every shard has its own page table into it
+    kc, vc, table = _paged_pool(w, dev, t0=rank * per * L, t1=(rank + 1) * per * L)
+    pps = L // w["page"]
+    shard_kv = [(kc, vc, table[:, j * pps:(j + 1) * pps].contiguous(), torch.full((B,), L, dtype=torch.int32, device=dev))
+                for j in range(per)]
     qs = _queries(w, dev, steps)
     args = bench.make_args(w)
 
@@ -265,15 +277,20 @@ def run(a, w):
     for i in range(max(a.warmup, 3)):
         out, mds = one(i, None)
     barrier()
+    out0, _ = one(0, None)
+    out_hash = hashlib.sha256(out0.float().cpu().numpy().tobytes()).hexdigest()
     sampler = bench.ClockSampler(local)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    launches0 = lib.hipattn_launch_count()
     e0.record()
     for i in range(steps):
         out, mds = one(i, None)   # every step re-estimates the mask: the worst case
     e1.record()
     barrier()
+    launches = lib.hipattn_launch_count() - launches0
     tms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     e0.record()
     for i in range(steps):
@@ -281,9 +298,23 @@ def run(a, w):
     e1.record()
     barrier()
     tms2 = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    # end to end: the query comes from pinned host memory and the merged output goes back, every step
+    hq = qs.cpu().pin_memory()
+    dq = torch.empty_like(qs[0])
+    ho = torch.empty(qs[0].shape, dtype=qs.dtype).pin_memory()
+    barrier()
+    e0.record()
+    for i in range(steps):
+        dq.copy_(hq[i], non_blocking=True)
+        o_, _ = hip_attention_12_sequence_sharded(dq, shard_kv, args, n_shards=S, shard_len=L, per_shard_k=w["keep"][-1],
+                                                  first_shard=rank * per)
+        ho.copy_(o_, non_blocking=True)
+    e1.record()
+    barrier()
+    tms3 = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        dist.all_reduce(tms2, op=dist.ReduceOp.MAX)
+        for t_ in (tms, tms2, tms3):
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
     graph_ms = None
     if world == 1:
         q_static = qs[0].clone()
@@ -306,44 +337,113 @@ def run(a, w):
         e1.record()
         barrier()
         graph_ms = e0.elapsed_time(e1) / steps
-    if rank == 0:
-        clocks = sampler.stop()
-        ms_step = float(tms.item()) / steps
-        wsh = dict(w, T=L)
-        sb = bench.scan_bytes(wsh, H) * S
-        line = {"metric": "hip_decode_ms_per_step", "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": steps,
-                "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
-                "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-                "config": {"workload": a.workload, "B": B, "TQ": 1, "T": T, "H": H, "HKV": HKV, "D": D, "page": w["page"],
-                           "logical_shards": S, "per_shard_top_k": w["keep"][-1], "mask": "re-estimated every step"},
-                "clocks": clocks, "cached_mask_ms_per_step": float(tms2.item()) / steps,
-                "cuda_graph_ms_per_step": graph_ms,
-                "roofline": {"kernel": "scan_stage_kernel", "bound": "hbm", "achieved": None, "peak": peak,
-                             "peak_source": peak_src, "unit": "GB/s", "frac": None, "traffic": None,
-                             "algorithmic_bytes_per_step": sb,
-                             "note": "whole-step figure: bytes / step time = %.1f GB/s" % (sb / 1e9 / (ms_step / 1e3))}}
-        _emit(a, w, line)
-    if world > 1:
-        dist.destroy_process_group()
+    _check_status(dev)
+    if rank != 0:
+        return None
+    clocks = sampler.stop()
+    ms_step = float(tms.item()) / steps
+    wsh = dict(w, T=L)
+    sb = fetched_scan_bytes(wsh, H) * S
+    att_bytes = HKV * (S * w["keep"][-1] + w["sink"] + w["sw"] + (S - 1) * w["chunks"][0]) * D * 2 * 2
+    gbs = (sb + att_bytes) / 1e9 / (ms_step / 1e3)
+    return {"metric": "hip_decode_ms_per_step", "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": steps,
+            "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {**bench.config_of(a, w, world), "mask": "re-estimated every step", "parallelism": f"sequence shards x{world}",
+                       "l2": "each step draws a new query; the 4.3 GB page pool exceeds the 126 MB L2"},
+            "clocks": clocks, "cached_mask_ms_per_step": float(tms2.item()) / steps,
+            "cuda_graph_ms_per_step": graph_ms,
+            "e2e": {"value": float(tms3.item()) / steps, "unit": "ms/step", "h2d_bytes_per_step": qs[0].numel() * 2,
+                    "d2h_bytes_per_step": qs[0].numel() * 2},
+            "gpu_launches": int(launches), "gpu_launches_counted_by": "hipattn_launch_count() around the timed steps (rank 0)",
+            "merged_output_sha256": out_hash,
+            "roofline": {"kernel": "whole step (scan + selection + split-KV attention + merge of every shard)", "bound": "hbm",
+                         "achieved": gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": gbs / peak,
+                         "traffic": None, "algorithmic_bytes_per_step": sb + att_bytes,
+                         "note": "launch-latency bound: a step is a few tens of short launches on 1/Nth of 5 MB of key rows"}}
 
 
-def _cpu_decode(w):
-    """CPU oracle on one of the B sequences: one refresh step and one cached step, scaled to B sequences."""
+def run_reference_arm(a, w, cores):
+    """CPU arm for the decode workloads: the oracle on one sequence (one refresh and one cached step per timed step)."""
+    w1 = dict(w, B=1)
+    if w["kind"] == "decode_sharded":
+        w1["T"] = w["T"] // w["shards"]   # one logical shard per step
+    q, k, v = bench.make_qkv(w1, "cpu")
+    vals = []
+    for i in range(a.warmup + a.steps):
+        rec, _, _ = _cpu_decode(dict(w1, refresh=w.get("refresh", 1)), q, k, v)
+        if i >= a.warmup:
+            vals.append(rec["value"])
+    scale = w["B"] if w["kind"] == "decode" else w["shards"]
+    val = float(np.mean(vals)) * scale
+    sample = (f"1 of {w['B']} sequences per step, scaled by {w['B']}" if w["kind"] == "decode"
+              else f"1 of {w['shards']} sequence shards per step, scaled by {w['shards']}")
+    line = {"impl": "reference", "metric": "hip_decode_ms_per_step", "value": val, "unit": "ms/step", "n_gpus": a.gpus,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": val, "higher_is_better": False,
+            "scaling": "weak" if w["kind"] == "decode" else "strong", "vs_baseline": None, "dtype": w["dtype"],
+            "data": "synthetic", "config": bench.config_of(a, w, a.gpus),
+            "cpu_baseline": {"value": val, "unit": "ms/step", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def _cpu_decode(w, q, k, v):
+    """CPU oracle on one sequence (q [1, 1, H, D], dense k / v): one refresh step and one cached step, scaled to
+    the batch and the refresh interval.  Returns (baseline record, output, mask)."""
     from oracle import hip_oracle as O
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
-    w1 = dict(w, B=1)
-    q, k, v = bench.make_qkv(w1, "cpu")
-    cfg = bench.oracle_config(w1)
-    pos = torch.full((1, 1), w["T"] - 1, dtype=torch.int64)
+    cfg = bench.oracle_config(w)
+    T = k.shape[1]
+    pos = torch.full((1, 1), T - 1, dtype=torch.int64)
     ks, vs = O.DenseKV(k), O.DenseKV(v)
     t0 = time.perf_counter()
     m = O.estimate_mask(q, ks, pos, cfg)
     t1 = time.perf_counter()
-    O.attention_on_mask(q, ks, vs, pos, m, sink=cfg.sink, sw=max(cfg.sw, cfg.stages[0].chunk_size), dtype=torch.float32)
+    out = O.attention_on_mask(q, ks, vs, pos, m, sink=cfg.sink, sw=max(cfg.sw, cfg.stages[0].chunk_size), dtype=torch.float32)
     t2 = time.perf_counter()
-    r = w["refresh"]
+    r = w.get("refresh", 1)
     per_seq = ((t1 - t0) + r * (t2 - t1)) / r
-    return {"value": 1e3 * per_seq * w["B"], "unit": "ms/step", "cores": cores, "kind": "port",
-            "sample": f"1 of {w['B']} sequences (estimator {t1 - t0:.2f} s once per {r} steps, attention {t2 - t1:.3f} s per step), "
-                      f"scaled by {w['B']}"}
+    rec = {"value": 1e3 * per_seq * w["B"], "unit": "ms/step", "cores": cores, "kind": "port",
+           "sample": f"1 of {w['B']} sequences (estimator {t1 - t0:.2f} s once per {r} steps, attention {t2 - t1:.3f} s per step), "
+                     f"scaled by {w['B']}"}
+    return rec, out, m
+
+
+def _triton_decode(w, kc, vc, table, qs, steps):
+    """The unmodified reference operator on the decode workload: dense K / V rebuilt from the page pool (the reference
+    refuses pages of more than 32 tokens, attention_metadata.py:239), its own flash-decode kernels, the same refresh
+    schedule, plain calls (no CUDA graph)."""
+    import sys
+    sys.path.insert(0, os.path.join(bench.ROOT, "baseline"))
+    try:
+        import reference_loader as R
+        if not R.available():
+            return {"unavailable": "no copy of the reference under baseline/_ref"}
+        op, Args, ScanStage = R.load_reference()
+        import triton
+        B, T, HKV, D = w["B"], w["T"], w["HKV"], w["D"]
+        k = kc[table.long()].reshape(B, T, HKV, D)
+        v = vc[table.long()].reshape(B, T, HKV, D)
+        pos = torch.full((B, 1), T - 1, dtype=torch.int64, device=k.device)
+        ra = R.reference_args(Args, ScanStage, bq=w["bq"], strides=w["strides"], chunks=w["chunks"], keep=w["keep"],
+                              sink=w["sink"], sw=w["sw"], position_ids=pos)
+        refresh = w["refresh"]
+
+        def run_steps(n):
+            md = None
+            for i in range(n):
+                out, md = op(qs[i % steps], k, v, args=ra, cached_metadata=None if i % refresh == 0 else md)
+            return out
+
+        run_steps(2 * refresh)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run_steps(steps)
+        e1.record()
+        torch.cuda.synchronize()
+        return {"ms_per_step": e0.elapsed_time(e1) / steps, "steps": steps, "kv": "dense (de-paged)", "launch": "plain calls",
+                "triton": triton.__version__, "torch": torch.__version__, "autotune": "off (HIP_DISABLE_AUTOTUNE=1)"}
+    except Exception as e:  # noqa: BLE001 - whatever stops the reference is reported, not raised
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}

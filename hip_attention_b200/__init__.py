@@ -7,7 +7,7 @@ from .metadata import (EnsembleScoreStage, EvalScoreStage, HiPAttentionArgs, HiP
                        HiPAttentionOutputMetadata, HiPAttentionStageInputCache, NopStage, ScanStage, Stage)
 from .operator import PhaseTimer, hip_attention_12, hip_attention_impl, read_status
 from .serving import (HiPAttentionConfig, HiPAttentionPerLayerConfig, HiPMaskRefreshState, HiPMetadataCache,
-                      HiPMetadataCachePool, forward_paged_hip)
+                      HiPMetadataCachePool, cuda_graph_capture_configs, forward_paged_hip)
 
 # the names the reference exports for this generation of the operator
 HiPAttentionArgs12 = HiPAttentionArgs
@@ -22,5 +22,5 @@ __all__ = [
     "HiPAttentionCacheAccessStatistics", "HiPAttentionCacheAccessStatistics12", "HiPAttentionStageInputCache",
     "Stage", "ScanStage", "ScanStage12", "NopStage", "EvalScoreStage", "EnsembleScoreStage",
     "HiPAttentionConfig", "HiPAttentionPerLayerConfig", "HiPMaskRefreshState", "HiPMetadataCache", "HiPMetadataCachePool",
-    "forward_paged_hip",
+    "forward_paged_hip", "cuda_graph_capture_configs",
 ]

@@ -12,7 +12,7 @@ F32, F16, BF16 = 0, 1, 2
 STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE, STATUS_TIMEOUT, STATUS_CHUNK_SIZE = 1, 2, 4, 8
 MAX_CHUNKS = 16384
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
-ABI_VERSION = 4
+ABI_VERSION = 5
 SCAN_AUTO, SCAN_STRICT, SCAN_CHECK = 0, 1, 2
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
@@ -66,6 +66,7 @@ SYMBOLS = {
     "hipattn_decode_scores": (i32, [vp, vp, i64, vp]),
     "hipattn_widen_i32": (i32, [vp, vp, i64, vp]),
     "hipattn_debug_bounded_wait": (i32, [vp, vp]),
+    "hipattn_launch_count": (C.c_uint64, []),
     "hipattn_error_string": (C.c_char_p, []),
     "hipattn_abi_version": (i32, []),
 }

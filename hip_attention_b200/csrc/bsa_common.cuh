@@ -7,7 +7,8 @@
 // pmax) a key at position t is admitted when
 //   sink / selected entry ("far" keys):  t <= p - window
 //   window entry:                        p - window < t <= p
-// and a selected entry must also satisfy sink <= t <= pmax and t < T.  The two rules are disjoint,
+// and a selected entry must also satisfy sink <= t <= pmax and t < T; sink and window entries are cut at T
+// as well (query positions beyond the keys set HIPATTN_STATUS_TOKEN_RANGE).  The two rules are disjoint,
 // so a token that appears in two groups is counted once.
 #pragma once
 #include "common.cuh"
@@ -34,10 +35,15 @@ __device__ __forceinline__ KeyList make_key_list(const hipattn_bsa_params_t& p, 
   kl.sink = p.sink;
   kl.T = p.T;
   kl.pmax = pmax;
-  kl.n_sink = max(0, min(p.sink, pmax + 1));
+  // Sink and window entries are positions, not table entries: keep them below T.  With dense K / V a
+  // query position at or beyond T would otherwise address rows past the end of the tensors (a paged
+  // cache maps such positions to page 0 by itself).  The clamp is reported, not silent.
+  const int t_end = min(pmax + 1, p.T);
+  if (pmax >= p.T && p.k.cache == nullptr && p.status && threadIdx.x == 0) atomicOr(p.status, HIPATTN_STATUS_TOKEN_RANGE);
+  kl.n_sink = max(0, min(p.sink, t_end));
   kl.n_sel = (int)ks * p.block_size_k;
   kl.w_start = max(0, pmin - p.window + 1);
-  kl.n_win = p.window > 0 ? max(0, pmax + 1 - kl.w_start) : 0;
+  kl.n_win = p.window > 0 ? max(0, t_end - kl.w_start) : 0;
   kl.total = kl.n_sink + kl.n_sel + kl.n_win;
   return kl;
 }

@@ -1,21 +1,20 @@
-// Block-sparse attention, prefill, 16-bit types, head dim 128: tcgen05 / TMEM kernel.
+// Block-sparse attention, prefill, 16-bit types, head dim 128: warp-specialised tcgen05 / TMEM kernel.
 //
-// One CTA (128 threads, one warpgroup) owns 128 query rows -- two heads of a KV group x 64 rows, or
-// one head x 128 rows -- and walks the key list [sink | selected blocks | window] in tiles of 64 keys.
-// Two CTAs are resident per SM, so one CTA's softmax overlaps the other's tensor-core work.
+// One CTA (7 warps) owns 128 query rows -- two heads of a KV group x 64 rows, or one head x 128
+// rows -- and walks the key list [sink | selected blocks | window] in tiles of 64 keys.  Two CTAs
+// are resident per SM, so one CTA's softmax overlaps the other's tensor-core work.
 //
 //   S = Q K^T   tcgen05.mma (M 128, N 64, K 16) x 8, operands in shared memory (128-byte-swizzled
-//               canonical layouts, K-major), accumulator in TMEM columns [0, 64)
+//               canonical layouts, K-major), accumulator double buffered in TMEM
 //   softmax     thread t owns row t = TMEM lane t: tcgen05.ld of its 64 logits, admission rule,
-//               base-2 online softmax with a lazily updated maximum, P written to shared memory as
-//               the next A operand
-//   O += P V    tcgen05.mma (M 128, N 128, K 16) x 4 into TMEM columns [64, 192); V is staged row-major
+//               base-2 online softmax with a lazily updated maximum, P written back to TMEM
+//   O += P V    tcgen05.mma (M 128, N 128, K 16) x 4, A operand = P in TMEM, V staged row-major
 //               (MN-major operand)
 //
-// K / V rows are gathered by all threads with 16-byte cp.async through the page table directly into
-// the swizzled operand layouts.  O stays in TMEM for the whole key list: the running maximum used
-// for the exponentials is only raised (and O rescaled in TMEM) when the true maximum has grown by
-// more than 2^8, which keeps P within bf16 / fp16 range and makes rescaling rare.
+// K / V rows are gathered with 16-byte cp.async through the page table directly into the swizzled
+// operand layouts.  O stays in TMEM for the whole key list: the running maximum used for the
+// exponentials is only raised (and O rescaled in TMEM) when the true maximum has grown by more than
+// 2^8, which keeps P within bf16 / fp16 range and makes rescaling rare.
 // Every wait on an mbarrier is bounded; a wait that runs out sets HIPATTN_STATUS_TIMEOUT and the CTA
 // leaves through the normal exit (TMEM freed), so a fault in the pipeline cannot hang the device.
 #include <cstdio>
@@ -63,16 +62,6 @@ __device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, un
   return r;
 }
 
-// Optional cycle accounting of one CTA's roles, printed from the device; compiled in with
-// -DHIPATTN_ATTN_PROFILE for experiments only.
-#ifdef HIPATTN_ATTN_PROFILE
-#define APROF_DECL(n) long long ap_[n] = {}; long long ap_t_ = clock64()
-#define APROF_LAP(k) do { const long long t_ = clock64(); ap_[k] += t_ - ap_t_; ap_t_ = t_; } while (0)
-#else
-#define APROF_DECL(n)
-#define APROF_LAP(k)
-#endif
-
 struct Meta5 {
   int tpos[TK5];
   int twin[TK5];
@@ -83,373 +72,6 @@ struct Meta5 {
   int win_ok[2];
 };
 
-
-template <int DT>
-__global__ void __launch_bounds__(128, 2) bsa_tcgen05_kernel(const hipattn_bsa_params_t p, int BQ, int n_sub) {
-  using T = typename Elem<DT>::type;
-  constexpr int Q_BYTES = 2 * 128 * 128;      // [2 k-blocks][128 rows][128 B]
-  constexpr int KT_BYTES = 2 * TK5 * 128;     // [2 k-blocks][64 keys][128 B]
-  constexpr int P_BYTES = 128 * 128;          // [128 rows][64 keys] 16-bit
-  extern __shared__ unsigned char smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-  unsigned char* sQ = smem;                   // also the output staging area
-  unsigned char* sK = sQ + Q_BYTES;           // 2 buffers
-  unsigned char* sV = sK + 2 * KT_BYTES;      // 1 buffer: [2 d-blocks][64 keys][128 B]
-  unsigned char* sP = sV + KT_BYTES;
-  Meta5* meta = reinterpret_cast<Meta5*>(sP + P_BYTES);  // 3 entries
-  __shared__ __align__(8) unsigned long long s_mbar[2];   // S ready, O ready
-  __shared__ uint32_t s_tmem;
-  __shared__ int s_abort;
-  __shared__ int s_rowpos[128];
-  __shared__ int s_mm[4];
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int Gq = p.H / p.HKV;
-  const int NH = 128 / BQ;
-  const int NBLK = cdiv(p.TQ, p.block_size_q);
-  const int hslots = p.H / NH;
-  int64_t bid = blockIdx.x;
-  const int sub = (int)(bid % n_sub); bid /= n_sub;
-  const int d = (int)(bid % NBLK); bid /= NBLK;
-  const int hs = (int)(bid % hslots); bid /= hslots;
-  const int b = (int)bid;
-  const int h0 = hs * NH;
-  const int hkv = h0 / Gq;
-  const int blk_t0 = d * p.block_size_q;
-  const int blk_rows = min(p.block_size_q, p.TQ - blk_t0);
-  const int row_t0 = blk_t0 + sub * BQ;
-  const int rows_here = max(0, min(BQ, blk_rows - sub * BQ));
-  const uint32_t mbar_s = smem_u32(&s_mbar[0]), mbar_o = smem_u32(&s_mbar[1]);
-
-  // ---- set-up: barriers, TMEM (256 columns), positions, Q tile ----
-  if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar_s));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar_o));
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    s_abort = 0;
-  }
-  if (tid < 4) s_mm[tid] = (tid & 1) ? -1 : 0x7fffffff;
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)), "r"(256u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = s_tmem;
-  {
-    int lo = 0x7fffffff, hi = -1;
-    for (int i = tid; i < blk_rows; i += 128) {
-      const long long x = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(blk_t0 + i) * p.pos_stride_t];
-      const int v = (int)(x > 0x7ffffff0LL ? 0x7ffffff0LL : (x < 0 ? 0 : x));
-      lo = min(lo, v); hi = max(hi, v);
-    }
-    if (hi >= 0) { atomicMin(&s_mm[0], lo); atomicMax(&s_mm[1], hi); }
-  }
-  {
-    const int i = tid % BQ;
-    int pv = -0x40000000;
-    if (i < rows_here) {
-      const long long x = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(row_t0 + i) * p.pos_stride_t];
-      pv = (int)(x > 0x7ffffff0LL ? 0x7ffffff0LL : (x < 0 ? 0 : x));
-      atomicMin(&s_mm[2], pv);
-      atomicMax(&s_mm[3], pv);
-    }
-    s_rowpos[tid] = pv;
-  }
-  for (int i = tid; i < 128 * 16; i += 128) {
-    const int r = i >> 4, pc = i & 15;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if ((r % BQ) < rows_here) {
-      const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(row_t0 + r % BQ) * p.q_stride_t +
-                    (int64_t)(h0 + r / BQ) * p.q_stride_h + pc * 8;
-      v = *reinterpret_cast<const uint4*>(qp);
-    }
-    *reinterpret_cast<uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(r, pc & 7)) = v;
-  }
-  fence_async_smem();
-  __syncthreads();
-  const int pmin = s_mm[0], pmax = s_mm[1];
-  const int rmin = s_mm[2], rmax = s_mm[3];
-  const KeyList kl = make_key_list(p, b, h0, d, pmin, pmax);
-  const int n_tiles = cdiv(kl.total, TK5);
-  const char* kbase = (const char*)(p.k.cache ? p.k.cache : p.k.dense);
-  const char* vbase = (const char*)(p.v.cache ? p.v.cache : p.v.dense);
-
-  auto make_meta = [&](int tile) {
-    if (tid < TK5) {
-      Meta5& m = meta[tile % 3];
-      bool w;
-      const int j = tile * TK5 + tid;
-      const int t = key_position(kl, j, &w);
-      m.tpos[tid] = t;
-      m.twin[tid] = (t >= 0 && w) ? 1 : 0;
-      long long ko = -1, vo = -1;
-      if (t >= 0) {
-        ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
-        vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
-      }
-      m.koff[tid] = ko;
-      m.voff[tid] = vo;
-      const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
-      const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
-      const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
-      if ((tid & 31) == 0) {
-        m.far_ok[tid >> 5] = f;
-        m.win_ok[tid >> 5] = g;
-      }
-    }
-  };
-  // rows of a tile: 64 keys x 16 pieces; piece pc belongs to 64-element block pc >> 3.  Thread tid
-  // always copies piece tid & 15 of rows (tid >> 4) + 8 i, so its destination offsets never change.
-  const int g_pc = tid & 15, g_r0 = tid >> 4;
-  int g_dst[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) g_dst[i] = (g_pc >> 3) * (TK5 * 128) + sw128(g_r0 + 8 * i, g_pc & 7);
-  auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst) {
-    const char* src = base + g_pc * 16;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const long long o = off[g_r0 + 8 * i];
-      if (o >= 0) cp_async16(dst + g_dst[i], src + o);
-      else *reinterpret_cast<uint4*>(dst + g_dst[i]) = make_uint4(0, 0, 0, 0);
-    }
-  };
-
-  constexpr int FMT = DT == HIPATTN_BF16 ? 1 : 0;
-  const uint32_t idesc_s = make_idesc(FMT, 128, TK5, 0);
-  const uint32_t idesc_o = make_idesc(FMT, 128, D5, 1);
-  const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-
-  float m_ref = -INFINITY;   // maximum the exponentials refer to
-  float l_run = 0.f;
-  const int prow = s_rowpos[tid];
-  const float cap = p.logit_softcap;
-  uint32_t phase = 0;
-  bool have_o = false;
-
-  // descriptors differ only in their start-address field (low word); the high words are constants
-  const uint64_t dk = make_desc(0, 16, 1024);            // K-major operands: Q, K, P
-  const uint64_t dv = make_desc(0, TK5 * 128, 1024);     // MN-major operand: V
-  const uint32_t q_lo = smem_u32(sQ) >> 4, k_lo = smem_u32(sK) >> 4, p_lo = smem_u32(sP) >> 4, v_lo = smem_u32(sV) >> 4;
-  constexpr int kIssuer = 96;  // first lane of warp 3: warps 0 and 1 resolve addresses, keep them free
-  auto issue_s = [&](int tile) {   // S(tile) = Q K(tile)^T, by one thread
-    const uint32_t kb = k_lo + (tile & 1) * (KT_BYTES >> 4);
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const uint32_t off = (kk >> 2) * ((128 * 128) >> 4) + (kk & 3) * 2;
-      const uint32_t offk = (kk >> 2) * ((TK5 * 128) >> 4) + (kk & 3) * 2;
-      umma(tmem_s, dk | (uint64_t)((q_lo + off) & 0x3fffu), dk | (uint64_t)((kb + offk) & 0x3fffu), idesc_s, kk > 0);
-    }
-    umma_commit(mbar_s);
-  };
-  auto issue_o = [&](bool accumulate) {   // O (+)= P V, by one thread
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk)
-      umma(tmem_o, dk | (uint64_t)((p_lo + kk * 2) & 0x3fffu), dv | (uint64_t)((v_lo + kk * 128) & 0x3fffu), idesc_o,
-           (accumulate || kk > 0) ? 1u : 0u);
-    umma_commit(mbar_o);
-  };
-
-  // Pipeline invariant at the top of iteration `it`: S(it) has been issued; the gathers of V(it) and
-  // K(it + 1) have been issued; PV(it - 1) has completed.
-  if (n_tiles > 0) {
-    make_meta(0);
-    if (n_tiles > 1) make_meta(1);
-    __syncthreads();
-    gather_rows(meta[0].koff, kbase, sK);
-    cp_async_commit();
-    cp_async_wait<0>();
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == kIssuer) {
-      tc_fence_after();
-      issue_s(0);
-    }
-    gather_rows(meta[0].voff, vbase, sV);
-    if (n_tiles > 1) gather_rows(meta[1].koff, kbase, sK + KT_BYTES);
-    cp_async_commit();
-  }
-  // optional cycle breakdown of CTA 0 / thread 0 (part_lse is unused by prefill): wait S, softmax,
-  // wait copies, barrier, issue, wait O, gather issue, meta
-  const bool prof = p.part_lse != nullptr && blockIdx.x == 0 && tid == kIssuer;
-  long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  long long tprev = clock64();
-  auto lap = [&](int i) { if (prof) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; } };
-  for (int it = 0; it < n_tiles; ++it) {
-    const Meta5& mt = meta[it % 3];
-    if (it + 2 < n_tiles) make_meta(it + 2);
-    lap(7);
-    // ---- softmax of row `tid` on S(it) ----
-    mbar_wait(mbar_s, phase, &s_abort, p.status);
-    __syncwarp();
-    tc_fence_after();
-    lap(0);
-    // Two passes over the 64 logits of the row, 16 columns at a time, in rolled loops (a compact loop
-    // body keeps the instruction cache warm): pass 1 finds the row maximum, pass 2 exponentiates.
-    const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
-    auto logit = [&](float x, int j) -> float {
-      if (cap > 0.f) x = tanhf(x / cap) * cap;
-      x *= kLog2e;
-      if (!full && !admits(prow, mt.tpos[j], mt.twin[j] != 0, p.window)) x = -INFINITY;
-      return x;
-    };
-    const bool plain = full && !(cap > 0.f);   // CTA-uniform: every key admitted for every row, no soft-cap
-    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    if (plain) {
-#pragma unroll 1
-      for (int c = 0; c < TK5 / 32; ++c) {
-        float v[32];
-        tmem_ld32(tmem_s + lane_base + c * 32, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], v[j]);
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) mx4[j] *= kLog2e;
-    } else {
-#pragma unroll 1
-      for (int c = 0; c < TK5 / 16; ++c) {
-        float v[16];
-        tmem_ld16(tmem_s + lane_base + c * 16, v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], logit(v[j], c * 16 + j));
-      }
-    }
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    // raise the reference maximum only when needed; O (in TMEM) and l are rescaled together.
-    // tcgen05.ld / st are warp-collective: if any lane of the warp rescales, every lane takes the
-    // branch (lanes that need no change multiply by one).
-    const bool need = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
-    if (__any_sync(0xffffffffu, need)) {
-      const float alpha = !need ? 1.f : (m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx));
-      if (have_o) {
-#pragma unroll 1
-        for (int c = 0; c < D5; c += 32) {
-          float o[32];
-          tmem_ld32(tmem_o + lane_base + c, o);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] *= alpha;
-          tmem_st32(tmem_o + lane_base + c, o);
-        }
-      }
-      if (need) {
-        l_run *= alpha;
-        m_ref = mx;
-      }
-    }
-    const float base = m_ref > -INFINITY ? m_ref : 0.f;
-    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-    if (plain) {
-#pragma unroll 1
-      for (int c = 0; c < TK5 / 32; ++c) {
-        float v[32];
-        tmem_ld32(tmem_s + lane_base + c * 32, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] = exp2_approx(fmaf(v[j], kLog2e, -base));
-          sum4[j & 3] += v[j];
-        }
-#pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          uint4 w;
-          w.x = pack2<DT>(v[g8 * 8 + 0], v[g8 * 8 + 1]); w.y = pack2<DT>(v[g8 * 8 + 2], v[g8 * 8 + 3]);
-          w.z = pack2<DT>(v[g8 * 8 + 4], v[g8 * 8 + 5]); w.w = pack2<DT>(v[g8 * 8 + 6], v[g8 * 8 + 7]);
-          *reinterpret_cast<uint4*>(sP + sw128(tid, c * 4 + g8)) = w;
-        }
-      }
-    } else {
-#pragma unroll 1
-      for (int c = 0; c < TK5 / 16; ++c) {
-        float v[16];
-        tmem_ld16(tmem_s + lane_base + c * 16, v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          v[j] = exp2_approx(logit(v[j], c * 16 + j) - base);
-          sum4[j & 3] += v[j];
-        }
-        uint4 w0, w1;
-        w0.x = pack2<DT>(v[0], v[1]); w0.y = pack2<DT>(v[2], v[3]); w0.z = pack2<DT>(v[4], v[5]); w0.w = pack2<DT>(v[6], v[7]);
-        w1.x = pack2<DT>(v[8], v[9]); w1.y = pack2<DT>(v[10], v[11]); w1.z = pack2<DT>(v[12], v[13]); w1.w = pack2<DT>(v[14], v[15]);
-        *reinterpret_cast<uint4*>(sP + sw128(tid, c * 2)) = w0;
-        *reinterpret_cast<uint4*>(sP + sw128(tid, c * 2 + 1)) = w1;
-      }
-    }
-    l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-    lap(1);
-    cp_async_wait<0>();   // V(it) and K(it + 1) have landed
-    fence_async_smem();
-    tc_fence_before();
-    lap(2);
-    if (__syncthreads_or(s_abort)) break;  // leave together if any wait ran out
-    lap(3);
-    // ---- O += P V(it), then straight on to S(it + 1) ----
-    if (tid == kIssuer) {
-      tc_fence_after();
-      issue_o(have_o);
-      if (it + 1 < n_tiles) issue_s(it + 1);
-    }
-    have_o = true;
-    lap(4);
-    mbar_wait(mbar_o, phase, &s_abort, p.status);   // PV(it) done: sV, sP and sK[it & 1] are free
-    __syncwarp();
-    tc_fence_after();
-    lap(5);
-    phase ^= 1;
-    if (it + 1 < n_tiles) {
-      gather_rows(meta[(it + 1) % 3].voff, vbase, sV);
-      if (it + 2 < n_tiles) gather_rows(meta[(it + 2) % 3].koff, kbase, sK + (it & 1) * KT_BYTES);
-    }
-    cp_async_commit();
-    lap(6);
-  }
-  if (prof) {
-    for (int i = 0; i < 8; ++i) p.part_lse[i] = (float)pc[i];
-    p.part_lse[8] = (float)n_tiles;
-  }
-  cp_async_wait<0>();
-  __syncthreads();
-  const bool aborted = s_abort != 0;
-
-  // ---- epilogue: O / l -> element type, staged through shared memory, 16-byte stores ----
-  const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-#pragma unroll
-  for (int c = 0; c < D5; c += 32) {
-    float o[32];
-    if (have_o && !aborted) {
-      tmem_ld32(tmem_o + lane_base + c, o);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) o[j] = 0.f;
-    }
-#pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      uint4 w;
-      w.x = pack2<DT>(o[j] * inv, o[j + 1] * inv); w.y = pack2<DT>(o[j + 2] * inv, o[j + 3] * inv);
-      w.z = pack2<DT>(o[j + 4] * inv, o[j + 5] * inv); w.w = pack2<DT>(o[j + 6] * inv, o[j + 7] * inv);
-      const int pc = (c + j) >> 3;
-      *reinterpret_cast<uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(tid, pc & 7)) = w;
-    }
-  }
-  if (p.lse_out && (tid % BQ) < rows_here)
-    p.lse_out[((int64_t)b * p.TQ + row_t0 + tid % BQ) * p.H + h0 + tid / BQ] = l_run > 0.f ? m_ref + log2f(l_run) : -INFINITY;
-  tc_fence_before();
-  __syncthreads();
-  for (int i = tid; i < 128 * 16; i += 128) {
-    const int r = i >> 4, pc = i & 15;
-    if ((r % BQ) < rows_here) {
-      T* op = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_stride_b + (int64_t)(row_t0 + r % BQ) * p.o_stride_t +
-              (int64_t)(h0 + r / BQ) * p.o_stride_h + pc * 8;
-      *reinterpret_cast<uint4*>(op) = *reinterpret_cast<const uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(r, pc & 7));
-    }
-  }
-  if (warp == 0) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256u) : "memory");
-  }
-}
 
 // ---------------------------------------------------------------------------------------------------
 // Warp-specialised variant (7 warps): warps 0-3 run the softmax (thread = query row = TMEM lane),
@@ -624,41 +246,28 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     cp_async_wait<0>();
     fence_async_smem();
     __syncthreads();  // B0: Q, K(0), K(1), V(0) are in place
-    APROF_DECL(7);
     for (int it = 0; it < n_tiles; ++it) {
-      APROF_LAP(0);
       // K(it + 2) goes where K(it) was: wait until S(it) has been computed
       if (it + 2 < n_tiles) {
         mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
-        APROF_LAP(1);
         gather_rows(meta[(it + 2) & 3].koff, kbase, sK + (it & 1) * KT_BYTES);
       }
       prefetch_start(it + 4, ptid);   // block start of this thread's entry of tile it + 4, used one tile from now
       cp_async_commit();
-      APROF_LAP(2);
       // V(it + 1) goes where V(it - 1) was: wait until PV(it - 1) has completed
       if (it + 1 < n_tiles) {
         if (it >= 1) mbar_wait(mbar_o, (it - 1) & 1, &s_abort, p.status);
         gather_rows(meta[(it + 1) & 3].voff, vbase, sV + ((it + 1) & 1) * KT_BYTES);
       }
       cp_async_commit();
-      APROF_LAP(3);
       // with both copies of this tile on their way, resolve the key positions and addresses of tile it + 3
       // (one entry per thread; its block start arrived with the copies of the previous tile)
       if (it + 3 < n_tiles) make_meta(it + 3, ptid, true);
-      APROF_LAP(6);
       cp_async_wait<1>();   // K(it + 2) and V(it) have landed; V(it + 1) may still be in flight
       fence_async_smem();
-      APROF_LAP(4);
       if (__syncthreads_or(s_abort)) break;  // B1(it)
-      APROF_LAP(5);
     }
     cp_async_wait<0>();
-#ifdef HIPATTN_ATTN_PROFILE
-    if (blockIdx.x == gridDim.x / 2 && ptid == 0)
-      printf("producer/tile: top %lld  waitS %lld  gatherK %lld  waitPV+gatherV %lld  records %lld  cpwait %lld  barrier %lld (tiles %d)\n",
-             ap_[0] / n_tiles, ap_[1] / n_tiles, ap_[2] / n_tiles, ap_[3] / n_tiles, ap_[6] / n_tiles, ap_[4] / n_tiles, ap_[5] / n_tiles, n_tiles);
-#endif
   } else if (warp == 4) {
     // ================================ MMA issuer ================================
     const uint64_t dk = make_desc(0, 16, 1024);
@@ -681,10 +290,8 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       if (n_tiles > 0) issue_s(0);
       if (n_tiles > 1) issue_s(1);
     }
-    APROF_DECL(3);
     for (int it = 0; it < n_tiles; ++it) {
       if (__syncthreads_or(s_abort)) break;  // B1(it): P(it) is in TMEM, V(it) and K(it + 2) have landed
-      APROF_LAP(0);
       if (lane == 0) {
         tc_fence_after();
         const uint32_t tp = tmem + (it & 1) * 64;                        // P(it): 32 columns of packed pairs
@@ -693,16 +300,10 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(tmem_o, tp + kk * 8, dv | (uint64_t)((vb + kk * 128) & 0x3fffu), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(mbar_o);
-        APROF_LAP(1);
         if (it + 2 < n_tiles) issue_s(it + 2);
-        APROF_LAP(2);
       }
       __syncwarp();
     }
-#ifdef HIPATTN_ATTN_PROFILE
-    if (blockIdx.x == gridDim.x / 2 && lane == 0)
-      printf("issuer/tile: barrier %lld  PV issue %lld  S issue %lld\n", ap_[0] / n_tiles, ap_[1] / n_tiles, ap_[2] / n_tiles);
-#endif
   } else {
     // ================================ softmax: thread = row = TMEM lane ================================
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
@@ -710,18 +311,15 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     const float cap = p.logit_softcap;
     float m_ref = -INFINITY, l_run = 0.f;
     __syncthreads();  // B0
-    APROF_DECL(5);
     for (int it = 0; it < n_tiles; ++it) {
       const Meta5& mt = meta[it & 3];
       const uint32_t ts = tmem + (it & 1) * 64 + lane_base;
       mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
       __syncwarp();
       tc_fence_after();
-      APROF_LAP(0);
       float s[TK5];
       tmem_ld32(ts, s);
       tmem_ld32(ts + 32, s + 32);
-      APROF_LAP(1);
       const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
       if (!(full && !(cap > 0.f))) {   // CTA-uniform slow path: soft-cap and / or per-element admission
 #pragma unroll
@@ -776,18 +374,10 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         (void)b0; (void)b1;
         l_run += a0 + a1;
       }
-      APROF_LAP(2);
       tmem_st32(ts, pk);        // P(it) over the first half of S(it)
       tc_fence_before();
-      APROF_LAP(3);
       if (__syncthreads_or(s_abort)) break;  // B1(it)
-      APROF_LAP(4);
     }
-#ifdef HIPATTN_ATTN_PROFILE
-    if (blockIdx.x == gridDim.x / 2 && tid == 0)
-      printf("softmax/tile: waitS %lld  ld %lld  max+exp+pack %lld  st %lld  barrier %lld\n", ap_[0] / n_tiles, ap_[1] / n_tiles,
-             ap_[2] / n_tiles, ap_[3] / n_tiles, ap_[4] / n_tiles);
-#endif
     // ---- epilogue for this thread's row ----
     bool ok = n_tiles > 0;
     if (ok) {
@@ -847,19 +437,6 @@ int launch5_ws(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t st
   return check_launch("bsa_tcgen05_ws_kernel");
 }
 
-template <int DT>
-int launch5(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t stream) {
-  const size_t smem = 1024 + 2 * 128 * 128 + 3 * (2 * TK5 * 128) + 128 * 128 + 3 * sizeof(Meta5);
-  const int NH = 128 / BQ;
-  const int NBLK = cdiv(p.TQ, p.block_size_q);
-  const int64_t grid = (int64_t)p.B * (p.H / NH) * NBLK * n_sub;
-  HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "attention grid of %lld blocks", (long long)grid);
-  auto kern = bsa_tcgen05_kernel<DT>;
-  HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)grid, 128, smem, stream>>>(p, BQ, n_sub);
-  return check_launch("bsa_tcgen05_kernel");
-}
-
 // One CTA waits on an mbarrier that nothing ever arrives on, through the same bounded wait the
 // attention kernel uses, and then leaves normally: exercises the time-out path without any fault.
 __global__ void bounded_wait_probe_kernel(uint32_t* status) {
@@ -894,9 +471,6 @@ int bsa_tcgen05(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handle
   else if (p.block_size_q % 128 == 0) { BQ = 128; n_sub = p.block_size_q / 128; }
   else return HIPATTN_OK;
   *handled = true;
-  const char* pk = getenv("HIPATTN_PREFILL_KERNEL");
-  if (pk && strcmp(pk, "tcgen05") == 0)   // single-warpgroup variant, kept for comparisons
-    return p.dtype == HIPATTN_BF16 ? launch5<HIPATTN_BF16>(p, BQ, n_sub, stream) : launch5<HIPATTN_F16>(p, BQ, n_sub, stream);
   return p.dtype == HIPATTN_BF16 ? launch5_ws<HIPATTN_BF16>(p, BQ, n_sub, stream) : launch5_ws<HIPATTN_F16>(p, BQ, n_sub, stream);
 }
 

@@ -1,5 +1,6 @@
 // C ABI glue: error reporting, argument validation, kernel selection for attention, and the
 // log-sum-exp merge of partial outputs.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -10,6 +11,9 @@
 namespace hipattn {
 
 static thread_local char g_error[512] = "";
+static std::atomic<unsigned long long> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -99,8 +103,7 @@ extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream
   bool handled = false;
   rc = bsa_decode(*p, (cudaStream_t)stream, &handled);
   if (handled) return rc;
-  // HIPATTN_PREFILL_KERNEL = tcgen05_ws (default: warp-specialised tcgen05 kernel) | tcgen05 (single
-  // warpgroup) | mma (mma.sync kernel); the last two exist for comparisons
+  // HIPATTN_PREFILL_KERNEL = tcgen05 (default: warp-specialised tcgen05 kernel) | mma (mma.sync kernel, for comparisons)
   const char* pk = getenv("HIPATTN_PREFILL_KERNEL");
   if (!(pk && strcmp(pk, "mma") == 0)) {
     rc = bsa_tcgen05(*p, (cudaStream_t)stream, &handled);
@@ -149,5 +152,6 @@ extern "C" int hipattn_debug_bounded_wait(uint32_t* status, void* stream) {
   return bounded_wait_probe(status, (cudaStream_t)stream);
 }
 
+extern "C" uint64_t hipattn_launch_count(void) { return hipattn::g_launches.load(std::memory_order_relaxed); }
 extern "C" const char* hipattn_error_string(void) { return g_error; }
-extern "C" int hipattn_abi_version(void) { return 4; }
+extern "C" int hipattn_abi_version(void) { return 5; }

@@ -31,7 +31,11 @@ void set_error(const char* fmt, ...);
     }                                                                                  \
   } while (0)
 
+// kernels launched by this library in this process (every launch site goes through check_launch)
+void count_launch();
+
 inline int check_launch(const char* what) {
+  count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("launch of %s failed: %s", what, cudaGetErrorString(e));

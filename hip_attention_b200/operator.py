@@ -139,6 +139,11 @@ def _reject_unsupported(args: HiPAttentionArgs) -> None:
             raise NotImplementedError(f"stage {i}: only ScanStage is built ({type(st).__name__} given)")
         if st.stage_stride != 1:
             raise NotImplementedError("stage_stride != 1 is not built")
+        # the selection kernel always realigns, resets the scores and sorts by position; the reference does
+        # each only when the stage asks for it (attention_extend.py:2075-2090, 2638)
+        if i > 0 and not (st.require_realign_index and st.require_reset_score and st.require_post_sort):
+            raise NotImplementedError(f"stage {i}: require_realign_index / require_reset_score / require_post_sort "
+                                      "= False is not built")
         if st.stage_block_size_q != args.stages[0].stage_block_size_q:
             raise NotImplementedError("all stages must use the same stage_block_size_q")
         if st.stage_block_size_q % st.stage_block_stride_q:
@@ -535,9 +540,11 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
             ks_start_end = cached_metadata.ks_start_end.clone()
             heads_share = bool(getattr(cached_metadata, "_heads_share", False))
             bsa_bq = min(args.block_sparse_block_size_q or bq, bq)
-            # cached rows may already be broken down to the attention block size
+            # cached rows may already be broken down to the attention block size: the fresh path returns
+            # BDST * (bq / bsa_bq) rows (repeat-interleave, attention_extend.py:3036-3051), of which a ragged
+            # last block uses only the first cdiv(TQ, bsa_bq)
             index_block_q = bq if indices.shape[1] == BDST else bsa_bq
-            if indices.shape[1] not in (BDST, _cdiv(TQ, bsa_bq)) or indices.shape[0] != B * H:
+            if indices.shape[1] not in (BDST, _cdiv(TQ, bsa_bq), BDST * (bq // bsa_bq)) or indices.shape[0] != B * H:
                 raise ValueError(f"cached indices shape {tuple(indices.shape)} does not fit this call")
             if indices.dtype != torch.int64 or ks.dtype != torch.int64:
                 indices, ks = indices.to(torch.int64), ks.to(torch.int64)

@@ -11,8 +11,9 @@ in-kernel RoPE (``using_extend`` must be false) and the host-offload cache.
 from __future__ import annotations
 
 import json
+import os
 from dataclasses import InitVar, dataclass, field
-from typing import Dict, List, Optional, Sequence, Union
+from typing import Any, Dict, List, Optional, Sequence, Union
 
 import torch
 from torch import Tensor
@@ -325,25 +326,42 @@ class HiPMetadataCachePool:
 LAST_DENSE = 64   # queries at the end of a prefill chunk that attend a near-full window (paged_hip.py:462)
 
 
+def cuda_graph_capture_configs(hip_config: HiPAttentionConfig):
+    """The ``(num_stage_cached,)`` variants of a decode step a server captures as CUDA graphs
+    (``paged_hip.py:27-32``): the whole mask cached (``None``) and one entry per stage the estimator may
+    restart from."""
+    configs = [(None,)]
+    for i_stage in range(len(hip_config.layers[0].stages)):
+        configs.append((i_stage,))
+    return configs
+
+
 def forward_paged_hip(query: Tensor, sm_scale: float, batch_size: int, k_cache: Optional[Tensor], v_cache: Optional[Tensor],
-                      positions: Tensor, seq_lens: Tensor, req_to_tokens: Tensor, req_pool_indices: Tensor, layer_id: int,
-                      logit_cap: float, orig_context_len: int, max_context_len: int, hip_config: HiPAttentionConfig,
-                      cached_metadata: Optional[HiPAttentionOutputMetadata] = None, k: Optional[Tensor] = None,
-                      v: Optional[Tensor] = None, is_decode: bool = False, query_for_mask: Optional[Tensor] = None,
-                      offload_cache=None, rope_cos: Optional[Tensor] = None, rope_sin: Optional[Tensor] = None):
-    """One attention layer of a serving step (paged_hip.py:35-131, 327-500).
+                      offload_cache: Any, positions: Tensor, seq_lens: Tensor, req_to_tokens: Tensor,
+                      req_pool_indices: Tensor, rope_cos: Optional[Tensor], rope_sin: Optional[Tensor], layer_id: int,
+                      logit_cap: float, orig_context_len: int, max_context_len: int, is_prefill: bool,
+                      hip_config: HiPAttentionConfig, cached_metadata: Optional[HiPAttentionOutputMetadata] = None,
+                      k: Optional[Tensor] = None, v: Optional[Tensor] = None, online_update_cache: bool = False,
+                      offloading_metadata: Any = None, is_decode: bool = False, query_for_mask: Optional[Tensor] = None,
+                      diag_sliding_window_indices: Optional[Tensor] = None):
+    """One attention layer of a serving step; parameter list and order of the reference's
+    ``forward_paged_hip`` (``paged_hip.py:35-62``, body ``:327-500``), so positional callers keep working.
 
     ``query`` [N, H, D] holds ``batch_size`` requests of N / batch_size tokens each; ``k_cache`` / ``v_cache``
-    [tokens, HKV, D] are the server's token-granular pools (page size 1) and ``req_to_tokens[req_pool_indices]`` the
-    per-request token tables; ``k`` / ``v`` [B, T, HKV, D] may be given instead (padded to ``max_context_len``).
-    Decode steps and short chunks are one operator call.  A prefill chunk of 128 tokens or more is split: all but
-    the last 64 queries run with the layer's window, the last 64 with the window sentinel 777, which the operator
-    turns into (model context - sink - second_stage_k - query block) so that they see nearly everything.
+    [tokens, HKV, D] are the server's token-granular pools (page size 1; a ``float8_e5m2`` pool is read as such)
+    and ``req_to_tokens[req_pool_indices]`` the per-request token tables; ``k`` / ``v`` [B, T, HKV, D] may be given
+    instead (padded to ``max_context_len``).  ``rope_cos`` / ``rope_sin`` are used when the configuration has
+    ``using_extend`` set.  Decode steps and short chunks are one operator call.  A prefill chunk of 128 tokens or
+    more is split: all but the last 64 queries run with the layer's window, the last 64 with the window sentinel
+    777, which the operator turns into (model context - sink - second_stage_k - query block) so that they see
+    nearly everything.  ``is_prefill`` only selects what the reference validates against its offload cache and is
+    otherwise unused, as there.  Not built (rejected): ``offload_cache``, ``online_update_cache``,
+    ``offloading_metadata``, ``diag_sliding_window_indices``.
     Returns (context [B, tokens, H, D], metadata of the last call)."""
-    if offload_cache is not None:
-        raise NotImplementedError("the host-offload cache is not built")
-    if hip_config.using_extend:
-        raise NotImplementedError("in-kernel RoPE (using_extend) is not built: configure using_extend = false")
+    if offload_cache is not None or online_update_cache or offloading_metadata is not None:
+        raise NotImplementedError("the host-offload cache (offload_cache / online_update_cache / offloading_metadata) is not built")
+    if diag_sliding_window_indices is not None:
+        raise NotImplementedError("diag_sliding_window_indices is not built")
     N, num_heads, hidden = query.shape
     if N % batch_size:
         raise ValueError(f"{N} query tokens are not a multiple of the batch size {batch_size}")
@@ -351,6 +369,7 @@ def forward_paged_hip(query: Tensor, sm_scale: float, batch_size: int, k_cache: 
     if is_decode and dst_len != 1:
         raise ValueError("a decode step has one query token per request")
     layer = hip_config.layer_config(layer_id, is_decode)
+    is_dense = layer_id in hip_config.dense_layers
     query = query.view(batch_size, dst_len, num_heads, hidden)
     if query_for_mask is not None:
         query_for_mask = query_for_mask.view(batch_size, -1, num_heads, hidden)
@@ -365,19 +384,29 @@ def forward_paged_hip(query: Tensor, sm_scale: float, batch_size: int, k_cache: 
             raise ValueError("k_cache and v_cache must be [tokens, kv_heads, head_dim] pools of q's head_dim")
         k_cache = k_cache.view(k_cache.shape[0], 1, k_cache.shape[1], hidden)
         v_cache = v_cache.view(v_cache.shape[0], 1, v_cache.shape[1], hidden)
+    elif k is None:
+        raise ValueError("neither k_cache nor k was given")
     block_table = req_to_tokens.index_select(0, req_pool_indices)
     if block_table.shape[0] != batch_size:
         raise ValueError("req_pool_indices must name one request per batch entry")
     head_dim = k_cache.shape[-1] if k_cache is not None else k.shape[-1]
+    # statistics are gathered whenever the mask is (re)estimated (paged_hip.py:399-405)
+    require_stats = (cached_metadata is None or cached_metadata.indices is None
+                     or os.getenv("HIP_DISABLE_COMPUTE_STATISTICS", "1") == "0")
+    scan_backend = layer.scan_extend_backend
+    if scan_backend is None:   # paged_hip.py:433-441
+        scan_backend = "relative" if hip_config.apply_v_dot else ("streaming" if is_dense else "relative")
 
     def make_args(position_ids: Tensor, window: int) -> HiPAttentionArgs:
         return HiPAttentionArgs(
             k_cache=k_cache, v_cache=v_cache, block_table=block_table, cache_seq_lens=seq_lens, position_ids=position_ids,
             block_size_k=32 if head_dim > 128 else 64, sliding_window_size=window, sink_token_size=layer.sink_token_size,
-            using_extend=False, need_apply_rope=False, logit_softcap=logit_cap if logit_cap != 0.0 else None,
+            using_extend=hip_config.using_extend, need_apply_rope=hip_config.using_extend, rope_cos=rope_cos, rope_sin=rope_sin,
+            logit_softcap=logit_cap if logit_cap != 0.0 else None,
             second_stage_k=layer.second_stage_k, stages=layer.stages, model_context_length=orig_context_len,
             extend_context_length=max_context_len, block_sparse_block_size_q=hip_config.block_sparse_block_size_q,
-            sa_extend_backend=layer.sa_extend_backend, require_cache_statistics=False, disable_flashdecode=not is_decode,
+            scan_extend_backend=scan_backend, sa_extend_backend=layer.sa_extend_backend,
+            require_cache_statistics=require_stats, disable_flashdecode=not is_decode,
             q_mask=(query_for_mask * sm_scale).to(query.dtype) if query_for_mask is not None else None, layer_id=layer_id)
 
     pos = positions.view(batch_size, dst_len)

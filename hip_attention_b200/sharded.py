@@ -60,12 +60,16 @@ def hip_attention_12_kv_head_parallel(q_local: Tensor, k_local: Optional[Tensor]
 
 
 def sequence_shard_args(args: HiPAttentionArgs, shard: int, n_shards: int, shard_len: int, per_shard_k: int,
-                        device) -> HiPAttentionArgs:
-    """Arguments of the operator call that covers logical shard ``shard`` of a decode step."""
+                        device, owns_window: Optional[bool] = None) -> HiPAttentionArgs:
+    """Arguments of the operator call that covers logical shard ``shard`` of a decode step.  The sink belongs to
+    shard 0, the sliding window to the last shard (``owns_window`` overrides that: with a partly filled sequence
+    it is the last shard that holds keys)."""
     a = copy.copy(args)
     a.second_stage_k = per_shard_k
     a.sink_token_size = args.sink_token_size if shard == 0 else 0
-    a.sliding_window_size = args.sliding_window_size if shard == n_shards - 1 else 0
+    if owns_window is None:
+        owns_window = shard == n_shards - 1
+    a.sliding_window_size = args.sliding_window_size if owns_window else 0
     a.position_ids = None
     a.extend_context_length = shard_len
     # the flash-decode path of the reference cannot run without a sink (it divides by the number of
@@ -91,36 +95,77 @@ def merge_shard_partials(outs: Tensor, lses: Tensor, dtype: torch.dtype) -> Tens
 
 def hip_attention_12_sequence_sharded(q: Tensor, shard_kv: Sequence[Tuple], args: HiPAttentionArgs, *, n_shards: int,
                                       shard_len: int, per_shard_k: int, first_shard: int = 0,
-                                      cached: Optional[List] = None, group=None):
+                                      cached: Optional[List] = None, group=None, seq_len: Optional[int] = None):
     """Decode step over a key sequence cut into ``n_shards`` logical shards.
 
-    ``shard_kv`` lists this rank's shards in order, each ``(k, v)`` dense slices [B, shard_len, HKV, D]
+    ``shard_kv`` lists this rank's shards in order, each ``(k, v)`` dense slices [B, live length, HKV, D]
     or ``(k_cache, v_cache, block_table, cache_seq_lens)``; ``first_shard`` is the global index of the
-    first one.  Ranks hold ``n_shards / world`` consecutive shards.  Returns
-    ``(context [B, 1, H, D], list of per-shard metadata)``; passing that list back as ``cached`` reuses
-    the masks.
+    first one.  Ranks hold ``n_shards / world`` consecutive shards.  ``seq_len`` is the live length of the whole
+    sequence (default ``n_shards * shard_len``): the last live shard may be partly filled -- its query position
+    and chunk grid follow its live length -- and shards beyond it hold no keys.  The sliding window belongs to
+    the last live shard.  Neighbouring full shards without sink and window that address the same page pool run
+    as ONE batched operator call (they are independent sequences with identical arguments).  Returns
+    ``(context [B, 1, H, D], list of metadata, one entry per operator call)``; passing that list back as
+    ``cached`` reuses the masks.
     """
     from .operator import hip_attention_impl
     if q.shape[1] != 1:
         raise ValueError("sequence sharding is a decode path (one query row)")
-    outs, lses, mds = [], [], []
+    B = q.shape[0]
+    total = n_shards * shard_len if seq_len is None else int(seq_len)
+    if not 0 < total <= n_shards * shard_len:
+        raise ValueError(f"seq_len {total} outside (0, {n_shards * shard_len}]")
+    last_live = (total - 1) // shard_len
+    live = [max(0, min(shard_len, total - (first_shard + j) * shard_len)) for j in range(len(shard_kv))]
     for j, kv in enumerate(shard_kv):
+        if len(kv) == 2 and live[j] > 0 and kv[0].shape[1] != live[j]:
+            raise ValueError(f"shard {first_shard + j}: dense slice of {kv[0].shape[1]} keys, live length {live[j]}")
+
+    def plain(j):   # a full shard without sink and window on a page pool: can share a call with its neighbours
         s = first_shard + j
-        a = sequence_shard_args(args, s, n_shards, shard_len, per_shard_k, q.device)
-        pos = torch.full((q.shape[0], 1), shard_len - 1, dtype=torch.int64, device=q.device)
-        a.position_ids = pos
+        return (len(shard_kv[j]) == 4 and live[j] == shard_len and s != last_live
+                and (s != 0 or args.sink_token_size == 0))
+
+    groups, j = [], 0
+    while j < len(shard_kv):
+        e = j + 1
+        if plain(j):
+            while e < len(shard_kv) and plain(e) and shard_kv[e][0] is shard_kv[j][0] and shard_kv[e][1] is shard_kv[j][1] \
+                    and shard_kv[e][2].shape == shard_kv[j][2].shape:
+                e += 1
+        groups.append((j, e))
+        j = e
+    outs, lses, mds = [], [], []
+    for gi, (j0, j1) in enumerate(groups):
+        m = j1 - j0
+        if live[j0] == 0:   # beyond the live sequence: an empty partial
+            outs.append(torch.zeros((1,) + tuple(q.shape), dtype=torch.float32, device=q.device))
+            lses.append(torch.full((1, B, 1, q.shape[2]), float("-inf"), dtype=torch.float32, device=q.device))
+            mds.append(None)
+            continue
+        s = first_shard + j0
+        a = sequence_shard_args(args, s, n_shards, live[j0], per_shard_k, q.device, owns_window=s == last_live)
+        a.position_ids = torch.full((m * B, 1), live[j0] - 1, dtype=torch.int64, device=q.device)
+        kv = shard_kv[j0]
         if len(kv) == 2:
             k, v = kv
+            qq = q
         else:
             k = v = None
-            a.k_cache, a.v_cache, a.block_table, a.cache_seq_lens = kv
+            a.k_cache, a.v_cache = kv[0], kv[1]
+            if m == 1:
+                a.block_table, a.cache_seq_lens, qq = kv[2], kv[3], q
+            else:
+                a.block_table = torch.cat([shard_kv[j][2] for j in range(j0, j1)], 0)
+                a.cache_seq_lens = torch.cat([shard_kv[j][3] for j in range(j0, j1)], 0)
+                qq = q.repeat(m, 1, 1, 1)
             a.update_flags()
-        o, md, lse = hip_attention_impl(q, k, v, a, None if cached is None else cached[j], return_lse=True)
-        outs.append(o.float())
-        lses.append(lse)
+        o, md, lse = hip_attention_impl(qq, k, v, a, None if cached is None else cached[gi], return_lse=True)
+        outs.append(o.float().view(m, B, 1, q.shape[2], q.shape[3]))
+        lses.append(lse.view(m, B, 1, q.shape[2]))
         mds.append(md)
-    po = torch.stack(outs)   # [S_local, B, 1, H, D]
-    pl = torch.stack(lses)   # [S_local, B, 1, H]
+    po = torch.cat(outs)   # [S_local, B, 1, H, D]
+    pl = torch.cat(lses)   # [S_local, B, 1, H]
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         world = dist.get_world_size(group)
         go = torch.empty((world,) + tuple(po.shape), dtype=po.dtype, device=po.device)

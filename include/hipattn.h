@@ -248,6 +248,11 @@ int hipattn_widen_i32(const int32_t* src, int64_t* dst, int64_t count, void* str
  */
 int hipattn_debug_bounded_wait(uint32_t* status, void* stream);
 
+/* Number of kernels this library has launched in this process so far (host-side counter; every launch
+ * site increments it).  No counterpart in the reference.  Benchmarks report the difference across
+ * their timed region. */
+uint64_t hipattn_launch_count(void);
+
 const char* hipattn_error_string(void);
 int hipattn_abi_version(void);
 

@@ -83,6 +83,7 @@ class OracleConfig:
     second_stage_k: int
     block_size_k: int = 64  # BLOCK_CHUNK seed, ``attention_extend.py:1970``
     softcap: Optional[float] = None  # logit soft-cap of the attention kernels
+    bsa_block_q: Optional[int] = None  # block_sparse_block_size_q when smaller than the estimator's query block
 
 
 class DenseKV:
@@ -455,6 +456,15 @@ def hip_attention_oracle(q, k, v, pos, cfg: OracleConfig, *, paged=None, restart
         ksrc, vsrc = DenseKV(k), DenseKV(v)
     if mask is None:
         mask = estimate_mask(q, ksrc, pos, cfg, restart=restart, keep_stage_outputs=keep_stage_outputs)
+        bq, TQ = mask.block_size_q, q.shape[1]
+        if cfg.bsa_block_q and cdiv(TQ, cfg.bsa_block_q) != cdiv(TQ, bq):
+            # break the mask down to the attention block size (``attention_extend.py:3035-3051``)
+            assert bq % cfg.bsa_block_q == 0
+            rep = bq // cfg.bsa_block_q
+            mask.indices, mask.ks = mask.indices.repeat_interleave(rep, 1), mask.ks.repeat_interleave(rep, 1)
+            mask.ks_count = mask.ks_count.repeat_interleave(rep, 1)
+            mask.ks_start_end = mask.ks_start_end.repeat_interleave(rep, 1)
+            mask.block_size_q = cfg.bsa_block_q
     sw_attn = max(0, cfg.sw - cfg.stages[0].chunk_size) + cfg.stages[0].chunk_size
     out = attention_on_mask(q, ksrc, vsrc, pos, mask, sink=cfg.sink, sw=sw_attn, dtype=out_dtype, softcap=cfg.softcap)
     return out, mask
@@ -462,4 +472,4 @@ def hip_attention_oracle(q, k, v, pos, cfg: OracleConfig, *, paged=None, restart
 
 def config_from_case(c) -> OracleConfig:
     return OracleConfig(stages=[OracleStage(*s) for s in c["stages"]], sink=c["sink"], sw=c["sw"],
-                        second_stage_k=c["second_k"], softcap=c.get("softcap"))
+                        second_stage_k=c["second_k"], softcap=c.get("softcap"), bsa_block_q=c.get("bsa_bq"))

@@ -57,6 +57,16 @@ CASES = {
                          second_k=128, stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=22, softcap=1.5),
     "softcap_decode_fp16": dict(B=2, TQ=1, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128,
                                 second_k=128, stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=23, softcap=1.5),
+    # head dim 128, three stages with 16 and 64 pooled query rows: the tcgen05 scan and attention kernels
+    "d128_fp16": dict(B=1, TQ=192, T=2048, H=4, HKV=2, D=128, dtype="fp16", sink=32, sw=128,
+                      second_k=256, stages=[(64, 4, 64, None), (64, 4, 16, 512), (64, 1, 8, 256)], seed=24),
+    # query blocks of 128 rows, eight query heads on one KV head, head dim 128 (the large-GQA prefill shape)
+    "bq128_fp16": dict(B=1, TQ=256, T=2048, H=8, HKV=1, D=128, dtype="fp16", sink=32, sw=128,
+                       second_k=256, stages=[(128, 4, 64, None), (128, 4, 16, 512), (128, 1, 8, 256)], seed=25),
+    # attention blocks of 16 rows under estimator blocks of 64, ragged last block: the returned mask is
+    # broken down to the attention block size (repeat-interleave)
+    "bsa16_fp16": dict(B=1, TQ=100, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128,
+                       second_k=128, stages=[(64, 2, 32, None), (64, 1, 8, 256)], seed=26, bsa_bq=16),
     # benchmark configuration 1 shape (fp32, 4096 x 4096, 8/2 heads, D 64)
     "config1_fp32": dict(B=1, TQ=4096, T=4096, H=8, HKV=2, D=64, dtype="fp32", sink=64, sw=256,
                          second_k=512, stages=[(64, 4, 32, None), (64, 1, 8, 1024)], seed=101,

@@ -119,7 +119,7 @@ def test_paged_equals_dense(page, tq):
         assert torch.equal(out_p, out_d)
 
 
-@pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "decode_fp16"])
+@pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "decode_fp16", "bsa16_fp16", "d128_fp16"])
 def test_cached_mask_and_stage_restart(name):
     """Reference invariant (tests/v1_2/test_gen3_stage_caching.py:170-186): replaying any prefix of the
     stage caches, or the whole cached mask, reproduces the output (sum of squared differences < 1e-8)."""
@@ -214,6 +214,64 @@ def test_invalid_arguments_raise_before_launch():
         hip_attention_12(q.cpu(), k.cpu(), k.cpu(), HiPAttentionArgs())
 
 
+@pytest.mark.parametrize("tq", [1, 70])
+def test_query_position_beyond_dense_keys_is_clamped_and_flagged(tq):
+    """Dense K / V and a query position at or beyond their length: sink and window entries stop at T (no row past
+    the end of the tensors is read -- the rows behind them hold NaN here and would poison the output), the status
+    word reports it, and the result is the softmax over the admitted keys below T."""
+    from hip_attention_b200 import hip_attention_impl, read_status
+    q, k, v, pos, c, cfg, _ = case_inputs("ragged_fp16", torch.bfloat16)
+    B, T = k.shape[0], k.shape[1]
+    q = q[:, :tq].contiguous()
+    big_k = torch.full((B, T + 64) + tuple(k.shape[2:]), float("nan"), dtype=k.dtype, device="cuda")
+    big_v = torch.full_like(big_k, float("nan"))
+    big_k[:, :T], big_v[:, :T] = k.cuda(), v.cuda()
+    kd, vd = big_k[:, :T], big_v[:, :T]          # views: the allocation continues behind them
+    pos_far = (torch.arange(tq)[None] + T + 5 - (tq - 1)).expand(B, tq).contiguous()   # last row at T + 5
+    read_status("cuda")
+    out, md = hip_attention_impl(q.cuda(), kd, vd, make_args(c, pos_far.cuda()))
+    torch.cuda.synchronize()
+    assert read_status("cuda") & 2
+    assert torch.isfinite(out.float()).all()
+    m = O.OracleMask(md.indices.cpu(), md.ks.cpu(), md.ks_count.cpu(), md.ks_start_end.cpu())
+    m.block_size_k, m.block_size_q = cfg.stages[-1].chunk_size, cfg.stages[-1].block_size_q
+    ref = _attention_below_T(q, k, v, pos_far, m, cfg)
+    _check_out(out, ref, torch.bfloat16)
+
+
+def _attention_below_T(q, k, v, pos, m, cfg):
+    """fp64 softmax over the attended set of ``oracle.attended_columns`` cut at the number of keys."""
+    B, TQ, H, D = q.shape
+    T, G = k.shape[1], H // k.shape[2]
+    sw = max(cfg.sw, cfg.stages[0].chunk_size)
+    bq = m.block_size_q
+    out = torch.zeros(B, TQ, H, D, dtype=torch.float64)
+    for b in range(B):
+        for d in range(-(-TQ // bq)):
+            r0, r1 = d * bq, min(TQ, (d + 1) * bq)
+            for h in range(H):
+                cols, allow = O.attended_columns(m.indices[b * H + h, d], int(m.ks[b * H + h, d]), pos[b, r0:r1], sink=cfg.sink,
+                                                 sw=sw, c_last=m.block_size_k, T=T)
+                keep = cols < T
+                cols, allow = cols[keep], allow[:, keep]
+                s = q[b, r0:r1, h].double() @ k[b, cols, h // G].double().T
+                s = s.masked_fill(~allow, float("-inf"))
+                out[b, r0:r1, h] = torch.nan_to_num(torch.softmax(s, -1)) @ v[b, cols, h // G].double()
+    return out
+
+
+def test_unbuilt_stage_flags_are_refused():
+    """A stage that switches off realignment, score reset or the position sort selects a branch the kernels do not
+    have: the call must say so instead of returning a different mask."""
+    from hip_attention_b200 import HiPAttentionArgs, ScanStage, hip_attention_12
+    q = torch.zeros(1, 8, 4, 64, device="cuda", dtype=torch.bfloat16)
+    k = torch.zeros(1, 4096, 2, 64, device="cuda", dtype=torch.bfloat16)
+    for flag in ("require_realign_index", "require_reset_score", "require_post_sort"):
+        stages = [ScanStage(64, 4, 256, None, 1), ScanStage(64, 4, 32, 2048, 1, **{flag: False})]
+        with pytest.raises(NotImplementedError):
+            hip_attention_12(q, k, k, HiPAttentionArgs(stages=stages, second_stage_k=512))
+
+
 def test_bad_page_table_is_clamped_and_flagged():
     """Out-of-range block-table entries never fault: they read page 0 and set a status bit."""
     from cases import make_paged
@@ -245,10 +303,10 @@ def _scan_check_run(dtype, TQ=512, T=16384):
     return stats.cpu(), md, (q, k, v, w)
 
 
-@pytest.mark.parametrize("scan_kernel", ["auto", "chunks", "dense", "rounds", "mma"])
+@pytest.mark.parametrize("scan_kernel", ["auto", "mma"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_scan_tensor_core_path_is_exact(dtype, scan_kernel, monkeypatch):
-    """The tensor-core scans (tcgen05 whole-chunk and round-based, mma.sync) take a shortcut only where rounding is certain.  In
+    """The tensor-core scans (tcgen05, mma.sync) take a shortcut only where rounding is certain.  In
     check mode every key is also scored by the strict definition: no shortcut may be wrong, and the
     observed deviation must stay well inside the assumed error radius.  Strict and automatic modes give
     identical masks."""
@@ -279,7 +337,7 @@ def test_scan_tensor_core_path_is_exact(dtype, scan_kernel, monkeypatch):
 ])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_scan_kernels_agree(shape, dtype, monkeypatch):
-    """The scan kernels (tcgen05 whole-chunk scoring, tcgen05 round by round, mma.sync, strict) give
+    """The scan kernels (tcgen05, mma.sync, strict) give
     identical per-head bounds and scores at every stage, dense and through a permuted page pool."""
     import bench
     from cases import make_paged
@@ -291,9 +349,6 @@ def test_scan_kernels_agree(shape, dtype, monkeypatch):
     q, k, v = bench.make_qkv(w, "cuda")
     results = {}
     for name, env in (("auto", {"HIPATTN_SCAN_KERNEL": "auto", "HIPATTN_SCAN_MODE": "auto"}),
-                      ("chunks", {"HIPATTN_SCAN_KERNEL": "chunks", "HIPATTN_SCAN_MODE": "auto"}),
-                      ("dense", {"HIPATTN_SCAN_KERNEL": "dense", "HIPATTN_SCAN_MODE": "auto"}),
-                      ("rounds", {"HIPATTN_SCAN_KERNEL": "rounds", "HIPATTN_SCAN_MODE": "auto"}),
                       ("mma", {"HIPATTN_SCAN_KERNEL": "mma", "HIPATTN_SCAN_MODE": "auto"}),
                       ("strict", {"HIPATTN_SCAN_KERNEL": "auto", "HIPATTN_SCAN_MODE": "strict"})):
         for k_, v_ in env.items():
@@ -313,7 +368,7 @@ def test_scan_kernels_agree(shape, dtype, monkeypatch):
                            extend_context_length=w["T"])
     out_p, md_p = hip_attention_impl(q, None, None, args)
     ref_st, ref_md = results["strict"]
-    for name in ("auto", "chunks", "dense", "rounds", "mma"):
+    for name in ("auto", "mma"):
         st, md = results[name]
         assert len(st) == len(ref_st)
         for i, (a, b_) in enumerate(zip(st, ref_st)):
@@ -323,7 +378,7 @@ def test_scan_kernels_agree(shape, dtype, monkeypatch):
     assert torch.equal(md_p.indices, ref_md.indices) and torch.equal(md_p.ks, ref_md.ks)
 
 
-@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_ws", "mma"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
 @pytest.mark.parametrize("bq,tq,hkv", [(64, 300, 2), (128, 300, 2), (64, 64, 4), (64, 1024, 1)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_prefill_head_dim_128_matches_oracle(kernel, bq, tq, hkv, dtype, monkeypatch):

@@ -97,9 +97,11 @@ def test_forward_paged_hip_matches_the_reference():
     T = c["T"]
 
     def call(q, positions, seq_len, is_decode, cached):
-        return forward_paged_hip(q, c["sm_scale"], 1, x["k_pool"], x["v_pool"], positions.cuda(), torch.tensor([seq_len], device="cuda"),
-                                 x["req_to_tokens"], x["req_pool_indices"], c["layer_id"], 0.0, c["model_context"], T, cfg,
-                                 cached_metadata=cached, is_decode=is_decode)
+        # positional, in the reference's order (paged_hip.py:35-62)
+        return forward_paged_hip(q, c["sm_scale"], 1, x["k_pool"], x["v_pool"], None, positions.cuda(),
+                                 torch.tensor([seq_len], device="cuda"), x["req_to_tokens"], x["req_pool_indices"], None, None,
+                                 c["layer_id"], 0.0, c["model_context"], T, not is_decode, cfg, cached, None, None, False, None,
+                                 is_decode)
 
     tol = 3e-3
     p0 = T - 3 - c["chunk"]
@@ -211,9 +213,13 @@ def test_decode_steps_through_the_metadata_pool_match_the_reference():
     T, lid = c["T"], c["layer_id"]
 
     def call(q, position, seq_len, cached):
-        return forward_paged_hip(q, c["sm_scale"], 1, x["k_pool"], x["v_pool"], torch.tensor([position], device="cuda"),
-                                 torch.tensor([seq_len], device="cuda"), x["req_to_tokens"], x["req_pool_indices"], lid, 0.0,
-                                 c["model_context"], T, cfg, cached_metadata=cached, is_decode=True)
+        # by keyword, exactly as the fixture generator calls the reference
+        return forward_paged_hip(
+            query=q, sm_scale=c["sm_scale"], batch_size=1, k_cache=x["k_pool"], v_cache=x["v_pool"], offload_cache=None,
+            positions=torch.tensor([position], device="cuda"), seq_lens=torch.tensor([seq_len], device="cuda"),
+            req_to_tokens=x["req_to_tokens"], req_pool_indices=x["req_pool_indices"], rope_cos=None, rope_sin=None, layer_id=lid,
+            logit_cap=0.0, orig_context_len=c["model_context"], max_context_len=T, is_prefill=False, hip_config=cfg,
+            cached_metadata=cached, is_decode=True)
 
     tol = 3e-3
     out0, md0 = call(x["q_decode"][0], T - 3, T - 2, pool.get_hip_metadata_cache(lid, 1, 1, -1))
@@ -226,3 +232,30 @@ def test_decode_steps_through_the_metadata_pool_match_the_reference():
     assert np.abs(out1.float().cpu().numpy() - g["decode1_out"]).max() < tol
     out2, _ = call(x["q_decode"][2], T - 1, T, pool.get_hip_metadata_cache(lid, 1, 1, None))
     assert np.abs(out2.float().cpu().numpy() - g["decode2_out"]).max() < tol
+
+
+def test_forward_paged_hip_has_the_reference_parameter_list():
+    """A caller written against the reference passes positionally: the names and their order must be the
+    reference's (paged_hip.py:35-62), and the unbuilt options must be refused, not silently dropped."""
+    import inspect
+    from hip_attention_b200 import HiPAttentionConfig, cuda_graph_capture_configs, forward_paged_hip
+    names = list(inspect.signature(forward_paged_hip).parameters)
+    assert names == ["query", "sm_scale", "batch_size", "k_cache", "v_cache", "offload_cache", "positions", "seq_lens",
+                     "req_to_tokens", "req_pool_indices", "rope_cos", "rope_sin", "layer_id", "logit_cap", "orig_context_len",
+                     "max_context_len", "is_prefill", "hip_config", "cached_metadata", "k", "v", "online_update_cache",
+                     "offloading_metadata", "is_decode", "query_for_mask", "diag_sliding_window_indices"]
+    params = inspect.signature(forward_paged_hip).parameters
+    assert all(params[n].default is inspect.Parameter.empty for n in names[:18])
+    assert params["cached_metadata"].default is None and params["is_decode"].default is False
+    cfg = HiPAttentionConfig()
+    assert cuda_graph_capture_configs(cfg) == [(None,), (0,), (1,), (2,)]
+    q = torch.zeros(2, 4, 64)
+    tbl = torch.zeros(1, 8, dtype=torch.int64)
+    common = (q, 1.0, 1, None, None)
+    rest = (torch.zeros(2, dtype=torch.int64), torch.tensor([8]), tbl, torch.tensor([0]), None, None, 0, 0.0, 64, 64, True, cfg)
+    with pytest.raises(NotImplementedError):
+        forward_paged_hip(*common, object(), *rest)
+    with pytest.raises(NotImplementedError):
+        forward_paged_hip(*common, None, *rest, online_update_cache=True)
+    with pytest.raises(NotImplementedError):
+        forward_paged_hip(*common, None, *rest, diag_sliding_window_indices=torch.zeros(1))

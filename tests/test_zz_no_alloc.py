@@ -69,8 +69,9 @@ def test_noalloc_decode_equals_regular_entry_point_twice(dtype):
         bp = _params(q, k, v, pos, c, md, ref, n_splits)
         bp.part_o, bp.part_lse = part_o.data_ptr(), part_lse.data_ptr()
         L.check(lib.hipattn_bsa_attention(C.byref(bp), stream), "bsa_attention")
+        ref_lse = torch.empty((B, TQ, H), dtype=torch.float32, device=q.device)
         L.check(lib.hipattn_merge_partials(part_o.data_ptr(), part_lse.data_ptr(), B * H, n_splits, D, bp.dtype,
-                                           ref.data_ptr(), D, None, stream), "merge_partials")
+                                           ref.data_ptr(), D, ref_lse.data_ptr(), stream), "merge_partials")
         # allocation-free path: outputs only
         out = torch.empty_like(q)
         lse = torch.empty((B, TQ, H), dtype=torch.float32, device=q.device)
@@ -81,8 +82,29 @@ def test_noalloc_decode_equals_regular_entry_point_twice(dtype):
         assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
         assert torch.equal(out, ref), f"call {call}: max diff {(out.float() - ref.float()).abs().max().item()}"
-        assert torch.isfinite(lse).all()
+        assert torch.isfinite(lse).all() and torch.equal(lse, ref_lse)
         assert out.float().abs().max().item() > 0
+
+
+def test_noalloc_decode_single_range_bypasses_the_array():
+    """With one key range there are no partial results: the call goes straight to the regular kernel and must
+    give what ``hipattn_bsa_attention`` gives, log-sum-exp included."""
+    from hip_attention_b200 import _lib as L
+    lib = L.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    q, k, v, pos, c, md = _decode_problem(torch.bfloat16)
+    B, TQ, H, D = q.shape
+    ref, out = torch.empty_like(q), torch.empty_like(q)
+    ref_lse = torch.empty((B, TQ, H), dtype=torch.float32, device=q.device)
+    lse = torch.empty_like(ref_lse)
+    bp = _params(q, k, v, pos, c, md, ref, 1)
+    bp.lse_out = ref_lse.data_ptr()
+    L.check(lib.hipattn_bsa_attention(C.byref(bp), stream), "bsa_attention")
+    bp2 = _params(q, k, v, pos, c, md, out, 1)
+    bp2.lse_out = lse.data_ptr()
+    L.check(lib.hipattn_bsa_decode_noalloc(C.byref(bp2), stream), "bsa_decode_noalloc")
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref) and torch.equal(lse, ref_lse)
 
 
 def test_noalloc_decode_rejects_oversized_requests():
@@ -97,4 +119,14 @@ def test_noalloc_decode_rejects_oversized_requests():
     assert b"exceeds the built-in scratch" in lib.hipattn_error_string()
     bp = _params(q, k, v, pos, c, md, out, 4)
     bp.TQ = 2
+    assert lib.hipattn_bsa_decode_noalloc(C.byref(bp), None) == 1
+    # the other refusals: more key ranges than the merge supports, no output, an output that is not contiguous
+    bp = _params(q, k, v, pos, c, md, out, 65)
+    assert lib.hipattn_bsa_decode_noalloc(C.byref(bp), None) == 1
+    bp = _params(q, k, v, pos, c, md, out, 4)
+    bp.out = None
+    assert lib.hipattn_bsa_decode_noalloc(C.byref(bp), None) == 1
+    wide = torch.empty(q.shape[:-1] + (2 * q.shape[-1],), dtype=q.dtype, device=q.device)
+    bp = _params(q, k, v, pos, c, md, wide[..., : q.shape[-1]], 4)
+    assert bp.o_stride_h != q.shape[-1]
     assert lib.hipattn_bsa_decode_noalloc(C.byref(bp), None) == 1

@@ -12,7 +12,7 @@ def make_args(c, pos=None, **kw):
         second_stage_k=c["second_k"],
         stages=[ScanStage(stage_block_size_q=bq, stage_block_stride_q=sq, stage_chunk_size=cs, stage_k=sk, stage_stride=1)
                 for (bq, sq, cs, sk) in c["stages"]],
-        block_sparse_block_size_q=c["stages"][-1][0], using_extend=False, need_apply_rope=False,
+        block_sparse_block_size_q=c.get("bsa_bq", c["stages"][-1][0]), using_extend=False, need_apply_rope=False,
         disable_flashdecode=c.get("disable_flashdecode", False), logit_softcap=c.get("softcap"), **kw)
 
 
