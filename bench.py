@@ -127,9 +127,11 @@ def oracle_config(w: dict):
     return O.OracleConfig(stages=st, sink=w["sink"], sw=w["sw"], second_stage_k=w["keep"][-1])
 
 
-def scan_bytes(w: dict, heads: int) -> float:
+def scan_bytes(w: dict, heads: int, fetched: bool = False) -> float:
     """Algorithmic bytes of the scan stages of one call: active chunks x (log2(chunk) + 1) rounds x 2 key
-    rows x D x element size, summed over (batch, query block, head, stage)."""
+    rows x D x element size, summed over (batch, query block, head, stage).  ``fetched``: the rows the kernels
+    actually gather -- a candidate that repeats the previous round's winner is not fetched again, which removes
+    three of the 2 (log2(chunk) + 1) rows of a chunk."""
     eb = 4 if w["dtype"] == "fp32" else 2
     B, TQ, T, D, bq = w["B"], w["TQ"], w["T"], w["D"], w["bq"]
     c0 = w["chunks"][0]
@@ -142,7 +144,10 @@ def scan_bytes(w: dict, heads: int) -> float:
         act = min(n0, max(0, (pt - w["sink"]) // c0 + 1)) if pt >= w["sink"] else 0
         n = n0
         for i, c in enumerate(w["chunks"]):
-            total += act * (int(math.log2(c)) + 1) * 2 * D * eb
+            rows = (int(math.log2(c)) + 1) * 2
+            if fetched:
+                rows -= 3 if c >= 4 else (2 if c >= 2 else 0)
+            total += act * rows * D * eb
             if i + 1 < len(w["chunks"]):
                 keep = min(w["keep"][i] // c, n)
                 split = c // w["chunks"][i + 1]
@@ -151,7 +156,7 @@ def scan_bytes(w: dict, heads: int) -> float:
     return total * B * heads
 
 
-def scan_flops(w: dict, heads: int) -> float:
+def scan_flops(w: dict, heads: int, fetched: bool = False) -> float:
     """Tensor-core FLOPs of the scan stages: every gathered key row is multiplied with the pooled query rows
     of its (query block, head): 2 * rows * D per key row."""
     eb = 4 if w["dtype"] == "fp32" else 2
@@ -159,7 +164,7 @@ def scan_flops(w: dict, heads: int) -> float:
     for i, c in enumerate(w["chunks"]):
         w1 = dict(w, chunks=w["chunks"][:i + 1], keep=w["keep"][:max(i, 1)])
         w0 = dict(w, chunks=w["chunks"][:i], keep=w["keep"][:max(i - 1, 1)]) if i else None
-        stage_bytes = scan_bytes(w1, heads) - (scan_bytes(w0, heads) if w0 else 0.0)
+        stage_bytes = scan_bytes(w1, heads, fetched) - (scan_bytes(w0, heads, fetched) if w0 else 0.0)
         rows = w["bq"] // w["strides"][i]
         total += stage_bytes / (w["D"] * eb) * 2.0 * rows * w["D"]
     return total
@@ -581,8 +586,12 @@ def run_prefill(a, w, dev, rank, world):
                  "traffic": NCU_DRAM_BYTES_PER_SCAN_LAUNCH.get((a.workload, world, w["TQ"])),
                  "traffic_source": NCU_TRAFFIC_SOURCE if (a.workload, world, w["TQ"]) in NCU_DRAM_BYTES_PER_SCAN_LAUNCH else None,
                  "flops_per_launch": sf / max(1, n_scan), "launch_ms": scan_ms / max(1, n_scan),
-                 "gathered_bytes_per_launch": sb / max(1, n_scan),
-                 "gather_gbs": sb / 1e9 / (scan_ms / 1e3) if scan_ms > 0 else None,
+                 "algorithm": "flops and bytes of the reference's rounds (two key rows per chunk, head and round); the "
+                              "kernels skip rows whose score is already known, see the *_executed figures",
+                 "flops_executed_per_launch": scan_flops(w, heads_local, True) / max(1, n_scan),
+                 "executed_tflops": scan_flops(w, heads_local, True) / 1e12 / (scan_ms / 1e3) if scan_ms > 0 else None,
+                 "gathered_bytes_per_launch": scan_bytes(w, heads_local, True) / max(1, n_scan),
+                 "gather_gbs": scan_bytes(w, heads_local, True) / 1e9 / (scan_ms / 1e3) if scan_ms > 0 else None,
                  "gather_served_by": "L2; the gather rate is not an HBM figure and may exceed the HBM copy peak",
                  "hbm_peak_gbs": hbm_peak}
     att_roof = {"kernel": "bsa_tcgen05 prefill attention kernel", "bound": "tensor", "achieved": att_tf, "peak": tc_peak,

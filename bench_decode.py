@@ -94,8 +94,8 @@ def fetched_scan_bytes(w, heads):
         r = int(math.log2(c)) + 1
         if 4 <= c <= 32 and c <= hb * 2 * r:
             total += rounds_bytes * c / (2.0 * r * hb)     # c rows per chunk and head batch instead of 2 r per head
-        else:
-            total += rounds_bytes
+        else:                                              # rounds: a candidate that repeats the last winner is not fetched
+            total += bench.scan_bytes(w1, heads, True) - (bench.scan_bytes(w0, heads, True) if w0 else 0.0)
     return total
 
 

@@ -142,12 +142,19 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
   for (int o = 16; o > 0; o >>= 1) max_rounds = max(max_rounds, __shfl_xor_sync(0xffffffffu, max_rounds, o));
 
   float score = HIPATTN_SCORE_INIT;
+  // The candidate that won the previous round and its score.  When the halved chunk proposes the same key again (both
+  // candidates of the last round, one of the round before it) the score is known -- the same key against the same
+  // pooled queries -- and the row is not fetched again.
+  int won_t = -1;
+  float won_score = 0.f;
 
   for (int it = 0; it < max_rounds; ++it) {
     const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
     if (!__any_sync(0xffffffffu, act)) break;  // a chunk that is inactive now stays inactive
     const int mid = (left + right) >> 1;
     int tl = (left + mid) >> 1, tr = (mid + right) >> 1;
+    const int tl_asked = tl, tr_asked = tr;
+    const bool known_l = act && tl == won_t, known_r = act && tr == won_t;
     const char* src_l = nullptr;
     const char* src_r = nullptr;
     if (act) {
@@ -156,8 +163,14 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
         tl = min(max(tl, 0), p.T - 1);
         tr = min(max(tr, 0), p.T - 1);
       }
-      src_l = token_row(p.k, b, tl, hkv, Elem<DT>::bytes, p.status);
-      src_r = token_row(p.k, b, tr, hkv, Elem<DT>::bytes, p.status);
+      if (!known_l) src_l = token_row(p.k, b, tl, hkv, Elem<DT>::bytes, p.status);
+      if (!known_r) src_r = token_row(p.k, b, tr, hkv, Elem<DT>::bytes, p.status);
+    }
+    if (!__any_sync(0xffffffffu, src_l != nullptr || src_r != nullptr)) {
+      // every live chunk of the warp knows both scores (both candidates are the previous winner): the round decides
+      // without touching memory; equal scores keep the right half and the chunk's best score is unchanged
+      if (act) left = mid;
+      continue;
     }
     // cooperative gather: 64 rows, kPieces lanes per row
     __syncwarp();
@@ -186,7 +199,7 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
 
     float sl = -INFINITY, sr = -INFINITY;
     if (act) {
-      for (int tile = 0; tile < ntile; ++tile) {
+      for (int tile = 0; tile < ntile && !(known_l && known_r); ++tile) {
         float accl[RT], accr[RT];
 #pragma unroll
         for (int r = 0; r < RT; ++r) accl[r] = accr[r] = 0.f;
@@ -220,9 +233,13 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
           }
         }
       }
+      if (known_l) sl = won_score;
+      if (known_r) sr = won_score;
       const bool win = sl > sr;
       if (win) right = mid; else left = mid;
       score = fmaxf(score, win ? sl : sr);
+      won_t = win ? tl_asked : tr_asked;
+      won_score = win ? sl : sr;
     }
   }
 
@@ -287,6 +304,7 @@ int dispatch_dim(const hipattn_scan_params_t& p, cudaStream_t stream) {
 
 int scan_stage_mma(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
 int scan_stage_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
+int scan_stage_regs(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
 int scan_chunks_strict(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
 int scan_prepare_keys(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* key_abs,
                       void* k_scaled, uint32_t* status, cudaStream_t stream);
@@ -317,6 +335,8 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
   HIPATTN_REQUIRE(p->mode >= HIPATTN_SCAN_AUTO && p->mode <= HIPATTN_SCAN_CHECK, HIPATTN_ERR_INVALID, "scan stage: unknown mode %d", p->mode);
   bool handled = false;
   rc = scan_chunks_strict(*p, s, &handled);
+  if (handled) return rc;
+  rc = scan_stage_regs(*p, s, &handled);
   if (handled) return rc;
   rc = scan_stage_tcgen05(*p, s, &handled);
   if (handled) return rc;

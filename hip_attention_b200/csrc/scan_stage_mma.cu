@@ -154,12 +154,17 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) max_rounds = max(max_rounds, __shfl_xor_sync(0xffffffffu, max_rounds, o));
   float score = HIPATTN_SCORE_INIT;
+  // the candidate that won the previous round and its score: proposed again, it is neither fetched nor scored again
+  int won_t = -1;
+  float won_score = 0.f;
 
   for (int it = 0; it < max_rounds; ++it) {
     const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
     if (!__any_sync(0xffffffffu, act)) break;
     const int mid = (left + right) >> 1;
     int tl = (left + mid) >> 1, tr = (mid + right) >> 1;
+    const int tl_asked = tl, tr_asked = tr;
+    const bool known_l = act && tl == won_t, known_r = act && tr == won_t;
     const char* src_l = nullptr;
     const char* src_r = nullptr;
     if (act) {
@@ -168,8 +173,13 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
         tl = min(max(tl, 0), p.T - 1);
         tr = min(max(tr, 0), p.T - 1);
       }
-      src_l = token_row(p.k, b, tl, hkv, 2, p.status);
-      src_r = token_row(p.k, b, tr, hkv, 2, p.status);
+      if (!known_l) src_l = token_row(p.k, b, tl, hkv, 2, p.status);
+      if (!known_r) src_r = token_row(p.k, b, tr, hkv, 2, p.status);
+    }
+    if (!__any_sync(0xffffffffu, src_l != nullptr || src_r != nullptr)) {
+      // every live chunk knows both scores (both candidates are the previous winner): equal scores keep the right half
+      if (act) left = mid;
+      continue;
     }
     // ---- gather the 64 candidate rows ----
     __syncwarp();
@@ -193,7 +203,7 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
 
     // ---- approximate scores on tensor cores ----
     float xl = -INFINITY, xr = -INFINITY, sl_abs = 0.f, sr_abs = 0.f;
-    if (have_abs && act) {  // precomputed key magnitudes (one per key row of the call)
+    if (have_abs && act && !(known_l && known_r)) {  // precomputed key magnitudes (one per key row of the call)
       sl_abs = p.key_abs[((int64_t)b * p.HKV + hkv) * p.T + tl];
       sr_abs = p.key_abs[((int64_t)b * p.HKV + hkv) * p.T + tr];
     }
@@ -269,8 +279,10 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
     float sl = Elem<DT>::round(xl), sr = Elem<DT>::round(xr);
     bool sure_l = Elem<DT>::round(xl - el) == Elem<DT>::round(xl + el);
     bool sure_r = Elem<DT>::round(xr - er) == Elem<DT>::round(xr + er);
-    unsigned need_l = __ballot_sync(0xffffffffu, act && (!sure_l || check));
-    unsigned need_r = __ballot_sync(0xffffffffu, act && (!sure_r || check));
+    if (known_l) sl = won_score;
+    if (known_r) sr = won_score;
+    unsigned need_l = __ballot_sync(0xffffffffu, act && !known_l && (!sure_l || check));
+    unsigned need_r = __ballot_sync(0xffffffffu, act && !known_r && (!sure_r || check));
     while (need_l | need_r) {
       const bool is_l = need_l != 0;
       const int owner = __ffs(is_l ? need_l : need_r) - 1;
@@ -290,10 +302,12 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
       }
     }
     if (act) {
-      st_keys += 2;
+      st_keys += (known_l ? 0 : 1) + (known_r ? 0 : 1);
       const bool win = sl > sr;
       if (win) right = mid; else left = mid;
       score = fmaxf(score, win ? sl : sr);
+      won_t = win ? tl_asked : tr_asked;
+      won_score = win ? sl : sr;
     }
   }
 

@@ -10,7 +10,7 @@
 // Layout of one round: a CTA of 128 threads owns 64 chunks; thread t owns ONE candidate key
 // (chunk t / 2, side t % 2).  The 128 candidate rows are gathered with 16-byte cp.async straight into
 // the 128-byte-swizzled K-major operand layout (A, M = 128); the pooled queries sit in shared memory
-// as the B operand (N = 16 / 32 / 64 rows).  D = K Q^T lands in TMEM with lane = key and
+// as the B operand (N = 16 / 32 / 64 / 128 rows).  D = K Q^T lands in TMEM with lane = key and
 // column = pooled row, so thread t reads its own lane with one tcgen05.ld and takes the row maximum
 // in registers: no shuffles, no ldmatrix, and one MMA issue per 16 head-dim elements for the whole CTA.
 //
@@ -203,6 +203,11 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
     const int my_rounds = gmax >= 1 ? 32 - __clz(gmax) : 0;
     const int cta_rounds = cta_max >= 1 ? 32 - __clz(cta_max) : 0;
     float score = HIPATTN_SCORE_INIT;
+    // The candidate that won the previous round and its score.  When the halved chunk proposes the same key again
+    // (always in the last round, for one of the two candidates in the round before it) the score is known: the same
+    // key against the same pooled queries, so the row is neither fetched nor multiplied again.
+    int won_t = -1;
+    float won_score = 0.f;
 
     for (int it = 0; it < cta_rounds; ++it) {
       // A warp goes straight from its decisions to the copies of its next 32 rows: those rows are its own (only this
@@ -211,8 +216,10 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
       const bool act = in_range && it < my_rounds && left < right && left <= pt && left >= 0;
       const int mid = (left + right) >> 1;
       int tk = side ? ((mid + right) >> 1) : ((left + mid) >> 1);
+      const int tk_asked = tk;
+      const bool known = act && tk == won_t;
       int idx = -1;
-      if (act) {
+      if (act && !known) {
         if (tk < 0 || tk >= p.T) {
           atomicOr(p.status, HIPATTN_STATUS_TOKEN_RANGE);
           tk = min(max(tk, 0), p.T - 1);
@@ -220,8 +227,9 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
         idx = (b * p.HKV + hkv) * p.T + tk;
       }
       // the key's magnitude is needed only after the MMA: requested here, its latency hides behind the row copies
-      const float s_abs = act ? __ldg(p.key_abs + idx) : 0.f;
+      const float s_abs = idx >= 0 ? __ldg(p.key_abs + idx) : 0.f;
       // ---- gather this warp's 32 rows: 8 lanes per row, 128 contiguous bytes per row and instruction ----
+      if (__any_sync(0xffffffffu, idx >= 0)) {   // a warp whose scores are all known (or inactive) copies nothing
 #pragma unroll
       for (int r0 = 0; r0 < 32; r0 += 4) {
         const int j = r0 + (lane >> 3);
@@ -233,14 +241,16 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb) cp_async16_zfill(sp + kb * K_BLOCK_BYTES, gp + kb * 128, live);
       }
+      }
       cp_async_commit();
       cp_async_wait<0>();
       fence_async_smem();
       tc_fence_before();
-      const int any = __syncthreads_or((act ? 1 : 0) | (*(volatile int*)&sh.abort ? 2 : 0));
+      const int any = __syncthreads_or((act ? 1 : 0) | (*(volatile int*)&sh.abort ? 2 : 0) | (idx >= 0 ? 4 : 0));
       if (any & 2) { aborted = true; break; }
       if (!(any & 1)) break;
-      if (tid == 0) {
+      const bool scored = (any & 4) != 0;   // somebody fetched a row: the tile is multiplied; else every score is known
+      if (scored && tid == 0) {
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -251,32 +261,41 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
         umma_commit(mbar);
       }
       __syncwarp();
-      bool ok = mbar_wait(mbar, phase, &sh.abort, p.status);
-      phase ^= 1u;
-      ok = __all_sync(0xffffffffu, ok);
-      tc_fence_after();
+      bool ok = true;
+      if (scored) {
+        ok = mbar_wait(mbar, phase, &sh.abort, p.status);
+        phase ^= 1u;
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+      }
       float x = -INFINITY;
-      if (ok) {
-        float v[NR];
-        if (NR == 16) tmem_ld16(my_tmem, v);
-        else if (NR == 32) tmem_ld32(my_tmem, v);
-        else tmem_ld64(my_tmem, v);
-        // four short maximum chains; the row mask is only paid for by a ragged last query block
+      if (ok && scored) {
+        // four short maximum chains; the row mask is only paid for by a ragged last query block.  128 pooled rows
+        // are read as two halves of 64 columns so that the live registers stay those of the 64-row variant.
+        constexpr int NLD = NR > 64 ? 64 : NR;
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (Rv >= NR) {
 #pragma unroll
-          for (int j = 0; j < NR; ++j) m4[j & 3] = fmaxf(m4[j & 3], v[j]);
-        } else {
+        for (int c0 = 0; c0 < NR; c0 += NLD) {
+          float v[NLD];
+          if (NLD == 16) tmem_ld16(my_tmem + c0, v);
+          else if (NLD == 32) tmem_ld32(my_tmem + c0, v);
+          else tmem_ld64(my_tmem + c0, v);
+          if (Rv >= NR) {
 #pragma unroll
-          for (int j = 0; j < NR; ++j)
-            if (j < Rv) m4[j & 3] = fmaxf(m4[j & 3], v[j]);
+            for (int j = 0; j < NLD; ++j) m4[j & 3] = fmaxf(m4[j & 3], v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < NLD; ++j)
+              if (c0 + j < Rv) m4[j & 3] = fmaxf(m4[j & 3], v[j]);
+          }
         }
         x = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
       const float e_ = eps_q * s_abs * 1.01f;
       float sc = Elem<DT>::round(x);
       const bool sure = Elem<DT>::round(x - e_) == Elem<DT>::round(x + e_);
-      unsigned need = __ballot_sync(0xffffffffu, act && ok && (!sure || check));
+      if (known) sc = won_score;
+      unsigned need = __ballot_sync(0xffffffffu, idx >= 0 && ok && (!sure || check));
       while (need) {
         const int owner = __ffs(need) - 1;
         need &= need - 1;
@@ -292,12 +311,15 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
         }
       }
       const float other = __shfl_xor_sync(0xffffffffu, sc, 1);   // the other candidate of the same chunk
+      const int other_t = __shfl_xor_sync(0xffffffffu, tk_asked, 1);
       if (act) {
-        st_keys += 1;
+        if (idx >= 0) st_keys += 1;
         const float sl = side ? other : sc, sr = side ? sc : other;
         const bool win = sl > sr;
         if (win) right = mid; else left = mid;
         score = fmaxf(score, win ? sl : sr);
+        won_t = (win != (side != 0)) ? tk_asked : other_t;    // left candidate when it won, else the right one
+        won_score = win ? sl : sr;
       }
     }
 
@@ -352,7 +374,8 @@ int dispatch_rows(const hipattn_scan_params_t& p, cudaStream_t stream) {
   const int R = p.block_size_q / p.stride_q;
   if (R <= 16) return launch<DT, D, 16>(p, stream);
   if (R <= 32) return launch<DT, D, 32>(p, stream);
-  return launch<DT, D, 64>(p, stream);
+  if (R <= 64) return launch<DT, D, 64>(p, stream);
+  return launch<DT, D, 128>(p, stream);
 }
 
 // Scaled copy of the keys and their absolute sums: 16 / 8 lanes per row of 256 / 128 bytes.
@@ -402,13 +425,13 @@ int scan_prepare_keys(const hipattn_tokens_t& k, int dtype, int D, int B, int T,
   return check_launch("scan_prepare_keys_kernel");
 }
 
-// Takes 16-bit prefill shapes (2 to 64 pooled rows in multiples of 16, head dim 64 or 128) when the
+// Takes 16-bit prefill shapes (16 to 128 pooled rows in multiples of 16, head dim 64 or 128) when the
 // caller supplies the prepared keys; anything else is left to the other scan kernels.
 int scan_stage_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled) {
   *handled = false;
   const int R = p.block_size_q / p.stride_q;
   const int rows = min(R, cdiv(p.TQ, p.stride_q));
-  if (p.mode == HIPATTN_SCAN_STRICT || p.dtype == HIPATTN_F32 || rows <= 1 || (R % 16) != 0 || R > 64 || (p.D != 64 && p.D != 128)) return HIPATTN_OK;
+  if (p.mode == HIPATTN_SCAN_STRICT || p.dtype == HIPATTN_F32 || rows <= 1 || (R % 16) != 0 || R > 128 || (p.D != 64 && p.D != 128)) return HIPATTN_OK;
   if (p.key_abs == nullptr || p.k_scaled == nullptr) return HIPATTN_OK;
   if ((int64_t)p.B * p.T * p.HKV >= 0x7fffffffLL) return HIPATTN_OK;
   const char* v = getenv("HIPATTN_SCAN_KERNEL");
