@@ -304,7 +304,6 @@ int dispatch_dim(const hipattn_scan_params_t& p, cudaStream_t stream) {
 
 int scan_stage_mma(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
 int scan_stage_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
-int scan_stage_regs(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
 int scan_chunks_strict(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
 int scan_prepare_keys(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* key_abs,
                       void* k_scaled, uint32_t* status, cudaStream_t stream);
@@ -335,8 +334,6 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
   HIPATTN_REQUIRE(p->mode >= HIPATTN_SCAN_AUTO && p->mode <= HIPATTN_SCAN_CHECK, HIPATTN_ERR_INVALID, "scan stage: unknown mode %d", p->mode);
   bool handled = false;
   rc = scan_chunks_strict(*p, s, &handled);
-  if (handled) return rc;
-  rc = scan_stage_regs(*p, s, &handled);
   if (handled) return rc;
   rc = scan_stage_tcgen05(*p, s, &handled);
   if (handled) return rc;

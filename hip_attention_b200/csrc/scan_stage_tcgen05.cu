@@ -37,6 +37,7 @@ struct ScanShared {
   int pmin;
   float qmax;
   int g[2][4];
+  int fetched[3];   // "some warp fetched rows in round r" for three consecutive rounds (r % 3)
 };
 constexpr uint32_t kScanSlack = 896;   // padding reserved in front of the tiles
 
@@ -86,6 +87,7 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     sh.abort = 0;
     sh.qmax = 0.f;
+    sh.fetched[0] = sh.fetched[1] = sh.fetched[2] = 0;
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem)), "r"(TMEM_COLS) : "memory");
@@ -164,6 +166,7 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
 
   bool aborted = Rv == 0;
   int cbi = 0;
+  int rr = 0;   // rounds executed by this CTA so far (the same number in every thread)
   // the bounds of a thread's chunk are requested one chunk block ahead, so that their latency is not part of the chain
   int next_left = 0, next_right = 0;
   if (cblk < nblk_total && cblk * 64 + (tid >> 1) < n) {
@@ -230,6 +233,7 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
       const float s_abs = idx >= 0 ? __ldg(p.key_abs + idx) : 0.f;
       // ---- gather this warp's 32 rows: 8 lanes per row, 128 contiguous bytes per row and instruction ----
       if (__any_sync(0xffffffffu, idx >= 0)) {   // a warp whose scores are all known (or inactive) copies nothing
+      if (lane == 0) *(volatile int*)&sh.fetched[rr % 3] = 1;
 #pragma unroll
       for (int r0 = 0; r0 < 32; r0 += 4) {
         const int j = r0 + (lane >> 3);
@@ -246,10 +250,13 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
       cp_async_wait<0>();
       fence_async_smem();
       tc_fence_before();
-      const int any = __syncthreads_or((act ? 1 : 0) | (*(volatile int*)&sh.abort ? 2 : 0) | (idx >= 0 ? 4 : 0));
-      if (any & 2) { aborted = true; break; }
-      if (!(any & 1)) break;
-      const bool scored = (any & 4) != 0;   // somebody fetched a row: the tile is multiplied; else every score is known
+      // the barrier's result is one bit (any predicate non-zero): "somebody is still searching, or gave up"
+      if (!__syncthreads_or(act || *(volatile int*)&sh.abort)) break;
+      if (*(volatile int*)&sh.abort) { aborted = true; break; }
+      // somebody fetched a row: the tile is multiplied; else every live score is known from the round before
+      const bool scored = *(volatile int*)&sh.fetched[rr % 3] != 0;
+      if (tid == 0) *(volatile int*)&sh.fetched[(rr + 2) % 3] = 0;   // next written two barriers from now
+      ++rr;
       if (scored && tid == 0) {
         tc_fence_after();
 #pragma unroll
