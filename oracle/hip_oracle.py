@@ -84,6 +84,39 @@ class OracleConfig:
     block_size_k: int = 64  # BLOCK_CHUNK seed, ``attention_extend.py:1970``
     softcap: Optional[float] = None  # logit soft-cap of the attention kernels
     bsa_block_q: Optional[int] = None  # block_sparse_block_size_q when smaller than the estimator's query block
+    rope: Optional["OracleRope"] = None  # in-kernel RoPE (``using_extend`` and ``need_apply_rope``)
+
+
+@dataclass
+class OracleRope:
+    """Un-rotated q / k plus cos / sin tables [T, D]: the kernels rotate on the fly (``attention_extend.py:248-407,
+    630-703``, ``attention_extend_bsa.py:126-392, 797-856``).  Backends built: scan ``relative`` / ``streaming``
+    (per stage, ``ScanStage.stage_extend_backend`` overrides), attention ``streaming``."""
+    cos: torch.Tensor
+    sin: torch.Tensor
+    scan_backend: str = "relative"
+    stage_backends: Optional[List[Optional[str]]] = None   # per-stage override (None entries fall back)
+    sa_backend: str = "streaming"
+
+    def backend_of(self, i: int) -> str:
+        b = self.stage_backends[i] if self.stage_backends is not None and self.stage_backends[i] is not None else self.scan_backend
+        if b not in ("relative", "streaming"):
+            raise NotImplementedError(f"scan_extend_backend {b!r}")
+        return b
+
+
+def rope_rotate(x: torch.Tensor, positions: torch.Tensor, rope: OracleRope, dtype: torch.dtype) -> torch.Tensor:
+    """x [..., D] fp32 holding dtype-rounded values, positions [...] (broadcastable to x's leading dims) ->
+    x * cos + rotate_half(x) * sin with cos / sin cast to ``dtype`` first and every product and the sum rounded to
+    ``dtype`` (the reference computes in the element type: ``attention_extend.py:392-407, 690-703``)."""
+    D = x.shape[-1]
+    h = D // 2
+    cos = round_to(rope.cos.float(), dtype)[positions.long()][..., :h]
+    sin = round_to(rope.sin.float(), dtype)[positions.long()][..., :h]
+    cos = torch.cat([cos, cos], -1)
+    sin = torch.cat([sin, sin], -1)
+    rot = torch.cat([-x[..., h:], x[..., :h]], -1)
+    return round_to(round_to(x * cos, dtype) + round_to(rot * sin, dtype), dtype)
 
 
 class DenseKV:
@@ -138,9 +171,11 @@ def strict_dot(qs: torch.Tensor, ks: torch.Tensor) -> torch.Tensor:
     return acc
 
 
-def pooled_queries(q: torch.Tensor, pos: torch.Tensor, b: int, d: int, bq: int, sq: int):
+def pooled_queries(q: torch.Tensor, pos: torch.Tensor, b: int, d: int, bq: int, sq: int, rope=None, new_tdst=None):
     """Mean-pooled, strided query rows of block d (``attention_extend.py:516-734``).
 
+    ``rope`` / ``new_tdst(pos_rows)``: with in-kernel RoPE every loaded row is first rotated to the position
+    ``new_tdst`` gives for the position of its group's FIRST row (``attention_extend.py:630-703``).
     Returns (Q̄ [H, R, D] fp32 holding dtype-rounded values, valid [R] bool, pmin int).
     """
     TQ = q.shape[1]
@@ -153,6 +188,9 @@ def pooled_queries(q: torch.Tensor, pos: torch.Tensor, b: int, d: int, bq: int, 
         ti = t + o
         ok = valid & (ti < TQ)
         rows = q[b, ti.clamp(max=TQ - 1)].float() * ok[:, None, None]
+        if rope is not None:
+            p_rows = torch.where(valid, pos[b, t.clamp(max=TQ - 1)], torch.zeros_like(t))
+            rows = rope_rotate(rows, new_tdst(p_rows)[:, None].expand(R, q.shape[2]), rope, q.dtype) * ok[:, None, None]
         acc = acc + rows
         cnt = cnt + ok.float()
     qbar = acc / (cnt[:, None, None] + torch.tensor(1e-12, dtype=torch.float32))
@@ -162,7 +200,7 @@ def pooled_queries(q: torch.Tensor, pos: torch.Tensor, b: int, d: int, bq: int, 
     return qbar, valid, pmin
 
 
-def scan_block(qbar, valid, pmin, ksrc, b, left, right, *, bq, sw_r, G, block_chunk, dtype):
+def scan_block(qbar, valid, pmin, ksrc, b, left, right, *, bq, sw_r, G, block_chunk, dtype, rope=None, backend=None):
     """Scan one (batch, query block) for all heads.
 
     left/right: int64 [H, n].  Returns narrowed (left, right) [H, n] and scores [H, n] fp32
@@ -200,19 +238,28 @@ def scan_block(qbar, valid, pmin, ksrc, b, left, right, *, bq, sw_r, G, block_ch
         tl_ = (left + mid) // 2
         tr_ = (mid + right) // 2
 
-        def side(t):
+        def side(t, is_right=False):
             out = torch.empty((H, n), dtype=torch.float32)
             for hk in range(H // G):
                 hs = slice(hk * G, (hk + 1) * G)
                 rows = ksrc.rows(b, t[hs], hk).float() * act[hs][..., None]  # [G, n, D]
-                kk = round_to(round_to(rows, dtype) * k_scale, dtype)
+                rows = round_to(rows, dtype)
+                if rope is not None:
+                    # representative keys are rotated to the chunk's ordinal (streaming) or to 0 / 1 for the left /
+                    # right candidate (relative), ``attention_extend.py:290-298``
+                    if backend == "streaming":
+                        new_t = torch.arange(n)[None, :].expand(G, n)
+                    else:
+                        new_t = torch.full((G, n), 1 if is_right else 0)
+                    rows = rope_rotate(rows, new_t, rope, dtype) * act[hs][..., None]
+                kk = round_to(rows * k_scale, dtype)
                 s = round_to(strict_dot(qs[hs], kk), dtype)  # [G, R, n]
                 s = torch.where(valid[None, :, None], s, neg_inf)
                 out[hs] = s.max(1).values
             return torch.where(act, out, neg_inf)
 
         sl = side(tl_)
-        sr = side(tr_)
+        sr = side(tr_, True)
         win = sl > sr
         left, right = (torch.where(act, torch.where(win, left, mid), left),
                        torch.where(act, torch.where(win, mid, right), right))
@@ -309,9 +356,16 @@ def estimate_mask(q: torch.Tensor, ksrc, pos: torch.Tensor, cfg: OracleConfig,
         nr = right.clone()
         for b in range(B):
             for d in range(BDST):
-                qbar, valid, pmin = pooled_queries(q, pos, b, d, bq, st.stride_q)
+                backend = new_tdst = None
+                if cfg.rope is not None:
+                    backend = cfg.rope.backend_of(i)
+                    if backend == "relative":      # ``attention_extend.py:641``
+                        new_tdst = lambda p: torch.full_like(p, 1 + sw_r)
+                    else:                          # streaming, ``:644-647``
+                        new_tdst = lambda p, n=n: torch.minimum(p, torch.full_like(p, n + sw_r))
+                qbar, valid, pmin = pooled_queries(q, pos, b, d, bq, st.stride_q, cfg.rope, new_tdst)
                 l2, r2, s2 = scan_block(qbar, valid, pmin, ksrc, b, left[b, d], right[b, d], bq=bq, sw_r=sw_r,
-                                        G=G, block_chunk=block_chunk, dtype=q.dtype)
+                                        G=G, block_chunk=block_chunk, dtype=q.dtype, rope=cfg.rope, backend=backend)
                 nl[b, d], nr[b, d], scores[b, d] = l2, r2, s2
         red = scores.max(dim=2, keepdim=True).values  # head reduce, ``attention_extend.py:2566-2570``
         if score_reduce is not None:  # heads split over processes: finish the max across them
@@ -386,9 +440,47 @@ def attended_columns(indices_row: torch.Tensor, ks: int, pos_rows: torch.Tensor,
     return cols, allow
 
 
+def rope_attention_block(q_rows, pos_rows, idx_row, ks: int, ksrc, vsrc, b: int, hkv: int, *, sink: int, sw: int, c_last: int,
+                         rope: OracleRope, dtype):
+    """Logits and values of one (query block, head) with in-kernel RoPE, attention backend ``streaming``.
+
+    Queries are rotated to their own position (``attention_extend_bsa.py:797-856``).  Window keys are rotated to
+    their own position; sink keys and selected-block keys to ``max(0, j * c_last + i + pmin - sw - sink - ks * c_last
+    + 1)`` with j the key's block rank in the list [sink blocks | selected blocks], i its offset in the block, pmin the
+    block's smallest query position and ks * c_last the number of selected tokens of the block (``:256-270, 1120,
+    1359``).  A token can sit in two groups; the admission rules of the groups are disjoint per row.
+    Returns (s [rows, C] fp64 logits with -inf where not admitted, values [C, D] fp64)."""
+    T = ksrc.T
+    pmax, pmin = int(pos_rows.max()), int(pos_rows.min())
+    qd = q_rows.dtype
+    qr = rope_rotate(q_rows.float(), pos_rows, rope, qd).to(dtype)
+    sel_start = idx_row[:ks]
+    jb = torch.arange(ks)[:, None].expand(ks, c_last).flatten()
+    io = torch.arange(c_last)[None, :].expand(ks, c_last).flatten()
+    sel_t = (sel_start[:, None] + torch.arange(c_last)[None, :]).flatten()
+    ok = (sel_t >= sink) & (sel_t <= pmax) & (sel_t < T) & (sel_t >= 0)
+    sel_t, jb, io = sel_t[ok], jb[ok], io[ok]
+    shift = pmin - sw - sink - ks * c_last + 1
+    sel_new = ((jb + sink // c_last) * c_last + io + shift).clamp(min=0)
+    sink_t = torch.arange(0, min(sink, pmax + 1, T))
+    sink_new = (sink_t + shift).clamp(min=0)
+    win_t = torch.arange(max(0, pmin - sw + 1), min(pmax + 1, T))
+    p = pos_rows[:, None]
+    parts = []
+    for t, new_t, is_win in ((sink_t, sink_new, False), (sel_t, sel_new, False), (win_t, win_t, True)):
+        if t.numel() == 0:
+            continue
+        kk = rope_rotate(ksrc.rows(b, t, hkv).to(qd).float(), new_t, rope, qd).to(dtype)
+        allow = ((t[None, :] <= p) & (t[None, :] > p - sw)) if is_win else (t[None, :] <= p - sw)
+        parts.append(((qr @ kk.T).masked_fill(~allow, float("-inf")), vsrc.rows(b, t, hkv).to(dtype)))
+    if not parts:
+        return torch.full((q_rows.shape[0], 0), float("-inf"), dtype=dtype), torch.zeros((0, q_rows.shape[-1]), dtype=dtype)
+    return torch.cat([x[0] for x in parts], 1), torch.cat([x[1] for x in parts], 0)
+
+
 def attention_on_mask(q: torch.Tensor, ksrc, vsrc, pos: torch.Tensor, mask: OracleMask, *, sink: int, sw: int,
                       bsa_block_q: Optional[int] = None, return_lse: bool = False, dtype=torch.float64,
-                      softcap: Optional[float] = None):
+                      softcap: Optional[float] = None, rope: Optional[OracleRope] = None):
     """Masked softmax attention recomputed in high precision on the estimator's mask.
 
     ``sw`` is the attention window (the reference restores ``max(sw, c_0)``, ``attention_extend.py:2901``).
@@ -408,14 +500,20 @@ def attention_on_mask(q: torch.Tensor, ksrc, vsrc, pos: torch.Tensor, mask: Orac
             r0, r1 = d * bq, min((d + 1) * bq, TQ)
             for h in range(H):
                 n = b * H + h
-                cols, allow = attended_columns(mask.indices[n, d], int(mask.ks[n, d]), pos[b, r0:r1], sink=sink,
-                                               sw=sw, c_last=mask.block_size_k, T=ksrc.T)
-                kk = ksrc.rows(b, cols, h // G).to(dtype)
-                vv = vsrc.rows(b, cols, h // G).to(dtype)
-                s = q[b, r0:r1, h].to(dtype) @ kk.T
-                if softcap:
-                    s = torch.tanh(s / softcap) * softcap
-                s = s.masked_fill(~allow, float("-inf"))
+                if rope is not None:
+                    s, vv = rope_attention_block(q[b, r0:r1, h], pos[b, r0:r1], mask.indices[n, d], int(mask.ks[n, d]), ksrc,
+                                                 vsrc, b, h // G, sink=sink, sw=sw, c_last=mask.block_size_k, rope=rope, dtype=dtype)
+                    if softcap:
+                        s = torch.where(torch.isinf(s), s, torch.tanh(s / softcap) * softcap)
+                else:
+                    cols, allow = attended_columns(mask.indices[n, d], int(mask.ks[n, d]), pos[b, r0:r1], sink=sink,
+                                                   sw=sw, c_last=mask.block_size_k, T=ksrc.T)
+                    kk = ksrc.rows(b, cols, h // G).to(dtype)
+                    vv = vsrc.rows(b, cols, h // G).to(dtype)
+                    s = q[b, r0:r1, h].to(dtype) @ kk.T
+                    if softcap:
+                        s = torch.tanh(s / softcap) * softcap
+                    s = s.masked_fill(~allow, float("-inf"))
                 m = s.max(-1, keepdim=True).values
                 m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
                 p = torch.exp(s - m)
@@ -466,10 +564,23 @@ def hip_attention_oracle(q, k, v, pos, cfg: OracleConfig, *, paged=None, restart
             mask.ks_start_end = mask.ks_start_end.repeat_interleave(rep, 1)
             mask.block_size_q = cfg.bsa_block_q
     sw_attn = max(0, cfg.sw - cfg.stages[0].chunk_size) + cfg.stages[0].chunk_size
-    out = attention_on_mask(q, ksrc, vsrc, pos, mask, sink=cfg.sink, sw=sw_attn, dtype=out_dtype, softcap=cfg.softcap)
+    out = attention_on_mask(q, ksrc, vsrc, pos, mask, sink=cfg.sink, sw=sw_attn, dtype=out_dtype, softcap=cfg.softcap,
+                            rope=cfg.rope)
     return out, mask
 
 
 def config_from_case(c) -> OracleConfig:
     return OracleConfig(stages=[OracleStage(*s) for s in c["stages"]], sink=c["sink"], sw=c["sw"],
-                        second_stage_k=c["second_k"], softcap=c.get("softcap"), bsa_block_q=c.get("bsa_bq"))
+                        second_stage_k=c["second_k"], softcap=c.get("softcap"), bsa_block_q=c.get("bsa_bq"),
+                        rope=rope_from_case(c))
+
+
+def rope_from_case(c) -> Optional[OracleRope]:
+    """cos / sin tables of a golden case with in-kernel RoPE (``rope_in_kernel`` = scan backend name)."""
+    if "rope_in_kernel" not in c:
+        return None
+    import cases
+    T = max(c.get("ext", c["T"]), c["T"]) + 8
+    cos, sin = cases.rope_tables(T, c["D"], c.get("rope_theta", 10000.0))
+    return OracleRope(cos=torch.from_numpy(cos), sin=torch.from_numpy(sin), scan_backend=c["rope_in_kernel"],
+                      stage_backends=c.get("stage_backends"))

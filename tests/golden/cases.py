@@ -67,6 +67,21 @@ CASES = {
     # broken down to the attention block size (repeat-interleave)
     "bsa16_fp16": dict(B=1, TQ=100, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128,
                        second_k=128, stages=[(64, 2, 32, None), (64, 1, 8, 256)], seed=26, bsa_bq=16),
+    # in-kernel RoPE (using_extend + need_apply_rope): q and k arrive un-rotated with cos / sin tables; scan backend
+    # "relative" (keys at position 0 / 1, queries at 1 + window) and "streaming" (keys at their chunk's ordinal),
+    # attention backend "streaming"
+    "rope_rel_fp16": dict(B=1, TQ=128, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                          stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=27, rope_in_kernel="relative", rope_theta=10000.0),
+    "rope_str_fp16": dict(B=1, TQ=100, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                          stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=28, rope_in_kernel="streaming", rope_theta=10000.0),
+    "rope_decode_fp16": dict(B=2, TQ=1, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                             stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=29, rope_in_kernel="relative", rope_theta=10000.0),
+    "rope_mixed_fp32": dict(B=1, TQ=192, T=2048, H=4, HKV=2, D=64, dtype="fp32", sink=32, sw=128, second_k=128,
+                            stages=[(64, 4, 64, None), (64, 2, 16, 512), (64, 1, 4, 256)], seed=30, rope_in_kernel="relative",
+                            stage_backends=[None, "streaming", None], rope_theta=500000.0),
+    "rope_str_decode_fp16": dict(B=2, TQ=1, T=1024, H=4, HKV=2, D=128, dtype="fp16", sink=32, sw=128, second_k=128,
+                                 stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=31, rope_in_kernel="streaming",
+                                 rope_theta=10000.0),
     # benchmark configuration 1 shape (fp32, 4096 x 4096, 8/2 heads, D 64)
     "config1_fp32": dict(B=1, TQ=4096, T=4096, H=8, HKV=2, D=64, dtype="fp32", sink=64, sw=256,
                          second_k=512, stages=[(64, 4, 32, None), (64, 1, 8, 1024)], seed=101,
@@ -119,7 +134,7 @@ def make_inputs(name: str):
         q = np.clip(np.round(q * 4) / 4, -2, 2)
         k = np.clip(np.round(k * 4) / 4, -2, 2)
         v = np.clip(np.round(v * 4) / 4, -2, 2)
-    if "rope_theta" in c:
+    if "rope_theta" in c and "rope_in_kernel" not in c:
         q = apply_rope(q, pos, c["rope_theta"])
         kpos = np.broadcast_to(np.arange(T), (B, T))
         k = apply_rope(k, kpos, c["rope_theta"])

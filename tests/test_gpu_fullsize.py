@@ -64,8 +64,19 @@ def _recompute_rows(q, k, v, md, w, rows, pos):
 
 
 def test_prefill_128k_full_size(monkeypatch):
+    _prefill_full_size(dict(bench.WORKLOADS["prefill_128k"]), monkeypatch)
+
+
+def test_prefill_256k_gqa_shape(monkeypatch):
+    """The large-GQA configuration (query blocks of 128 rows, 64 query heads on 8 KV heads, 262144 keys, sink 256,
+    window 2048, stages keeping 65536 / 16384 / 4096 tokens): one sequence and its last 32768 queries, which keeps
+    every stage shape (32 / 32 / 128 pooled rows, 1015 / 2048 / 2048 chunks, 512 selected blocks) at a sixteenth of
+    the work."""
+    _prefill_full_size(dict(bench.WORKLOADS["prefill_256k_gqa"], B=1, TQ=32768), monkeypatch)
+
+
+def _prefill_full_size(w, monkeypatch):
     from hip_attention_b200 import HiPAttentionOutputMetadata, hip_attention_12, hip_attention_impl, read_status
-    w = dict(bench.WORKLOADS["prefill_128k"])
     q, k, v = bench.make_qkv(w, "cuda")
     args = bench.make_args(w)
     TQ, T = w["TQ"], w["T"]
