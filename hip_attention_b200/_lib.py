@@ -12,8 +12,9 @@ F32, F16, BF16 = 0, 1, 2
 STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE, STATUS_TIMEOUT, STATUS_CHUNK_SIZE = 1, 2, 4, 8
 MAX_CHUNKS = 16384
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
-ABI_VERSION = 5
+ABI_VERSION = 6
 SCAN_AUTO, SCAN_STRICT, SCAN_CHECK = 0, 1, 2
+ROPE_NONE, ROPE_RELATIVE, ROPE_STREAMING = 0, 1, 2
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
@@ -33,7 +34,8 @@ class ScanParams(C.Structure):
                 ("left_out", vp), ("right_out", vp), ("score_out", vp), ("status", vp), ("key_abs", vp), ("k_scaled", vp), ("stats", vp),
                 ("dtype", i32), ("D", i32), ("B", i32), ("TQ", i32), ("H", i32), ("HKV", i32), ("T", i32),
                 ("block_size_q", i32), ("stride_q", i32), ("n_chunks", i32), ("block_chunk", i32),
-                ("scan_window", i32), ("q_scale", f32), ("k_scale", f32), ("mode", i32), ("chunk_size", i32)]
+                ("scan_window", i32), ("q_scale", f32), ("k_scale", f32), ("mode", i32), ("chunk_size", i32),
+                ("rope_cos", vp), ("rope_sin", vp), ("rope_stride", i64), ("rope_rows", i32), ("rope_mode", i32)]
 
 
 class BsaParams(C.Structure):
@@ -47,7 +49,7 @@ class BsaParams(C.Structure):
                 ("dtype", i32), ("D", i32), ("B", i32), ("TQ", i32), ("H", i32), ("HKV", i32), ("T", i32),
                 ("block_size_q", i32), ("index_block_q", i32), ("block_size_k", i32), ("K", i32),
                 ("sink", i32), ("window", i32), ("n_splits", i32), ("heads_share_mask", i32),
-                ("logit_softcap", f32)]
+                ("logit_softcap", f32), ("rope_rows", i32), ("rope_cos", vp), ("rope_sin", vp), ("rope_stride", i64)]
 
 
 # name -> (restype, argtypes); every symbol include/hipattn.h declares

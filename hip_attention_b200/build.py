@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libhipattn_sm100.so")
 SOURCES = ["capi.cu", "scan_stage.cu", "scan_stage_mma.cu", "scan_stage_tcgen05.cu", "scan_chunks_strict.cu", "select.cu", "bsa_generic.cu", "bsa_mma.cu", "bsa_tcgen05.cu", "bsa_decode.cu", "decode_noalloc.cu"]
-HEADERS = ["common.cuh", "bsa_common.cuh", "scan_common.cuh", "mma_common.cuh", "tcgen05_common.cuh", os.path.join("..", "..", "include", "hipattn.h")]
+HEADERS = ["common.cuh", "bsa_common.cuh", "scan_common.cuh", "mma_common.cuh", "tcgen05_common.cuh", "rope.cuh", os.path.join("..", "..", "include", "hipattn.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math=false"]
 

@@ -17,7 +17,7 @@ namespace hipattn {
 
 struct KeyList {
   int n_sink, n_sel, n_win, w_start, total;
-  int pmax;
+  int pmax, pmin;
   const int64_t* idx;  // selected block starts of this query block
   int block_k, sink, T;
   int block_k_shift;   // log2(block_k) when it is a power of two, else -1
@@ -35,6 +35,7 @@ __device__ __forceinline__ KeyList make_key_list(const hipattn_bsa_params_t& p, 
   kl.sink = p.sink;
   kl.T = p.T;
   kl.pmax = pmax;
+  kl.pmin = pmin;
   // Sink and window entries are positions, not table entries: keep them below T.  With dense K / V a
   // query position at or beyond T would otherwise address rows past the end of the tensors (a paged
   // cache maps such positions to page 0 by itself).  The clamp is reported, not silent.
@@ -77,6 +78,24 @@ __device__ __forceinline__ int key_position_at(const KeyList& kl, int j, long lo
 __device__ __forceinline__ int key_position(const KeyList& kl, int j, bool* is_window) {
   const int blk = selected_block_of(kl, j);
   return key_position_at(kl, j, blk >= 0 ? kl.idx[blk] : 0, is_window);
+}
+
+// Table position the key at entry j (position t) is rotated to by the attention's in-kernel RoPE, backend
+// "streaming" (attention_extend_bsa.py:256-270, 1120, 1359): window keys keep their own position; sink and selected
+// keys get their rank in the list [sink | selected blocks] shifted by pmin - window - sink - (selected tokens) + 1,
+// floored at 0 (pmin = smallest query position of the attention block).
+__device__ __forceinline__ int rope_key_position(const KeyList& kl, int j, int t, int window) {
+  if (j >= kl.n_sink + kl.n_sel) return t;
+  const int shift = kl.pmin - window - kl.sink - kl.n_sel + 1;
+  int rank;
+  if (j < kl.n_sink) {
+    rank = t;
+  } else {
+    const int jj = j - kl.n_sink;
+    const int blk = kl.block_k_shift >= 0 ? (jj >> kl.block_k_shift) : (jj / kl.block_k);
+    rank = (blk + kl.sink / kl.block_k) * kl.block_k + (jj - blk * kl.block_k);
+  }
+  return max(0, rank + shift);
 }
 
 __device__ __forceinline__ bool admits(int p_row, int t, bool is_window, int window) {

@@ -9,6 +9,7 @@
 // table (or from the dense tensor), widened to fp32 and staged in shared memory; S = Q K^T and
 // O += P V run as register-blocked FMA loops; softmax is online, in base 2.
 #include "bsa_common.cuh"
+#include "rope.cuh"
 
 namespace hipattn {
 namespace {
@@ -116,6 +117,16 @@ __global__ void __launch_bounds__(kThreads) bsa_generic_kernel(const hipattn_bsa
       const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)ti * p.q_stride_t +
                     (int64_t)hh * p.q_stride_h + pc * VEC;
       widen16<DT>(*reinterpret_cast<const uint4*>(qp), v);
+      if (p.rope_cos) {   // in-kernel RoPE: the query row at its own position (attention_extend_bsa.py:797-856)
+        constexpr int HALF = PIECES / 2;
+        float vr[VEC], tc[VEC], ts[VEC];
+        widen16<DT>(*reinterpret_cast<const uint4*>(qp + (pc < HALF ? HALF : -HALF) * VEC), vr);
+        const long long x = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)ti * p.pos_stride_t];
+        const int qpos = (int)(x > 0x7ffffff0LL ? 0x7ffffff0LL : (x < 0 ? 0 : x));
+        rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, qpos, pc % HALF, tc);
+        rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, qpos, pc % HALF, ts);
+        rope_rotate_piece<DT, VEC>(v, vr, tc, ts, pc < HALF);
+      }
     }
 #pragma unroll
     for (int e = 0; e < VEC; e += 4)
@@ -162,6 +173,15 @@ __global__ void __launch_bounds__(kThreads) bsa_generic_kernel(const hipattn_bsa
         const char* vr = token_row(p.v, b, t, hkv, Elem<DT>::bytes, p.status);
         widen16<DT>(*reinterpret_cast<const uint4*>(kr + pc * 16), kv);
         widen16<DT>(*reinterpret_cast<const uint4*>(vr + pc * 16), vv);
+        if (p.rope_cos) {   // in-kernel RoPE: the key at the position its place in the list maps to
+          constexpr int HALF = PIECES / 2;
+          float xr[VEC], tc[VEC], ts[VEC];
+          widen16<DT>(*reinterpret_cast<const uint4*>(kr + (pc < HALF ? pc + HALF : pc - HALF) * 16), xr);
+          const int new_t = rope_key_position(kl, j0 + kk, t, p.window);
+          rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, new_t, pc % HALF, tc);
+          rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, new_t, pc % HALF, ts);
+          rope_rotate_piece<DT, VEC>(kv, xr, tc, ts, pc < HALF);
+        }
       }
 #pragma unroll
       for (int e = 0; e < VEC; e += 4) {

@@ -1,34 +1,9 @@
 // Pieces shared by the two scan kernels: pooled queries and the per-call work split.
 #pragma once
 #include "common.cuh"
+#include "rope.cuh"
 
 namespace hipattn {
-
-template <int DT>
-__device__ __forceinline__ void widen_piece(const uint4& w, float* out);
-template <>
-__device__ __forceinline__ void widen_piece<HIPATTN_F32>(const uint4& w, float* out) {
-  out[0] = __uint_as_float(w.x); out[1] = __uint_as_float(w.y); out[2] = __uint_as_float(w.z); out[3] = __uint_as_float(w.w);
-}
-template <>
-__device__ __forceinline__ void widen_piece<HIPATTN_BF16>(const uint4& w, float* out) {
-  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    out[2 * i] = __uint_as_float(v[i] << 16);
-    out[2 * i + 1] = __uint_as_float(v[i] & 0xffff0000u);
-  }
-}
-template <>
-__device__ __forceinline__ void widen_piece<HIPATTN_F16>(const uint4& w, float* out) {
-  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v[i]));
-    out[2 * i] = f.x;
-    out[2 * i + 1] = f.y;
-  }
-}
 
 // One 16-byte piece of a pooled, scaled query row (attention_extend.py:607-734, 924-931): the mean of
 // stride_q consecutive query rows starting at row t, accumulated in fp32 in row order, divided by the
@@ -42,11 +17,28 @@ __device__ __forceinline__ void pooled_query_piece(const hipattn_scan_params_t& 
   for (int e = 0; e < VEC; ++e) sum[e] = 0.f;
   float cnt = 0.f;
   const T* base = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)h * p.q_stride_h + piece * VEC;
+  // in-kernel RoPE: every row of the group is rotated to the position derived from the group's FIRST row
+  // (attention_extend.py:630-647) before it is added up
+  float tc[VEC], ts[VEC];
+  const int pieces = p.D / VEC, half = pieces / 2;
+  if (p.rope_mode != HIPATTN_ROPE_NONE) {
+    long long pv = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)t * p.pos_stride_t];
+    const long long cap = (long long)p.n_chunks + p.scan_window;
+    const int new_t = p.rope_mode == HIPATTN_ROPE_RELATIVE ? 1 + p.scan_window : (int)(pv < cap ? (pv < 0 ? 0 : pv) : cap);
+    rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, new_t, piece % half, tc);
+    rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, new_t, piece % half, ts);
+  }
 #pragma unroll 4
   for (int o = 0; o < p.stride_q; ++o) {
     if (t + o < p.TQ) {
       float v[VEC];
       widen_piece<DT>(*reinterpret_cast<const uint4*>(base + (int64_t)(t + o) * p.q_stride_t), v);
+      if (p.rope_mode != HIPATTN_ROPE_NONE) {
+        float vr[VEC];
+        const int shift = (piece < half ? half : -half) * VEC;
+        widen_piece<DT>(*reinterpret_cast<const uint4*>(base + (int64_t)(t + o) * p.q_stride_t + shift), vr);
+        rope_rotate_piece<DT, VEC>(v, vr, tc, ts, piece < half);
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) sum[e] = __fadd_rn(sum[e], v[e]);
       cnt += 1.f;

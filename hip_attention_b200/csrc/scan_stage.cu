@@ -66,6 +66,23 @@ __device__ __forceinline__ void unpack_scaled<HIPATTN_F16>(const uint4& w, float
   }
 }
 
+// the same for a staged key row that is first rotated to table position `new_t` (in-kernel RoPE,
+// attention_extend.py:248-407): piece `pc` of the row at `row`, its partner half a row away, cos / sin of new_t
+template <int DT, int D>
+__device__ __forceinline__ void unpack_rope_scaled(const unsigned char* row, int pc, int new_t, const hipattn_scan_params_t& p,
+                                                   float* out) {
+  constexpr int VEC = 16 / Elem<DT>::bytes;
+  constexpr int PIECES = D / VEC, HALF = PIECES / 2;
+  float xr[VEC], tc[VEC], ts[VEC];
+  widen_piece<DT>(*reinterpret_cast<const uint4*>(row + pc * 16), out);
+  widen_piece<DT>(*reinterpret_cast<const uint4*>(row + (pc < HALF ? pc + HALF : pc - HALF) * 16), xr);
+  rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, new_t, pc % HALF, tc);
+  rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, new_t, pc % HALF, ts);
+  rope_rotate_piece<DT, VEC>(out, xr, tc, ts, pc < HALF);
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) out[e] = Elem<DT>::round(__fmul_rn(out[e], p.k_scale));
+}
+
 template <int DT>
 __device__ __forceinline__ float mac(float q, float k, float acc) {
   if (DT == HIPATTN_F32) return __fadd_rn(acc, __fmul_rn(q, k));  // two roundings, reproducible on a CPU
@@ -154,7 +171,9 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
     const int mid = (left + right) >> 1;
     int tl = (left + mid) >> 1, tr = (mid + right) >> 1;
     const int tl_asked = tl, tr_asked = tr;
-    const bool known_l = act && tl == won_t, known_r = act && tr == won_t;
+    // (with in-kernel RoPE a key's score depends on the side it is proposed for: nothing is reused)
+    const bool reuse = p.rope_mode == HIPATTN_ROPE_NONE;
+    const bool known_l = act && reuse && tl == won_t, known_r = act && reuse && tr == won_t;
     const char* src_l = nullptr;
     const char* src_r = nullptr;
     if (act) {
@@ -207,8 +226,14 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
 #pragma unroll 2
         for (int pc = 0; pc < G::kPieces; ++pc) {
           float kl[G::kVec], kr[G::kVec];
-          unpack_scaled<DT>(*reinterpret_cast<const uint4*>(my_l + pc * 16), p.k_scale, kl);
-          unpack_scaled<DT>(*reinterpret_cast<const uint4*>(my_r + pc * 16), p.k_scale, kr);
+          if (p.rope_mode == HIPATTN_ROPE_NONE) {
+            unpack_scaled<DT>(*reinterpret_cast<const uint4*>(my_l + pc * 16), p.k_scale, kl);
+            unpack_scaled<DT>(*reinterpret_cast<const uint4*>(my_r + pc * 16), p.k_scale, kr);
+          } else {   // keys at their chunk's index (streaming) or at 0 / 1 for the left / right candidate (relative)
+            const bool rel = p.rope_mode == HIPATTN_ROPE_RELATIVE;
+            unpack_rope_scaled<DT, D>(my_l, pc, rel ? 0 : c, p, kl);
+            unpack_rope_scaled<DT, D>(my_r, pc, rel ? 1 : c, p, kr);
+          }
 #pragma unroll
           for (int r = 0; r < RT; ++r) {
 #pragma unroll
@@ -333,12 +358,22 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
   cudaStream_t s = (cudaStream_t)stream;
   HIPATTN_REQUIRE(p->mode >= HIPATTN_SCAN_AUTO && p->mode <= HIPATTN_SCAN_CHECK, HIPATTN_ERR_INVALID, "scan stage: unknown mode %d", p->mode);
   bool handled = false;
+  if (p->rope_mode != HIPATTN_ROPE_NONE) {
+    // in-kernel RoPE is built into the strict kernel only
+    HIPATTN_REQUIRE(p->rope_mode == HIPATTN_ROPE_RELATIVE || p->rope_mode == HIPATTN_ROPE_STREAMING, HIPATTN_ERR_INVALID,
+                    "scan stage: unknown rope_mode %d", p->rope_mode);
+    HIPATTN_REQUIRE(p->rope_cos && p->rope_sin && p->rope_rows > 0, HIPATTN_ERR_INVALID, "scan stage: rope_mode without cos / sin tables");
+    HIPATTN_REQUIRE(((uintptr_t)p->rope_cos % 16) == 0 && ((uintptr_t)p->rope_sin % 16) == 0 && p->rope_stride % ra == 0 &&
+                        p->rope_stride >= p->D / 2,
+                    HIPATTN_ERR_INVALID, "scan stage: cos / sin rows must start on 16-byte boundaries and hold D / 2 columns");
+  } else {
   rc = scan_chunks_strict(*p, s, &handled);
   if (handled) return rc;
   rc = scan_stage_tcgen05(*p, s, &handled);
   if (handled) return rc;
   rc = scan_stage_mma(*p, s, &handled);
   if (handled) return rc;
+  }
   switch (p->dtype) {
     case HIPATTN_F32: return dispatch_dim<HIPATTN_F32>(*p, s);
     case HIPATTN_F16: return dispatch_dim<HIPATTN_F16>(*p, s);

@@ -32,6 +32,7 @@ _DT = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
 INT64_MAX = torch.iinfo(torch.int64).max
 SCORE_INIT = -32000.0
 _status_words = {}
+_ROPE_MODES = {"relative": L.ROPE_RELATIVE, "streaming": L.ROPE_STREAMING}
 
 
 def _cdiv(a: int, b: int) -> int:
@@ -113,11 +114,44 @@ def _tokens(dense: Optional[Tensor], cache: Optional[Tensor], table: Optional[Te
     return t
 
 
+def _rope_tables(args: HiPAttentionArgs, q: Tensor) -> Optional[Tuple[Tensor, Tensor]]:
+    """cos / sin [rows, D] in q's element type, contiguous (the kernels cast the tables to the element type before
+    use, ``attention_extend.py:308-321``; doing it once here is the same arithmetic)."""
+    if not args.using_extend:
+        return None
+    D = q.shape[-1]
+    out = []
+    for t in (args.rope_cos, args.rope_sin):
+        if t.ndim != 2 or t.shape[-1] < D // 2:
+            raise ValueError(f"rope tables must be [positions, >= head_dim / 2], got {tuple(t.shape)}")
+        if t.device != q.device:
+            raise ValueError(f"rope table on {t.device}, q on {q.device}")
+        t = t.to(q.dtype)
+        if t.stride(-1) != 1 or t.stride(0) % 8 or t.data_ptr() % 16:
+            t = t.contiguous()
+            if t.shape[-1] % 8:
+                pad = torch.zeros((t.shape[0], -(-t.shape[-1] // 8) * 8), dtype=t.dtype, device=t.device)
+                pad[:, :t.shape[-1]] = t
+                t = pad
+        out.append(t)
+    return out[0], out[1]
+
+
 def _reject_unsupported(args: HiPAttentionArgs) -> None:
     if args.offload_cache is not None or args.online_update_cache:
         raise NotImplementedError("host-offloaded KV (offload_cache / online_update_cache) is not part of this build")
-    if args.using_extend or args.need_apply_rope:
-        raise NotImplementedError("in-kernel RoPE (using_extend / need_apply_rope) is not built yet; rotate q and k first")
+    if args.using_extend != args.need_apply_rope:
+        raise NotImplementedError("using_extend and need_apply_rope must be set together (rotation of already rotated "
+                                  "q / k, attention_extend.py:299-323, is not built)")
+    if args.using_extend:
+        if args.rope_cos is None or args.rope_sin is None:
+            raise ValueError("using_extend needs rope_cos and rope_sin")
+        if args.sa_extend_backend != "streaming":
+            raise NotImplementedError(f"sa_extend_backend {args.sa_extend_backend!r} is not built (streaming)")
+        for st in args.stages:
+            name = getattr(st, "stage_extend_backend", None) or args.scan_extend_backend
+            if name not in _ROPE_MODES:
+                raise NotImplementedError(f"scan_extend_backend {name!r} is not built (relative, streaming)")
     if args.low_percent > 0 and args.low_k_ratio < 1:
         raise NotImplementedError("low_percent / low_k_ratio is dead code in the reference and is not built")
     if not args.is_causal:
@@ -186,7 +220,8 @@ class PhaseTimer:
 
 def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, args: HiPAttentionArgs,
                    restart: Optional[Tuple[int, Tensor, Tensor]], want_stage_inputs: bool,
-                   debug: Optional[dict] = None, score_reduce=None, timer: Optional[PhaseTimer] = None) -> _Mask:
+                   debug: Optional[dict] = None, score_reduce=None, timer: Optional[PhaseTimer] = None,
+                   rope: Optional[Tuple[Tensor, Tensor]] = None) -> _Mask:
     """Run the scan stages.  ``score_reduce(score_int32)`` is called after every scan, before the
     selection: a KV-head-parallel caller all-reduces (MAX) the head-reduced scores there."""
     lib = L.load()
@@ -226,7 +261,7 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
     # scaled keys and their magnitudes (error radius) for the tensor-core scan (16-bit prefill only), once per call
     key_abs = k_scaled = None
     R_min = min(bq // s_.stage_block_stride_q for s_ in stages)
-    if (q.dtype != torch.float32 and D in (64, 128) and min(TQ, bq) > 1 and _scan_mode() != L.SCAN_STRICT
+    if (q.dtype != torch.float32 and D in (64, 128) and min(TQ, bq) > 1 and _scan_mode() != L.SCAN_STRICT and rope is None
             and all((bq // s_.stage_block_stride_q) % 16 == 0 for s_ in stages) and R_min >= 16 and n > 0):
         if timer: timer.mark("start")
         key_abs = torch.empty((B, HKV, T), dtype=torch.float32, device=dev)
@@ -269,6 +304,10 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         sp.q_scale, sp.k_scale = q_scale, k_scale
         sp.mode = _scan_mode()
         sp.chunk_size = s_i.stage_chunk_size
+        if rope is not None:
+            sp.rope_cos, sp.rope_sin = rope[0].data_ptr(), rope[1].data_ptr()
+            sp.rope_stride, sp.rope_rows = rope[0].stride(0), rope[0].shape[0]
+            sp.rope_mode = _ROPE_MODES[getattr(s_i, "stage_extend_backend", None) or args.scan_extend_backend]
         if debug is not None and "scan_stats" in debug:
             sp.stats = debug["scan_stats"].data_ptr()
         if timer: timer.mark("start")
@@ -368,7 +407,8 @@ def _decode_splits(B: int, HKV: int, total_tokens: int) -> int:
 
 def _attention(q: Tensor, ktok: L.Tokens, vtok: L.Tokens, T: int, HKV: int, pos: Tensor, indices: Tensor, ks: Tensor,
                *, sink: int, window: int, block_size_k: int, bsa_block_q: int, index_block_q: int, heads_share: bool,
-               decode: bool, softcap: Optional[float], want_lse: bool) -> Tuple[Tensor, Optional[Tensor]]:
+               decode: bool, softcap: Optional[float], want_lse: bool,
+               rope: Optional[Tuple[Tensor, Tensor]] = None) -> Tuple[Tensor, Optional[Tensor]]:
     lib = L.load()
     dev = q.device
     st = _stream(dev)
@@ -391,6 +431,9 @@ def _attention(q: Tensor, ktok: L.Tokens, vtok: L.Tokens, T: int, HKV: int, pos:
     bp.sink, bp.window = sink, window
     bp.heads_share_mask = int(heads_share or decode)
     bp.logit_softcap = float(softcap) if softcap else 0.0
+    if rope is not None:
+        bp.rope_cos, bp.rope_sin = rope[0].data_ptr(), rope[1].data_ptr()
+        bp.rope_stride, bp.rope_rows = rope[0].stride(0), rope[0].shape[0]
     n_splits = _decode_splits(B, HKV, K * block_size_k + sink + window) if decode else 1
     bp.n_splits = n_splits
     if n_splits > 1:
@@ -481,6 +524,7 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
                 raise ValueError("position_ids must be given under CUDA graph capture")
             pos = (torch.arange(0, TQ, device=dev, dtype=torch.int64) + (T - TQ))[None, :].expand(B, TQ)
 
+        rope = _rope_tables(args, q)
         stages = args.stages
         bq = stages[-1].stage_block_size_q
         BDST = _cdiv(TQ, bq)
@@ -518,7 +562,7 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
                 l32, r32 = _restart_inputs(stage_caches[i0], B * BDST)
                 restart = (i0, l32, r32)
             m = _estimate_mask(q, ktok_scan, T, HKV, pos, args, restart, stage_caches is not None, debug,
-                               score_reduce, timer)
+                               score_reduce, timer, rope)
             if stage_caches is not None:
                 for i in range(len(stage_caches), len(stages)):
                     si = m.stage_inputs[i] if i < len(m.stage_inputs) else None
@@ -565,7 +609,7 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
         context, lse = _attention(q_bsa, ktok, vtok, T, HKV, pos, indices, ks, sink=args.sink_token_size, window=sw_attn,
                                   block_size_k=c_last, bsa_block_q=bsa_bq, index_block_q=index_block_q,
                                   heads_share=heads_share, decode=decode, softcap=args.logit_softcap,
-                                  want_lse=return_lse)
+                                  want_lse=return_lse, rope=rope)
         if timer: timer.mark("attention")
 
         if fresh_mask and _cdiv(TQ, bsa_bq) != BDST:

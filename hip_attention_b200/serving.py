@@ -5,8 +5,8 @@ layer with its token-granular KV pool.
 
 Mirrors the reference's adapter (``hip_attn/v1_2/hip_config.py``, ``mask_refresh_interval.py``,
 ``hip_memory_pool.py`` and ``paged_hip.py:327-500``): same class and field names, same JSON keys, same
-schedule, same split of a prefill chunk into a sparse part and its last 64 queries.  Not covered:
-in-kernel RoPE (``using_extend`` must be false) and the host-offload cache.
+schedule, same split of a prefill chunk into a sparse part and its last 64 queries, in-kernel RoPE
+(``using_extend``, the serving default) included.  Not covered: the host-offload cache.
 """
 from __future__ import annotations
 

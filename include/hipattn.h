@@ -60,6 +60,10 @@ typedef struct hipattn_tokens {
   int32_t page_size;
 } hipattn_tokens_t;
 
+#define HIPATTN_ROPE_NONE 0
+#define HIPATTN_ROPE_RELATIVE 1
+#define HIPATTN_ROPE_STREAMING 2
+
 #define HIPATTN_SCAN_AUTO 0   /* tensor-core scores with exact fallback where built, else strict */
 #define HIPATTN_SCAN_STRICT 1 /* sequential fp32 dot products only */
 #define HIPATTN_SCAN_CHECK 2  /* as AUTO, but every key is also scored strictly and compared (slow) */
@@ -106,6 +110,15 @@ typedef struct hipattn_scan_params {
   int32_t chunk_size;        /* optional: upper bound of right - left (the stage's chunk size), 0 = unknown.  A small
                                 power of two lets the scan score whole chunks once for all heads of a KV head and
                                 replay the search on the scores (same results, fewer key rows gathered) */
+  /* In-kernel RoPE of the estimator (attention_extend.py:248-407, 630-703): q and k arrive un-rotated and are
+   * rotated on the fly, x * cos + rotate_half(x) * sin in the element type.  rope_mode HIPATTN_ROPE_RELATIVE:
+   * queries at position 1 + scan_window, left / right candidate keys at 0 / 1; HIPATTN_ROPE_STREAMING: queries
+   * at min(position, n_chunks + scan_window), keys at their chunk's index in the list. */
+  const void* rope_cos;      /* [rope_rows, D] in the element type of q (only the first D / 2 columns are read) */
+  const void* rope_sin;
+  int64_t rope_stride;       /* elements between table rows */
+  int32_t rope_rows;
+  int32_t rope_mode;         /* HIPATTN_ROPE_NONE / _RELATIVE / _STREAMING */
 } hipattn_scan_params_t;
 
 int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);
@@ -199,6 +212,13 @@ typedef struct hipattn_bsa_params {
   int32_t n_splits;
   int32_t heads_share_mask;  /* 1: indices / ks are identical for the heads of a KV group */
   float logit_softcap;       /* 0 = off; attention_extend_bsa.py:389-390 */
+  /* In-kernel RoPE of the attention, backend "streaming" (attention_extend_bsa.py:126-392, 797-856), when rope_cos
+   * is given: queries are rotated to their own position, window keys to theirs, sink and selected keys to
+   * max(0, rank_in_list + pmin - window - sink - ks * block_size_k + 1) with pmin the block's smallest query position. */
+  int32_t rope_rows;
+  const void* rope_cos;      /* [rope_rows, D] in the element type of q */
+  const void* rope_sin;
+  int64_t rope_stride;
 } hipattn_bsa_params_t;
 
 int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream);

@@ -80,11 +80,67 @@ def config_record(cfg):
                 using_extend=cfg.using_extend, layers=[layer(l) for l in cfg.layers], prefill_layers=[layer(l) for l in cfg.prefill_layers])
 
 
+# The dense-layer entry uses window 128 here: with second_stage_k 256, sink 16 and window 64 the reference's flash-decode
+# kernel cuts the 32 selected blocks into 7 ranges of 5 blocks and walks each range two blocks at a time without stopping at
+# the range's end (attention_decode_bsa.py:235-249), so the block at every seam enters the softmax twice; with window 128
+# the ranges hold 6 blocks and nothing is counted twice.
+_EXTEND_LAYERS = [dict(_SMALL_LAYERS[0], sliding_window_size=128), _SMALL_LAYERS[1]]
+EXTEND_JSON = json.dumps({"using_extend": True, "mask_refresh_interval": [4, 2, 1], "metadata_cache_max_batch_size": 8,
+                          "block_sparse_block_size_q": 32, "layers": _EXTEND_LAYERS, "prefill_layers": _EXTEND_LAYERS})
+EXTEND_THETA = 10000.0
+
+
+def paged_extend(a, ph, cfgm):
+    """The paged forward call with the serving default ``using_extend``: un-rotated keys in the pool, cos / sin
+    tables handed in, scan backends relative (layer 7 overrides to streaming through its layer entry) and streaming
+    (layer 0, a dense layer), attention backend streaming.  A split prefill chunk and one decode step per layer."""
+    import numpy as np
+    import torch
+    from cases import rope_tables
+    _sort = torch.Tensor.sort
+
+    def stable_sort(self, *args, **kw):
+        kw["stable"] = True
+        return _sort(self, *args, **kw)
+
+    def stable_topk(self, k, dim=-1, largest=True, sorted=True):
+        r = _sort(self, dim=dim, descending=largest, stable=True)
+        return torch.return_types.topk((r.values.narrow(dim, 0, k), r.indices.narrow(dim, 0, k)))
+
+    torch.Tensor.sort = stable_sort
+    torch.Tensor.topk = stable_topk
+    c = PAGED
+    x = paged_inputs()
+    cfg = cfgm.HiPAttentionConfig(json_or_path=EXTEND_JSON)
+    T = c["T"]
+    cos, sin = rope_tables(T + 8, c["D"], EXTEND_THETA)
+    cos, sin = torch.from_numpy(cos), torch.from_numpy(sin)
+    save = {}
+    for layer_id in (0, c["layer_id"]):
+        def call(q, positions, seq_len, is_decode):
+            return ph.forward_paged_hip(
+                query=q, sm_scale=c["sm_scale"], batch_size=1, k_cache=x["k_pool"], v_cache=x["v_pool"], offload_cache=None,
+                positions=positions, seq_lens=torch.tensor([seq_len], dtype=torch.int64), req_to_tokens=x["req_to_tokens"],
+                req_pool_indices=x["req_pool_indices"], rope_cos=cos, rope_sin=sin, layer_id=layer_id, logit_cap=0.0,
+                orig_context_len=c["model_context"], max_context_len=T, is_prefill=not is_decode, hip_config=cfg,
+                cached_metadata=None, is_decode=is_decode)
+        p0 = T - 3 - c["chunk"]
+        out, md = call(x["q_prefill"], torch.arange(p0, p0 + c["chunk"], dtype=torch.int64), T - 3, False)
+        save[f"l{layer_id}_prefill_out"], save[f"l{layer_id}_prefill_indices"] = out.float().numpy(), md.indices.numpy()
+        save[f"l{layer_id}_prefill_ks"] = md.ks.numpy()
+        out0, md0 = call(x["q_decode"][0], torch.tensor([T - 3], dtype=torch.int64), T - 2, True)
+        save[f"l{layer_id}_decode_out"], save[f"l{layer_id}_decode_indices"] = out0.float().numpy(), md0.indices.numpy()
+        save[f"l{layer_id}_decode_ks"] = md0.ks.numpy()
+    np.savez_compressed(os.path.join(a.out, "serving_paged_extend.npz"), **save)
+    print("wrote serving_paged_extend.npz")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of DeepAuto-AI/hip-attention")
     ap.add_argument("--out", default=HERE)
     ap.add_argument("--skip-paged", action="store_true")
+    ap.add_argument("--only-extend", action="store_true", help="only the in-kernel RoPE run (serving_paged_extend.npz)")
     a = ap.parse_args()
     import gen_golden
     gen_golden._import_reference(a.reference)
@@ -96,6 +152,8 @@ def main():
     mrm = importlib.import_module("hip_attn.v1_2.mask_refresh_interval")
     md_mod = importlib.import_module("hip_attn.v1_2.attention_metadata")
 
+    if a.only_extend:
+        return paged_extend(a, importlib.import_module("hip_attn.v1_2.paged_hip"), cfgm)
     record = {"configs": {}, "bad": {}, "schedules": {}}
     for name, js in CONFIG_JSONS.items():
         record["configs"][name] = config_record(cfgm.HiPAttentionConfig(json_or_path=js))

@@ -57,7 +57,8 @@ def test_matches_reference_fixture(name):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "decode_fp16", "square_fp16", "oddsink_fp16",
                                   "shortwin_fp16", "paged_decode_fp16", "shard_nosink_fp16", "positions_fp16",
-                                  "softcap_fp16", "softcap_decode_fp16"])
+                                  "softcap_fp16", "softcap_decode_fp16", "rope_rel_fp16", "rope_str_fp16", "rope_decode_fp16",
+                                  "rope_mixed_fp32", "rope_str_decode_fp16"])
 def test_matches_oracle_all_dtypes(name, dtype):
     q, k, v, pos, c, cfg, paged = case_inputs(name, dtype)
     (ref, m) = _oracle(q, k, v, pos, cfg, paged)
@@ -66,7 +67,8 @@ def test_matches_oracle_all_dtypes(name, dtype):
     _check_out(out, ref, dtype)
 
 
-@pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "oddsink_fp16", "shortwin_fp16"])
+@pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "oddsink_fp16", "shortwin_fp16", "rope_rel_fp16",
+                                  "rope_mixed_fp32"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_scan_stage_outputs(name, dtype):
     """Per-head narrowed bounds and scores of every scan stage equal the oracle's, bit for bit."""
@@ -203,7 +205,13 @@ def test_invalid_arguments_raise_before_launch():
     with pytest.raises(ValueError):
         hip_attention_12(q, k, k[:, :512], HiPAttentionArgs())
     with pytest.raises(NotImplementedError):
-        hip_attention_12(q, k, k, HiPAttentionArgs(using_extend=True, need_apply_rope=True))
+        hip_attention_12(q, k, k, HiPAttentionArgs(using_extend=True, need_apply_rope=False))
+    with pytest.raises(ValueError):
+        hip_attention_12(q, k, k, HiPAttentionArgs(using_extend=True, need_apply_rope=True))   # no cos / sin tables
+    tab = torch.zeros(2048, 64, device="cuda")
+    with pytest.raises(NotImplementedError):
+        hip_attention_12(q, k, k, HiPAttentionArgs(using_extend=True, need_apply_rope=True, rope_cos=tab, rope_sin=tab,
+                                                   scan_extend_backend="dynamic_extend"))
     with pytest.raises(ValueError):
         hip_attention_12(q, k, k, HiPAttentionArgs(stages=[ScanStage(64, 4, 256, 128, 1)]))
     with pytest.raises(ValueError):

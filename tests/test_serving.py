@@ -259,3 +259,35 @@ def test_forward_paged_hip_has_the_reference_parameter_list():
         forward_paged_hip(*common, None, *rest, online_update_cache=True)
     with pytest.raises(NotImplementedError):
         forward_paged_hip(*common, None, *rest, diag_sliding_window_indices=torch.zeros(1))
+
+
+@pytest.mark.gpu
+def test_forward_paged_hip_with_in_kernel_rope_matches_the_reference():
+    """The serving default ``using_extend``: un-rotated keys in the pool and cos / sin tables handed to the call.  A
+    dense layer (scan backend streaming) and a sparse one, each a split prefill chunk and a decode step: masks
+    identical to the reference's, outputs within fp16 tolerance."""
+    from cases import rope_tables
+    from hip_attention_b200 import HiPAttentionConfig, forward_paged_hip
+    g = np.load(os.path.join(GOLD, "serving_paged_extend.npz"))
+    c = G.PAGED
+    x = {k_: v_.cuda() for k_, v_ in G.paged_inputs().items()}
+    cfg = HiPAttentionConfig(json_or_path=G.EXTEND_JSON)
+    assert cfg.using_extend
+    T = c["T"]
+    cos, sin = rope_tables(T + 8, c["D"], G.EXTEND_THETA)
+    cos, sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    for layer_id in (0, c["layer_id"]):
+        def call(q, positions, seq_len, is_decode):
+            return forward_paged_hip(q, c["sm_scale"], 1, x["k_pool"], x["v_pool"], None, positions.cuda(),
+                                     torch.tensor([seq_len], device="cuda"), x["req_to_tokens"], x["req_pool_indices"], cos, sin,
+                                     layer_id, 0.0, c["model_context"], T, not is_decode, cfg, None, None, None, False, None,
+                                     is_decode)
+        p0 = T - 3 - c["chunk"]
+        out, md = call(x["q_prefill"], torch.arange(p0, p0 + c["chunk"]), T - 3, False)
+        assert np.array_equal(md.indices.cpu().numpy(), g[f"l{layer_id}_prefill_indices"])
+        assert np.array_equal(md.ks.cpu().numpy(), g[f"l{layer_id}_prefill_ks"])
+        assert np.abs(out.float().cpu().numpy() - g[f"l{layer_id}_prefill_out"]).max() < 3e-3
+        out0, md0 = call(x["q_decode"][0], torch.tensor([T - 3]), T - 2, True)
+        assert np.array_equal(md0.indices.cpu().numpy(), g[f"l{layer_id}_decode_indices"])
+        assert np.array_equal(md0.ks.cpu().numpy(), g[f"l{layer_id}_decode_ks"])
+        assert np.abs(out0.float().cpu().numpy() - g[f"l{layer_id}_decode_out"]).max() < 3e-3

@@ -7,12 +7,20 @@ from oracle import hip_oracle as O
 
 def make_args(c, pos=None, **kw):
     from hip_attention_b200 import HiPAttentionArgs, ScanStage
+    sb = c.get("stage_backends") or [None] * len(c["stages"])
+    if "rope_in_kernel" in c:
+        from cases import rope_tables
+        dev = pos.device if pos is not None else "cpu"
+        cos, sin = rope_tables(max(c.get("ext", c["T"]), c["T"]) + 8, c["D"], c.get("rope_theta", 10000.0))
+        kw = dict(rope_cos=torch.from_numpy(cos).to(dev), rope_sin=torch.from_numpy(sin).to(dev),
+                  scan_extend_backend=c["rope_in_kernel"], sa_extend_backend="streaming", **kw)
     return HiPAttentionArgs(
         position_ids=pos, sliding_window_size=c["sw"], sink_token_size=c["sink"], block_size_k=64,
         second_stage_k=c["second_k"],
-        stages=[ScanStage(stage_block_size_q=bq, stage_block_stride_q=sq, stage_chunk_size=cs, stage_k=sk, stage_stride=1)
-                for (bq, sq, cs, sk) in c["stages"]],
-        block_sparse_block_size_q=c.get("bsa_bq", c["stages"][-1][0]), using_extend=False, need_apply_rope=False,
+        stages=[ScanStage(stage_block_size_q=bq, stage_block_stride_q=sq, stage_chunk_size=cs, stage_k=sk, stage_stride=1,
+                          stage_extend_backend=sb[i]) for i, (bq, sq, cs, sk) in enumerate(c["stages"])],
+        block_sparse_block_size_q=c.get("bsa_bq", c["stages"][-1][0]), using_extend="rope_in_kernel" in c,
+        need_apply_rope="rope_in_kernel" in c,
         disable_flashdecode=c.get("disable_flashdecode", False), logit_softcap=c.get("softcap"), **kw)
 
 
