@@ -30,19 +30,23 @@ namespace hipattn {
 namespace {
 
 // the CTA's small shared variables (behind the operand tiles in dynamic shared memory)
+// (kept at 56 bytes: with the 16-row operand tiles six CTAs share a multiprocessor's shared memory to the byte)
 struct ScanShared {
   unsigned long long mbar;
   uint32_t tmem;
   int abort;
-  int pmin;
-  float qmax;
-  int g[2][4];
-  int fetched[3];   // "some warp fetched rows in round r" for three consecutive rounds (r % 3)
+  int g[2][4];      // per-warp largest chunk of the current chunk block, double buffered; during set-up g[1][2] holds the
+                    // block's smallest position and g[1][3] the largest |pooled query| (read before g[1] is first written,
+                    // which happens behind the first chunk block's barrier)
+  unsigned char fetched[4];   // [r % 3]: "some warp fetched rows in round r"
+  int pad_;
 };
 constexpr uint32_t kScanSlack = 896;   // padding reserved in front of the tiles
 
+// Resident CTAs per multiprocessor the register allocation aims at: five with 16 or 32 pooled rows (measured faster
+// than six CTAs squeezed into 80 registers), four with 64, three with 128 (shared memory).
 template <int DT, int D, int NR>
-__global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int check) {
+__global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_stage_tcgen05_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int check) {
   constexpr int ROWB = D * 2;                 // bytes per key / query row
   constexpr int PIECES = ROWB / 16;
   constexpr int KB = D / 64;                  // 128-byte K-blocks per row
@@ -86,7 +90,7 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar));
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     sh.abort = 0;
-    sh.qmax = 0.f;
+    sh.g[1][3] = 0;
     sh.fetched[0] = sh.fetched[1] = sh.fetched[2] = 0;
   }
   if (warp == 0) {
@@ -113,16 +117,16 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) qmax_local = fmaxf(qmax_local, __shfl_xor_sync(0xffffffffu, qmax_local, o));
-  if (lane == 0) atomicMax(reinterpret_cast<int*>(&sh.qmax), __float_as_int(qmax_local));  // non-negative floats order as ints
+  if (lane == 0) atomicMax(&sh.g[1][3], __float_as_int(qmax_local));  // non-negative floats order as ints
   if (warp == 0) {
     const int m = block_min_position(p, b, t0, Rv, lane);
-    if (lane == 0) sh.pmin = m;
+    if (lane == 0) sh.g[1][2] = m;
   }
   fence_async_smem();
   __syncthreads();
 
-  const int pt = max(sh.pmin - p.scan_window, 0);
-  const float eps_q = kEps * sh.qmax;
+  const int pt = max(sh.g[1][2] - p.scan_window, 0);
+  const float eps_q = kEps * __int_as_float(sh.g[1][3]);
   const int n = p.n_chunks;
   const int64_t row = (int64_t)b * BDST + d;
   const char* kbase = reinterpret_cast<const char*>(p.k_scaled);
@@ -233,7 +237,7 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
       const float s_abs = idx >= 0 ? __ldg(p.key_abs + idx) : 0.f;
       // ---- gather this warp's 32 rows: 8 lanes per row, 128 contiguous bytes per row and instruction ----
       if (__any_sync(0xffffffffu, idx >= 0)) {   // a warp whose scores are all known (or inactive) copies nothing
-      if (lane == 0) *(volatile int*)&sh.fetched[rr % 3] = 1;
+      if (lane == 0) *(volatile unsigned char*)&sh.fetched[rr % 3] = 1;
 #pragma unroll
       for (int r0 = 0; r0 < 32; r0 += 4) {
         const int j = r0 + (lane >> 3);
@@ -254,8 +258,8 @@ __global__ void __launch_bounds__(128) scan_stage_tcgen05_kernel(const hipattn_s
       if (!__syncthreads_or(act || *(volatile int*)&sh.abort)) break;
       if (*(volatile int*)&sh.abort) { aborted = true; break; }
       // somebody fetched a row: the tile is multiplied; else every live score is known from the round before
-      const bool scored = *(volatile int*)&sh.fetched[rr % 3] != 0;
-      if (tid == 0) *(volatile int*)&sh.fetched[(rr + 2) % 3] = 0;   // next written two barriers from now
+      const bool scored = *(volatile unsigned char*)&sh.fetched[rr % 3] != 0;
+      if (tid == 0) *(volatile unsigned char*)&sh.fetched[(rr + 2) % 3] = 0;   // next written two barriers from now
       ++rr;
       if (scored && tid == 0) {
         tc_fence_after();
