@@ -12,7 +12,7 @@ F32, F16, BF16 = 0, 1, 2
 STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE, STATUS_TIMEOUT, STATUS_CHUNK_SIZE = 1, 2, 4, 8
 MAX_CHUNKS = 16384
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
-ABI_VERSION = 6
+ABI_VERSION = 7
 SCAN_AUTO, SCAN_STRICT, SCAN_CHECK = 0, 1, 2
 ROPE_NONE, ROPE_RELATIVE, ROPE_STREAMING = 0, 1, 2
 
@@ -23,7 +23,8 @@ class Tokens(C.Structure):
     _fields_ = [("dense", vp), ("stride_b", i64), ("stride_t", i64), ("stride_h", i64),
                 ("cache", vp), ("stride_page", i64), ("stride_off", i64), ("stride_ch", i64),
                 ("block_table", vp), ("table_stride_b", i64), ("cache_seq_lens", vp), ("n_pages", i64),
-                ("table_width", i32), ("table_is_i64", i32), ("seq_lens_is_i64", i32), ("page_size", i32)]
+                ("table_width", i32), ("table_is_i64", i32), ("seq_lens_is_i64", i32), ("page_size", i32),
+                ("fp8_e5m2", i32), ("reserved_", i32)]
 
 
 class ScanParams(C.Structure):

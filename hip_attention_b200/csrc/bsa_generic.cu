@@ -171,12 +171,15 @@ __global__ void __launch_bounds__(kThreads) bsa_generic_kernel(const hipattn_bsa
       if (t >= 0) {
         const char* kr = token_row(p.k, b, t, hkv, Elem<DT>::bytes, p.status);
         const char* vr = token_row(p.v, b, t, hkv, Elem<DT>::bytes, p.status);
-        widen16<DT>(*reinterpret_cast<const uint4*>(kr + pc * 16), kv);
-        widen16<DT>(*reinterpret_cast<const uint4*>(vr + pc * 16), vv);
+        constexpr int KDT = DT == HIPATTN_F32 ? HIPATTN_F16 : DT;   // (an fp8 cache is only accepted with 16-bit queries)
+        const bool k8 = DT != HIPATTN_F32 && p.k.fp8_e5m2, v8 = DT != HIPATTN_F32 && p.v.fp8_e5m2;
+        widen16<DT>(k8 ? widen_fp8_e5m2<KDT>(*reinterpret_cast<const uint2*>(kr + pc * 8)) : *reinterpret_cast<const uint4*>(kr + pc * 16), kv);
+        widen16<DT>(v8 ? widen_fp8_e5m2<KDT>(*reinterpret_cast<const uint2*>(vr + pc * 8)) : *reinterpret_cast<const uint4*>(vr + pc * 16), vv);
         if (p.rope_cos) {   // in-kernel RoPE: the key at the position its place in the list maps to
           constexpr int HALF = PIECES / 2;
           float xr[VEC], tc[VEC], ts[VEC];
-          widen16<DT>(*reinterpret_cast<const uint4*>(kr + (pc < HALF ? pc + HALF : pc - HALF) * 16), xr);
+          const int pr = pc < HALF ? pc + HALF : pc - HALF;
+          widen16<DT>(k8 ? widen_fp8_e5m2<KDT>(*reinterpret_cast<const uint2*>(kr + pr * 8)) : *reinterpret_cast<const uint4*>(kr + pr * 16), xr);
           const int new_t = rope_key_position(kl, j0 + kk, t, p.window);
           rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, new_t, pc % HALF, tc);
           rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, new_t, pc % HALF, ts);

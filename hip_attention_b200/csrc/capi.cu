@@ -23,6 +23,10 @@ void set_error(const char* fmt, ...) {
 }
 
 int validate_tokens(const hipattn_tokens_t& t, int elem_bytes, int D, const char* name) {
+  if (t.fp8_e5m2) {
+    HIPATTN_REQUIRE(elem_bytes == 2, HIPATTN_ERR_UNSUPPORTED, "%s: an fp8 cache needs 16-bit queries", name);
+    elem_bytes = 2;   // 8-byte pieces of 1-byte elements: the same "multiple of 8 elements" rule as 16-byte pieces of 2-byte ones
+  }
   const int64_t row_align = 16 / elem_bytes;
   if (t.cache != nullptr) {
     HIPATTN_REQUIRE(t.block_table && t.cache_seq_lens, HIPATTN_ERR_INVALID, "%s: paged cache without block_table / cache_seq_lens", name);
@@ -100,6 +104,12 @@ extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream
   if (rc) return rc;
   rc = validate_tokens(p->v, eb, p->D, "v");
   if (rc) return rc;
+  if (p->k.fp8_e5m2 || p->v.fp8_e5m2) {
+    // an fp8 KV cache is read by the general kernel (prefill and decode, key splits included), RoPE or not
+    if (p->rope_cos || p->rope_sin)
+      HIPATTN_REQUIRE(p->rope_cos && p->rope_sin && p->rope_rows > 0, HIPATTN_ERR_INVALID, "attention: cos and sin tables go together");
+    return bsa_generic(*p, (cudaStream_t)stream);
+  }
   if (p->rope_cos || p->rope_sin) {
     // in-kernel RoPE is built into the general kernel only (prefill and decode, key splits included)
     HIPATTN_REQUIRE(p->rope_cos && p->rope_sin && p->rope_rows > 0, HIPATTN_ERR_INVALID, "attention: cos and sin tables go together");
@@ -162,4 +172,4 @@ extern "C" int hipattn_debug_bounded_wait(uint32_t* status, void* stream) {
 
 extern "C" uint64_t hipattn_launch_count(void) { return hipattn::g_launches.load(std::memory_order_relaxed); }
 extern "C" const char* hipattn_error_string(void) { return g_error; }
-extern "C" int hipattn_abi_version(void) { return 6; }
+extern "C" int hipattn_abi_version(void) { return 7; }

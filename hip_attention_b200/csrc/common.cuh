@@ -102,6 +102,7 @@ __device__ __forceinline__ unsigned long long score_sort_key(int32_t code, unsig
 // read page 0 (as the reference does: the table lookup is masked with other=0).
 __device__ __forceinline__ const char* token_row(const hipattn_tokens_t& tk, int b, int64_t t, int hkv, int elem_bytes,
                                                  uint32_t* status) {
+  if (tk.fp8_e5m2) elem_bytes = 1;
   if (tk.cache == nullptr) {
     int64_t off = (int64_t)b * tk.stride_b + t * tk.stride_t + (int64_t)hkv * tk.stride_h;
     return (const char*)tk.dense + off * elem_bytes;
@@ -130,6 +131,23 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Eight e5m2 values (8 bytes) as eight elements of the 16-bit type DT.  An e5m2 value is the upper byte of the
+// half-precision number with the same value, and every such number is also exact in bfloat16, so the conversion
+// loses nothing (the reference converts the same way on load, uvm_gpu_cache.py:1043-1046).
+template <int DT>
+__device__ __forceinline__ uint4 widen_fp8_e5m2(uint2 w) {
+  const uint32_t h[4] = {__byte_perm(w.x, 0, 0x1404), __byte_perm(w.x, 0, 0x3424), __byte_perm(w.y, 0, 0x1404), __byte_perm(w.y, 0, 0x3424)};
+  if (DT == HIPATTN_F16) return make_uint4(h[0], h[1], h[2], h[3]);
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+    __nv_bfloat162 b2 = __floats2bfloat162_rn(f.x, f.y);
+    o[i] = *reinterpret_cast<uint32_t*>(&b2);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {

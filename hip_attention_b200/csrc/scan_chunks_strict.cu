@@ -308,6 +308,7 @@ int scan_chunks_strict(const hipattn_scan_params_t& p, cudaStream_t stream, bool
   const int R = p.block_size_q / p.stride_q;
   const int rows = min(R, cdiv(p.TQ, p.stride_q));
   if (rows > 1 || (p.D != 64 && p.D != 128 && p.D != 256)) return HIPATTN_OK;
+  if (p.k.fp8_e5m2) return HIPATTN_OK;   // an fp8 cache goes through the round-by-round kernel
   const int C = p.chunk_size;
   if (C < 4 || C > 32 || (C & (C - 1)) != 0) return HIPATTN_OK;
   const char* v = getenv("HIPATTN_DECODE_SCAN");

@@ -200,8 +200,13 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
         const int rr = r0 + sub;             // staged row: side * 32 + owner lane
         const int owner = rr & 31, side = rr >> 5;
         const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)(side ? src_r : src_l), owner);
-        if (a != 0ull && sub < kRowsPerIter)
-          cp_async16(wstage + (size_t)rr * G::kRowStride + piece * 16, (const char*)a + piece * 16);
+        if (a != 0ull && sub < kRowsPerIter) {
+          if (DT != HIPATTN_F32 && p.k.fp8_e5m2)   // an fp8 cache: 8 bytes become one 16-byte piece of the element type
+            *reinterpret_cast<uint4*>(wstage + (size_t)rr * G::kRowStride + piece * 16) =
+                widen_fp8_e5m2<DT == HIPATTN_F32 ? HIPATTN_F16 : DT>(__ldg(reinterpret_cast<const uint2*>((const char*)a + piece * 8)));
+          else
+            cp_async16(wstage + (size_t)rr * G::kRowStride + piece * 16, (const char*)a + piece * 16);
+        }
       }
     } else {  // rows longer than 512 bytes: every lane copies several pieces
       for (int rr = 0; rr < 64; ++rr) {

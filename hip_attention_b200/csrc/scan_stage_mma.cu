@@ -375,6 +375,7 @@ int scan_stage_mma(const hipattn_scan_params_t& p, cudaStream_t stream, bool* ha
   const int R = p.block_size_q / p.stride_q;
   const int rows = min(R, cdiv(p.TQ, p.stride_q));
   if (p.mode == 1 || p.dtype == HIPATTN_F32 || rows <= 1 || (R % 16) != 0 || (p.D != 64 && p.D != 128)) return HIPATTN_OK;
+  if (p.k.fp8_e5m2) return HIPATTN_OK;   // an fp8 cache is read by the strict kernel (or through the prepared 16-bit copy)
   *handled = true;
   if (p.dtype == HIPATTN_BF16) return p.D == 128 ? dispatch_rows<HIPATTN_BF16, 128>(p, stream) : dispatch_rows<HIPATTN_BF16, 64>(p, stream);
   return p.D == 128 ? dispatch_rows<HIPATTN_F16, 128>(p, stream) : dispatch_rows<HIPATTN_F16, 64>(p, stream);

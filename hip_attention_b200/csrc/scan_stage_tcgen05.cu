@@ -403,7 +403,8 @@ __global__ void scan_prepare_keys_kernel(const hipattn_tokens_t k, int D, int B,
     const int64_t bt = r / HKV;
     const int t = (int)(bt % T), b = (int)(bt / T);
     const char* src = token_row(k, b, t, hkv, 2, status);
-    const uint4 w = *reinterpret_cast<const uint4*>(src + piece * 16);
+    const uint4 w = k.fp8_e5m2 ? widen_fp8_e5m2<DT>(*reinterpret_cast<const uint2*>(src + piece * 8))
+                               : *reinterpret_cast<const uint4*>(src + piece * 16);
     uint32_t v[4] = {w.x, w.y, w.z, w.w};
     float s = 0.f;
 #pragma unroll

@@ -32,6 +32,9 @@ _DT = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
 INT64_MAX = torch.iinfo(torch.int64).max
 SCORE_INIT = -32000.0
 _status_words = {}
+# an fp8 KV cache: e5m2 values, handed over as float8_e5m2 or as the uint8 view the serving adapter makes of it
+# (paged_hip.py:409-418); every value is read as the 16-bit number it converts to exactly
+_FP8 = (torch.float8_e5m2, torch.uint8)
 _ROPE_MODES = {"relative": L.ROPE_RELATIVE, "streaming": L.ROPE_STREAMING}
 
 
@@ -95,6 +98,7 @@ def _tokens(dense: Optional[Tensor], cache: Optional[Tensor], table: Optional[Te
         if not seq_lens.is_contiguous():
             raise ValueError("cache_seq_lens must be contiguous")
         t.cache = cache.data_ptr()
+        t.fp8_e5m2 = int(cache.dtype in _FP8)
         t.stride_page, t.stride_off, t.stride_ch = cache.stride(0), cache.stride(1), cache.stride(2)
         t.block_table = table.data_ptr()
         t.table_stride_b = table.stride(0)
@@ -110,6 +114,7 @@ def _tokens(dense: Optional[Tensor], cache: Optional[Tensor], table: Optional[Te
         if dense.ndim != 4 or dense.stride(-1) != 1:
             raise ValueError(f"{what} must be [B, T, kv_heads, head_dim] with a contiguous last dim")
         t.dense = dense.data_ptr()
+        t.fp8_e5m2 = int(dense.dtype in _FP8)
         t.stride_b, t.stride_t, t.stride_h = dense.stride(0), dense.stride(1), dense.stride(2)
     return t
 
@@ -466,12 +471,18 @@ def _check_inputs(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args: HiP
     for name, t in (("k", k), ("v", v), ("k_cache", args.k_cache), ("v_cache", args.v_cache), ("q_mask", args.q_mask),
                     ("k_mask", args.k_mask)):
         if t is not None:
-            if t.dtype != q.dtype:
-                raise NotImplementedError(f"{name} dtype {t.dtype} differs from q dtype {q.dtype} (fp8 KV is not built yet)")
+            if t.dtype in _FP8 and name in ("k", "v", "k_cache", "v_cache"):
+                if q.dtype == torch.float32:
+                    raise NotImplementedError("an fp8 (e5m2) KV cache needs float16 or bfloat16 queries")
+            elif t.dtype != q.dtype:
+                raise NotImplementedError(f"{name} dtype {t.dtype} differs from q dtype {q.dtype}")
             if t.device != q.device:
                 raise ValueError(f"{name} is on {t.device}, q on {q.device}")
     if k is not None and k.shape != v.shape:
         raise ValueError("k and v must have the same shape")
+    for a_, b_, what in ((k, v, "k and v"), (args.k_cache, args.v_cache, "k_cache and v_cache")):
+        if a_ is not None and b_ is not None and (a_.dtype in _FP8) != (b_.dtype in _FP8):
+            raise NotImplementedError(f"{what} must both be fp8 or both be q's dtype")
     if k is None and args.k_cache is None:
         raise ValueError("k is None and args.k_cache is None")
     if args.k_cache is not None and args.v_cache is None:

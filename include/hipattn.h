@@ -43,7 +43,7 @@ extern "C" {
  * Where the rows of K (or V) live: a dense tensor [B, T, HKV, D] or a page pool
  * [n_pages, P, HKV, D] addressed through block_table[b, t / P] (src/hip_attn/v1_2/uvm_gpu_cache.py:865-890,
  * 1034-1042).  Strides are in elements; the last dimension must be contiguous and every row must
- * start on a 16-byte boundary.  `cache != NULL` selects paging.
+ * start on a 16-byte boundary (8 bytes for an fp8 cache).  `cache != NULL` selects paging.
  */
 typedef struct hipattn_tokens {
   const void* dense;
@@ -58,6 +58,10 @@ typedef struct hipattn_tokens {
   int32_t table_is_i64;
   int32_t seq_lens_is_i64;
   int32_t page_size;
+  int32_t fp8_e5m2;          /* 1: the rows hold 1-byte e5m2 values (an fp8 KV cache, uvm_gpu_cache.py:1043-1046,
+                                paged_hip.py:409-418); strides are then in bytes and every value is used as the 16-bit
+                                number it converts to exactly.  Needs a 16-bit q. */
+  int32_t reserved_;
 } hipattn_tokens_t;
 
 #define HIPATTN_ROPE_NONE 0

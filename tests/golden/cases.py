@@ -82,6 +82,12 @@ CASES = {
     "rope_str_decode_fp16": dict(B=2, TQ=1, T=1024, H=4, HKV=2, D=128, dtype="fp16", sink=32, sw=128, second_k=128,
                                  stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=31, rope_in_kernel="streaming",
                                  rope_theta=10000.0),
+    # fp8 KV: k and v are e5m2 values, handed to the operator as 1-byte tensors (make_inputs returns them widened to
+    # the case dtype, which is exact; the generator and the GPU tests pass the 1-byte form)
+    "fp8_prefill_fp16": dict(B=2, TQ=100, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                             stages=[(64, 2, 32, None), (64, 1, 8, 256)], seed=32, kv_fp8=True),
+    "fp8_decode_fp16": dict(B=2, TQ=1, T=2048, H=8, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                            stages=[(64, 4, 64, None), (64, 4, 16, 512), (64, 1, 4, 256)], seed=33, kv_fp8=True),
     # benchmark configuration 1 shape (fp32, 4096 x 4096, 8/2 heads, D 64)
     "config1_fp32": dict(B=1, TQ=4096, T=4096, H=8, HKV=2, D=64, dtype="fp32", sink=64, sw=256,
                          second_k=512, stages=[(64, 4, 32, None), (64, 1, 8, 1024)], seed=101,
@@ -140,8 +146,10 @@ def make_inputs(name: str):
         k = apply_rope(k, kpos, c["rope_theta"])
     q = q * np.float32(D ** -0.5)
     dt = torch_dtype(c["dtype"])
-    return (torch.from_numpy(q).to(dt), torch.from_numpy(k).to(dt), torch.from_numpy(v).to(dt),
-            torch.from_numpy(pos), c)
+    kt, vt = torch.from_numpy(k), torch.from_numpy(v)
+    if c.get("kv_fp8"):
+        kt, vt = kt.to(torch.float8_e5m2).float(), vt.to(torch.float8_e5m2).float()
+    return (torch.from_numpy(q).to(dt), kt.to(dt), vt.to(dt), torch.from_numpy(pos), c)
 
 
 def make_paged(k: torch.Tensor, v: torch.Tensor, page: int, seed: int, extra_pages: int = 7):

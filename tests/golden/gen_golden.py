@@ -122,6 +122,8 @@ def main():
             out, md = op(q, None, None, args=args)
         else:
             args = mk()
+            if c.get("kv_fp8"):   # the 1-byte form the serving adapter hands over (paged_hip.py:409-418)
+                k, v = k.to(torch.float8_e5m2).view(torch.uint8), v.to(torch.float8_e5m2).view(torch.uint8)
             out, md = op(q, k, v, args=args)
         el = time.time() - t0
         rs = c.get("out_row_stride", 1)

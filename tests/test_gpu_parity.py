@@ -58,7 +58,7 @@ def test_matches_reference_fixture(name):
 @pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "decode_fp16", "square_fp16", "oddsink_fp16",
                                   "shortwin_fp16", "paged_decode_fp16", "shard_nosink_fp16", "positions_fp16",
                                   "softcap_fp16", "softcap_decode_fp16", "rope_rel_fp16", "rope_str_fp16", "rope_decode_fp16",
-                                  "rope_mixed_fp32", "rope_str_decode_fp16"])
+                                  "rope_mixed_fp32", "rope_str_decode_fp16", "fp8_prefill_fp16", "fp8_decode_fp16"])
 def test_matches_oracle_all_dtypes(name, dtype):
     q, k, v, pos, c, cfg, paged = case_inputs(name, dtype)
     (ref, m) = _oracle(q, k, v, pos, cfg, paged)
@@ -266,6 +266,45 @@ def _attention_below_T(q, k, v, pos, m, cfg):
                 s = s.masked_fill(~allow, float("-inf"))
                 out[b, r0:r1, h] = torch.nan_to_num(torch.softmax(s, -1)) @ v[b, cols, h // G].double()
     return out
+
+
+@pytest.mark.parametrize("name", ["fp8_prefill_fp16", "fp8_decode_fp16"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fp8_cache_forms_agree(name, dtype):
+    """An fp8 (e5m2) KV cache as a dense 1-byte tensor, as a permuted page pool, and as the uint8 view a serving
+    adapter makes of it: identical masks and outputs; float32 queries are refused."""
+    from cases import make_paged
+    from hip_attention_b200 import hip_attention_impl
+    q, k, v, pos, c, cfg, _ = case_inputs(name, dtype)
+    out_d, md_d = run_gpu(q, k, v, pos, c, None)
+    kc, vc, table = make_paged(k, v, 16, 11)
+    for view in (torch.float8_e5m2, torch.uint8):
+        k8, v8 = kc.to(torch.float8_e5m2).view(view).cuda(), vc.to(torch.float8_e5m2).view(view).cuda()
+        args = make_args(c, pos.cuda(), k_cache=k8, v_cache=v8, block_table=table.cuda(),
+                         cache_seq_lens=torch.full((c["B"],), c["T"], dtype=torch.int64, device="cuda"), extend_context_length=c["T"])
+        out_p, md_p = hip_attention_impl(q.cuda(), None, None, args)
+        assert torch.equal(md_p.indices, md_d.indices) and torch.equal(md_p.ks, md_d.ks)
+        assert torch.equal(out_p, out_d)
+    with pytest.raises(NotImplementedError):
+        hip_attention_impl(q.float().cuda(), k.to(torch.float8_e5m2).cuda(), v.to(torch.float8_e5m2).cuda(), make_args(c, pos.cuda()))
+
+
+def test_fp8_cache_on_the_benchmark_shape():
+    """Head dim 128, bf16 queries, fp8 keys and values (prefill through the prepared 16-bit key copy and the tensor-core
+    scan): the mask equals the one of the same call on the widened values, the output stays within tolerance of it."""
+    import bench
+    from hip_attention_b200 import hip_attention_impl, read_status
+    w = dict(bench.WORKLOADS["prefill_128k"], TQ=512, T=8192, keep=[4096, 2048, 1024])
+    q, k, v = bench.make_qkv(w, "cuda")
+    k8, v8 = k.to(torch.float8_e5m2), v.to(torch.float8_e5m2)
+    read_status("cuda")
+    out8, md8 = hip_attention_impl(q, k8, v8, bench.make_args(w))
+    out16, md16 = hip_attention_impl(q, k8.to(q.dtype), v8.to(q.dtype), bench.make_args(w))
+    torch.cuda.synchronize()
+    assert read_status("cuda") == 0
+    assert torch.equal(md8.indices, md16.indices) and torch.equal(md8.ks, md16.ks)
+    d = (out8.float() - out16.float()).abs()
+    assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3
 
 
 def test_unbuilt_stage_flags_are_refused():

@@ -53,6 +53,8 @@ def run_gpu(q, k, v, pos, c, paged, dev="cuda", **kw):
         args = make_args(c, pos.to(dev), k_cache=kc.to(dev), v_cache=vc.to(dev), block_table=table.to(dev),
                          cache_seq_lens=seq.to(dev), extend_context_length=ext)
         return hip_attention_impl(q.to(dev), None, None, args, **kw)
+    if c.get("kv_fp8") and q.dtype != torch.float32:
+        k, v = k.to(torch.float8_e5m2), v.to(torch.float8_e5m2)
     return hip_attention_impl(q.to(dev), k.to(dev), v.to(dev), make_args(c, pos.to(dev)), **kw)
 
 
