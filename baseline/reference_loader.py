@@ -68,5 +68,6 @@ def reference_args(Args, ScanStage, *, bq, strides, chunks, keep, sink, sw, **kw
     """Reference argument object for a stage list given as chunk sizes / kept tokens / query strides."""
     stages = [ScanStage(stage_block_size_q=bq, stage_block_stride_q=strides[i], stage_chunk_size=c,
                         stage_k=None if i == 0 else keep[i - 1], stage_stride=1) for i, c in enumerate(chunks)]
+    kw.setdefault("require_cache_statistics", False)   # the benchmarks of this project switch the access counters off
     return Args(sink_token_size=sink, sliding_window_size=sw, second_stage_k=keep[-1], stages=stages,
                 block_sparse_block_size_q=bq, using_extend=False, need_apply_rope=False, **kw)

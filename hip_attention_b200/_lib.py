@@ -12,7 +12,7 @@ F32, F16, BF16 = 0, 1, 2
 STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE, STATUS_TIMEOUT, STATUS_CHUNK_SIZE = 1, 2, 4, 8
 MAX_CHUNKS = 16384
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
-ABI_VERSION = 7
+ABI_VERSION = 8
 SCAN_AUTO, SCAN_STRICT, SCAN_CHECK = 0, 1, 2
 ROPE_NONE, ROPE_RELATIVE, ROPE_STREAMING = 0, 1, 2
 
@@ -36,7 +36,8 @@ class ScanParams(C.Structure):
                 ("dtype", i32), ("D", i32), ("B", i32), ("TQ", i32), ("H", i32), ("HKV", i32), ("T", i32),
                 ("block_size_q", i32), ("stride_q", i32), ("n_chunks", i32), ("block_chunk", i32),
                 ("scan_window", i32), ("q_scale", f32), ("k_scale", f32), ("mode", i32), ("chunk_size", i32),
-                ("rope_cos", vp), ("rope_sin", vp), ("rope_stride", i64), ("rope_rows", i32), ("rope_mode", i32)]
+                ("rope_cos", vp), ("rope_sin", vp), ("rope_stride", i64), ("rope_rows", i32), ("rope_mode", i32),
+                ("access_counter", vp), ("access_stride_b", i64), ("access_stride_h", i64), ("access_n", i32), ("reserved_", i32)]
 
 
 class BsaParams(C.Structure):
@@ -63,6 +64,7 @@ SYMBOLS = {
     "hipattn_finalize_indices": (i32, [vp, vp, i64, i64, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     "hipattn_bsa_attention": (i32, [C.POINTER(BsaParams), vp]),
     "hipattn_merge_partials": (i32, [vp, vp, i64, i32, i32, i32, vp, i64, vp, vp]),
+    "hipattn_mark_attention_access": (i32, [C.POINTER(BsaParams), vp, i64, i64, i32, i32, vp]),
     "hipattn_bsa_decode_noalloc": (i32, [C.POINTER(BsaParams), vp]),
     "hipattn_encode_score": (i32, [f32]),
     "hipattn_decode_score": (f32, [i32]),

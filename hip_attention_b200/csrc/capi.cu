@@ -73,10 +73,66 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
   if (lse_out && threadIdx.x == 0) lse_out[row] = tot > 0.f ? m + log2f(tot) : -INFINITY;
 }
 
+// Access statistics of the attention: one CTA per (batch, KV head, attention block) marks the tokens the reference's
+// kernels load for that block (see hipattn_mark_attention_access in the header).
+__global__ void mark_attention_access_kernel(const hipattn_bsa_params_t p, int32_t* counter, int64_t stride_b, int64_t stride_h,
+                                             int n, int window_block_rows) {
+  __shared__ int s_pmax;
+  const int NBLK = cdiv(p.TQ, p.block_size_q);
+  int64_t bid = blockIdx.x;
+  const int d = (int)(bid % NBLK); bid /= NBLK;
+  const int hkv = (int)(bid % p.HKV); bid /= p.HKV;
+  const int b = (int)bid;
+  const int t0 = d * p.block_size_q, rows = min(p.block_size_q, p.TQ - t0);
+  if (threadIdx.x == 0) s_pmax = -1;
+  __syncthreads();
+  int hi = -1;
+  for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+    const long long x = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(t0 + i) * p.pos_stride_t];
+    hi = max(hi, (int)(x > 0x7ffffff0LL ? 0x7ffffff0LL : (x < 0 ? 0 : x)));
+  }
+  if (hi >= 0) atomicMax(&s_pmax, hi);
+  __syncthreads();
+  const int cur = s_pmax + 1;   // one past the block's last position
+  if (cur <= 0) return;
+  const int h = hkv * (p.H / p.HKV);
+  const int64_t nrow = (int64_t)b * p.H + h;
+  const int d_idx = (int)(((int64_t)d * p.block_size_q) / p.index_block_q);
+  long long ks = p.ks[nrow * p.ks_stride_n + (int64_t)d_idx * p.ks_stride_d];
+  ks = ks < 0 ? 0 : (ks > p.K ? p.K : ks);
+  const int64_t* idx = p.indices + nrow * p.idx_stride_n + (int64_t)d_idx * p.idx_stride_d;
+  for (int t = threadIdx.x; t < min(p.sink, cur); t += blockDim.x) mark_access(counter, stride_b, stride_h, n, p.k, b, hkv, t);
+  for (int j = threadIdx.x; j < (int)ks * p.block_size_k; j += blockDim.x) {
+    const long long t = idx[j / p.block_size_k] + j % p.block_size_k;
+    if (t >= p.sink && t < cur && t < p.T) mark_access(counter, stride_b, stride_h, n, p.k, b, hkv, t);
+  }
+  if (p.window > 0)
+    for (int t = max(0, cur - p.window - window_block_rows) + threadIdx.x; t < cur; t += blockDim.x)
+      mark_access(counter, stride_b, stride_h, n, p.k, b, hkv, t);
+}
+
 }  // namespace
 }  // namespace hipattn
 
 using namespace hipattn;
+
+extern "C" int hipattn_mark_attention_access(const hipattn_bsa_params_t* p, int32_t* counter, int64_t stride_b, int64_t stride_h,
+                                             int32_t n, int32_t window_block_rows, void* stream) {
+  HIPATTN_REQUIRE(p != nullptr && counter != nullptr, HIPATTN_ERR_INVALID, "mark_attention_access: null pointer");
+  HIPATTN_REQUIRE(p->pos && p->indices && p->ks, HIPATTN_ERR_INVALID, "mark_attention_access: pos, indices and ks are required");
+  HIPATTN_REQUIRE(p->B > 0 && p->TQ > 0 && p->H > 0 && p->HKV > 0 && p->H % p->HKV == 0 && p->T > 0 && n > 0, HIPATTN_ERR_INVALID,
+                  "mark_attention_access: bad shape");
+  HIPATTN_REQUIRE(p->block_size_q > 0 && p->index_block_q >= p->block_size_q && p->index_block_q % p->block_size_q == 0 &&
+                      p->block_size_k > 0 && p->K >= 0 && window_block_rows >= 0,
+                  HIPATTN_ERR_INVALID, "mark_attention_access: bad mask geometry");
+  if (p->k.cache != nullptr)
+    HIPATTN_REQUIRE(p->k.block_table && p->k.cache_seq_lens && p->k.page_size > 0, HIPATTN_ERR_INVALID,
+                    "mark_attention_access: paged keys without block_table / cache_seq_lens");
+  const int64_t grid = (int64_t)p->B * p->HKV * cdiv(p->TQ, p->block_size_q);
+  HIPATTN_REQUIRE(grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "mark_attention_access: grid of %lld blocks", (long long)grid);
+  mark_attention_access_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(*p, counter, stride_b, stride_h, n, window_block_rows);
+  return check_launch("mark_attention_access_kernel");
+}
 
 extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream) {
   HIPATTN_REQUIRE(p != nullptr, HIPATTN_ERR_INVALID, "attention params are null");
@@ -172,4 +228,4 @@ extern "C" int hipattn_debug_bounded_wait(uint32_t* status, void* stream) {
 
 extern "C" uint64_t hipattn_launch_count(void) { return hipattn::g_launches.load(std::memory_order_relaxed); }
 extern "C" const char* hipattn_error_string(void) { return g_error; }
-extern "C" int hipattn_abi_version(void) { return 7; }
+extern "C" int hipattn_abi_version(void) { return 8; }

@@ -122,6 +122,23 @@ __device__ __forceinline__ const char* token_row(const hipattn_tokens_t& tk, int
   return (const char*)tk.cache + off * elem_bytes;
 }
 
+// Access statistics: 1 at the position (dense) or page (paged: the block-table entry, page 0 beyond the sequence) of
+// token t in counter [B, HKV, n] (uvm_gpu_cache.py:846-909 stores the same 1 on every load).
+__device__ __forceinline__ void mark_access(int32_t* counter, int64_t stride_b, int64_t stride_h, int n, const hipattn_tokens_t& tk,
+                                            int b, int hkv, int64_t t) {
+  int64_t i = t;
+  if (tk.cache != nullptr) {
+    const int64_t seq = tk.seq_lens_is_i64 ? ((const int64_t*)tk.cache_seq_lens)[b] : (int64_t)((const int32_t*)tk.cache_seq_lens)[b];
+    const int64_t pi = t / tk.page_size;
+    i = 0;
+    if (t >= 0 && t < seq && pi < tk.table_width) {
+      const int64_t o = (int64_t)b * tk.table_stride_b + pi;
+      i = tk.table_is_i64 ? ((const int64_t*)tk.block_table)[o] : (int64_t)((const int32_t*)tk.block_table)[o];
+    }
+  }
+  if (i >= 0 && i < n) counter[(int64_t)b * stride_b + (int64_t)hkv * stride_h + i] = 1;
+}
+
 // two floats rounded to the 16-bit element type and packed, low half first
 template <int DT>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {

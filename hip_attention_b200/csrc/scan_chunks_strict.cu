@@ -239,6 +239,10 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
       for (int it = 0; it < rounds; ++it) {
         if (!(wl < wr && wl <= pt && wl >= 0)) break;
         const int mid = (wl + wr) >> 1;
+        if (p.access_counter) {   // the rows the reference's round would have loaded
+          mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, (wl + mid) >> 1);
+          mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, (mid + wr) >> 1);
+        }
         const float sl = sc[min(((wl + mid) >> 1) - l, C - 1)];
         const float sr = sc[min(((mid + wr) >> 1) - l, C - 1)];
         const bool win = sl > sr;

@@ -175,6 +175,10 @@ __global__ void __launch_bounds__(128) scan_stage_mma_kernel(const hipattn_scan_
       }
       if (!known_l) src_l = token_row(p.k, b, tl, hkv, 2, p.status);
       if (!known_r) src_r = token_row(p.k, b, tr, hkv, 2, p.status);
+      if (p.access_counter) {   // (a candidate whose score is known was marked when it was fetched)
+        if (!known_l) mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, tl);
+        if (!known_r) mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, tr);
+      }
     }
     if (!__any_sync(0xffffffffu, src_l != nullptr || src_r != nullptr)) {
       // every live chunk knows both scores (both candidates are the previous winner): equal scores keep the right half

@@ -232,6 +232,7 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
           tk = min(max(tk, 0), p.T - 1);
         }
         idx = (b * p.HKV + hkv) * p.T + tk;
+        if (p.access_counter) mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, tk);
       }
       // the key's magnitude is needed only after the MMA: requested here, its latency hides behind the row copies
       const float s_abs = idx >= 0 ? __ldg(p.key_abs + idx) : 0.f;

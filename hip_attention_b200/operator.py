@@ -226,7 +226,7 @@ class PhaseTimer:
 def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, args: HiPAttentionArgs,
                    restart: Optional[Tuple[int, Tensor, Tensor]], want_stage_inputs: bool,
                    debug: Optional[dict] = None, score_reduce=None, timer: Optional[PhaseTimer] = None,
-                   rope: Optional[Tuple[Tensor, Tensor]] = None) -> _Mask:
+                   rope: Optional[Tuple[Tensor, Tensor]] = None, access: Optional[Tensor] = None) -> _Mask:
     """Run the scan stages.  ``score_reduce(score_int32)`` is called after every scan, before the
     selection: a KV-head-parallel caller all-reduces (MAX) the head-reduced scores there."""
     lib = L.load()
@@ -309,6 +309,9 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         sp.q_scale, sp.k_scale = q_scale, k_scale
         sp.mode = _scan_mode()
         sp.chunk_size = s_i.stage_chunk_size
+        if access is not None:
+            sp.access_counter, sp.access_n = access.data_ptr(), access.shape[-1]
+            sp.access_stride_b, sp.access_stride_h = access.stride(0), access.stride(1)
         if rope is not None:
             sp.rope_cos, sp.rope_sin = rope[0].data_ptr(), rope[1].data_ptr()
             sp.rope_stride, sp.rope_rows = rope[0].stride(0), rope[0].shape[0]
@@ -413,7 +416,7 @@ def _decode_splits(B: int, HKV: int, total_tokens: int) -> int:
 def _attention(q: Tensor, ktok: L.Tokens, vtok: L.Tokens, T: int, HKV: int, pos: Tensor, indices: Tensor, ks: Tensor,
                *, sink: int, window: int, block_size_k: int, bsa_block_q: int, index_block_q: int, heads_share: bool,
                decode: bool, softcap: Optional[float], want_lse: bool,
-               rope: Optional[Tuple[Tensor, Tensor]] = None) -> Tuple[Tensor, Optional[Tensor]]:
+               rope: Optional[Tuple[Tensor, Tensor]] = None, access: Optional[Tensor] = None) -> Tuple[Tensor, Optional[Tensor]]:
     lib = L.load()
     dev = q.device
     st = _stream(dev)
@@ -439,6 +442,9 @@ def _attention(q: Tensor, ktok: L.Tokens, vtok: L.Tokens, T: int, HKV: int, pos:
     if rope is not None:
         bp.rope_cos, bp.rope_sin = rope[0].data_ptr(), rope[1].data_ptr()
         bp.rope_stride, bp.rope_rows = rope[0].stride(0), rope[0].shape[0]
+    if access is not None:   # which tokens / pages the attention loads (require_cache_statistics)
+        L.check(lib.hipattn_mark_attention_access(C.byref(bp), access.data_ptr(), access.stride(0), access.stride(1),
+                                                  access.shape[-1], 1 if decode else bsa_block_q, st), "mark_attention_access")
     n_splits = _decode_splits(B, HKV, K * block_size_k + sink + window) if decode else 1
     bp.n_splits = n_splits
     if n_splits > 1:
@@ -563,6 +569,14 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
                 stage_caches = cached_metadata.stage_caches  # extended in place, like the reference
 
         fresh_mask = cached_metadata is None or cached_metadata.indices is None
+        # access statistics (attention_extend.py:1988-2010): one int32 per key position (dense) or page; no offload
+        # cache exists here, so the miss counters stay zero
+        mask_stats = sa_stats = None
+        if args.require_cache_statistics:
+            n_slots = args.k_cache.shape[0] if args.k_cache is not None else T
+            sa_stats = torch.zeros((2, B, HKV, n_slots), dtype=torch.int32, device=dev)
+            if fresh_mask:
+                mask_stats = torch.zeros((2, B, HKV, n_slots), dtype=torch.int32, device=dev)
         if fresh_mask:
             restart = None
             if cached_metadata is not None and cached_metadata.stage_caches is not None and stage_caches is not None \
@@ -573,7 +587,7 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
                 l32, r32 = _restart_inputs(stage_caches[i0], B * BDST)
                 restart = (i0, l32, r32)
             m = _estimate_mask(q, ktok_scan, T, HKV, pos, args, restart, stage_caches is not None, debug,
-                               score_reduce, timer, rope)
+                               score_reduce, timer, rope, None if mask_stats is None else mask_stats[0])
             if stage_caches is not None:
                 for i in range(len(stage_caches), len(stages)):
                     si = m.stage_inputs[i] if i < len(m.stage_inputs) else None
@@ -620,7 +634,7 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
         context, lse = _attention(q_bsa, ktok, vtok, T, HKV, pos, indices, ks, sink=args.sink_token_size, window=sw_attn,
                                   block_size_k=c_last, bsa_block_q=bsa_bq, index_block_q=index_block_q,
                                   heads_share=heads_share, decode=decode, softcap=args.logit_softcap,
-                                  want_lse=return_lse, rope=rope)
+                                  want_lse=return_lse, rope=rope, access=None if sa_stats is None else sa_stats[0])
         if timer: timer.mark("attention")
 
         if fresh_mask and _cdiv(TQ, bsa_bq) != BDST:
@@ -631,11 +645,12 @@ def hip_attention_impl(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], args
             ks_count = ks_count.repeat_interleave(rep, 1)
             ks_start_end = ks_start_end.repeat_interleave(rep, 1)
 
-        stats_none = HiPAttentionCacheAccessStatistics(access_counter=None, cache_miss_counter=None)
+        def stats(t):
+            return HiPAttentionCacheAccessStatistics(None, None) if t is None else HiPAttentionCacheAccessStatistics(t[0], t[1])
         md = HiPAttentionOutputMetadata(
             indices=indices, ks=ks, ks_count=ks_count, ks_start_end=ks_start_end,
-            mask_cache_statistics=HiPAttentionCacheAccessStatistics(None, None) if fresh_mask else None,
-            sa_cache_statistics=stats_none, stage_caches=stage_caches)
+            mask_cache_statistics=stats(mask_stats) if fresh_mask else None,
+            sa_cache_statistics=stats(sa_stats), stage_caches=stage_caches)
         md._heads_share = heads_share
     if return_lse:
         return context, md, lse

@@ -123,6 +123,13 @@ typedef struct hipattn_scan_params {
   int64_t rope_stride;       /* elements between table rows */
   int32_t rope_rows;
   int32_t rope_mode;         /* HIPATTN_ROPE_NONE / _RELATIVE / _STREAMING */
+  /* Access statistics (require_cache_statistics, uvm_gpu_cache.py:846-909): optional int32 [B, HKV, access_n] that
+   * receives 1 at every key position (dense K) or page (paged K: the block-table entry, page 0 beyond the sequence)
+   * whose row a round of the scan asked for.  The caller zeroes it. */
+  int32_t* access_counter;
+  int64_t access_stride_b, access_stride_h;
+  int32_t access_n;
+  int32_t reserved_;
 } hipattn_scan_params_t;
 
 int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);
@@ -226,6 +233,18 @@ typedef struct hipattn_bsa_params {
 } hipattn_bsa_params_t;
 
 int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream);
+
+/*
+ * Access statistics of the attention (the `sa` counter of require_cache_statistics): writes 1 into counter
+ * [B, HKV, n] (int32, zeroed by the caller, strides in elements) at every key position / page the reference's
+ * attention kernels load for the given mask: the sink tokens below the block's last position, the tokens of the
+ * selected blocks inside [sink, last position], and the window from last position + 1 - window - block rows up to
+ * the last position (attention_extend_bsa.py:858-891, 1133-1137, 1370-1383; `block rows` = p->block_size_q for the
+ * prefill kernel, 1 for the decode kernel: pass it as window_block_rows).  Reads p->pos, indices, ks, k (for the page
+ * table) and the mask geometry; no counterpart kernel in the reference, which marks inside load_tokens.
+ */
+int hipattn_mark_attention_access(const hipattn_bsa_params_t* p, int32_t* counter, int64_t stride_b, int64_t stride_h,
+                                  int32_t n, int32_t window_block_rows, void* stream);
 
 /*
  * Log-sum-exp merge of partial outputs (attention_decode_bsa.py:1149-1225).

@@ -200,7 +200,8 @@ def pooled_queries(q: torch.Tensor, pos: torch.Tensor, b: int, d: int, bq: int, 
     return qbar, valid, pmin
 
 
-def scan_block(qbar, valid, pmin, ksrc, b, left, right, *, bq, sw_r, G, block_chunk, dtype, rope=None, backend=None):
+def scan_block(qbar, valid, pmin, ksrc, b, left, right, *, bq, sw_r, G, block_chunk, dtype, rope=None, backend=None,
+               touched=None):
     """Scan one (batch, query block) for all heads.
 
     left/right: int64 [H, n].  Returns narrowed (left, right) [H, n] and scores [H, n] fp32
@@ -258,6 +259,11 @@ def scan_block(qbar, valid, pmin, ksrc, b, left, right, *, bq, sw_r, G, block_ch
                 out[hs] = s.max(1).values
             return torch.where(act, out, neg_inf)
 
+        if touched is not None:   # access statistics: the candidate rows of the active chunks, per KV head
+            for t_ in (tl_, tr_):
+                for hk in range(H // G):
+                    hs = slice(hk * G, (hk + 1) * G)
+                    touched[hk].append(t_[hs][act[hs]])
         sl = side(tl_)
         sr = side(tr_, True)
         win = sl > sr
@@ -281,6 +287,7 @@ class OracleMask:
     stage_outputs: List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]] = field(default_factory=list)
     block_size_k: int = 0          # last stage chunk size
     block_size_q: int = 0
+    mask_access: Optional[torch.Tensor] = None   # access statistics of the estimator (``statistics=True``)
 
 
 def initial_chunks(T: int, cfg: OracleConfig, B: int, BDST: int, H: int):
@@ -312,9 +319,53 @@ def next_stage_inputs(left: torch.Tensor, cfg: OracleConfig, i: int):
     return nl, nr
 
 
+def access_counter(ksrc, B: int, touched) -> torch.Tensor:
+    """The reference's access statistics (``uvm_gpu_cache.py:846-909``): int32 [B, HKV, positions] (dense K) or
+    [B, HKV, pages] (paged: the page the block table gives, page 0 for positions beyond the sequence), 1 where a
+    token was loaded.  ``touched[b][hkv]`` = list of int64 token tensors."""
+    paged = isinstance(ksrc, PagedKV)
+    n = ksrc.cache.shape[0] if paged else ksrc.T
+    out = torch.zeros((B, ksrc.HKV, n), dtype=torch.int32)
+    for b in range(B):
+        for hk in range(ksrc.HKV):
+            if not touched[b][hk]:
+                continue
+            t = torch.cat([x.flatten() for x in touched[b][hk]])
+            if paged:
+                ok = (t >= 0) & (t < ksrc.seq[b])
+                pidx = (t // ksrc.P).clamp(0, ksrc.table.shape[1] - 1)
+                t = torch.where(ok, ksrc.table[b][pidx].long(), torch.zeros_like(t))
+            out[b, hk, t.clamp(0, n - 1)] = 1
+    return out
+
+
+def attention_access(mask: "OracleMask", pos: torch.Tensor, ksrc, H: int, *, sink: int, sw: int, decode: bool) -> torch.Tensor:
+    """Tokens the reference's attention kernels load for every (batch, KV head): sink tokens below the block's last
+    position, the tokens of the selected blocks inside [sink, last position], and the window from
+    last position + 1 - window - block rows up to the last position (``attention_extend_bsa.py:858-891, 1133-1137,
+    1370-1383``; the decode kernel's block is one row)."""
+    B, TQ = pos.shape
+    G = H // ksrc.HKV
+    bq = 1 if decode else mask.block_size_q
+    touched = [[[] for _ in range(ksrc.HKV)] for _ in range(B)]
+    for b in range(B):
+        for d in range(cdiv(TQ, mask.block_size_q)):
+            r0, r1 = d * mask.block_size_q, min((d + 1) * mask.block_size_q, TQ)
+            cur = int(pos[b, r0:r1].max()) + 1
+            for hk in range(ksrc.HKV):
+                n = b * H + hk * G
+                ks = int(mask.ks[n, d])
+                sel = (mask.indices[n, d, :ks, None] + torch.arange(mask.block_size_k)[None, :]).flatten()
+                sel = sel[(sel >= sink) & (sel < cur) & (sel < ksrc.T)]
+                touched[b][hk] += [torch.arange(0, min(sink, cur)), sel]
+                if sw > 0:
+                    touched[b][hk].append(torch.arange(max(0, cur - sw - bq), cur))
+    return access_counter(ksrc, B, touched)
+
+
 def estimate_mask(q: torch.Tensor, ksrc, pos: torch.Tensor, cfg: OracleConfig,
                   restart: Optional[Tuple[int, torch.Tensor, torch.Tensor]] = None,
-                  keep_stage_outputs: bool = False, score_reduce=None) -> OracleMask:
+                  keep_stage_outputs: bool = False, score_reduce=None, statistics: bool = False) -> OracleMask:
     """Run the hierarchical mask estimator.
 
     q [B, TQ, H, D] (pre-scaled by the caller), ksrc a DenseKV/PagedKV over K, pos [B, TQ] int64.
@@ -330,6 +381,7 @@ def estimate_mask(q: torch.Tensor, ksrc, pos: torch.Tensor, cfg: OracleConfig,
     sw_r = max(0, cfg.sw - cfg.stages[0].chunk_size)
     block_chunk = cfg.block_size_k
     out = OracleMask(None, None, None, None)
+    touched = [[[] for _ in range(ksrc.HKV)] for _ in range(B)] if statistics else None
 
     left, right = initial_chunks(T, cfg, B, BDST, H)
     first = 0
@@ -365,7 +417,8 @@ def estimate_mask(q: torch.Tensor, ksrc, pos: torch.Tensor, cfg: OracleConfig,
                         new_tdst = lambda p, n=n: torch.minimum(p, torch.full_like(p, n + sw_r))
                 qbar, valid, pmin = pooled_queries(q, pos, b, d, bq, st.stride_q, cfg.rope, new_tdst)
                 l2, r2, s2 = scan_block(qbar, valid, pmin, ksrc, b, left[b, d], right[b, d], bq=bq, sw_r=sw_r,
-                                        G=G, block_chunk=block_chunk, dtype=q.dtype, rope=cfg.rope, backend=backend)
+                                        G=G, block_chunk=block_chunk, dtype=q.dtype, rope=cfg.rope, backend=backend,
+                                        touched=None if touched is None else touched[b])
                 nl[b, d], nr[b, d], scores[b, d] = l2, r2, s2
         red = scores.max(dim=2, keepdim=True).values  # head reduce, ``attention_extend.py:2566-2570``
         if score_reduce is not None:  # heads split over processes: finish the max across them
@@ -384,6 +437,8 @@ def estimate_mask(q: torch.Tensor, ksrc, pos: torch.Tensor, cfg: OracleConfig,
     c_last = cfg.stages[-1].chunk_size
     assert cfg.second_stage_k % c_last == 0
     idx = left[..., : cfg.second_stage_k // c_last] // c_last * c_last
+    if statistics:
+        out.mask_access = access_counter(ksrc, B, touched)
     return finalize_indices(idx, pos, H, bq, c_last, out)
 
 

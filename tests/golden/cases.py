@@ -88,6 +88,15 @@ CASES = {
                              stages=[(64, 2, 32, None), (64, 1, 8, 256)], seed=32, kv_fp8=True),
     "fp8_decode_fp16": dict(B=2, TQ=1, T=2048, H=8, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
                             stages=[(64, 4, 64, None), (64, 4, 16, 512), (64, 1, 4, 256)], seed=33, kv_fp8=True),
+    # access statistics (require_cache_statistics): which tokens / pages the estimator and the attention kernels loaded
+    "stats_prefill_fp16": dict(B=2, TQ=100, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                               stages=[(64, 2, 32, None), (64, 1, 8, 256)], seed=34, stats=True),
+    "stats_decode_fp16": dict(B=2, TQ=1, T=2048, H=8, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                              stages=[(64, 4, 64, None), (64, 4, 16, 512), (64, 1, 4, 256)], seed=35, stats=True),
+    "stats_paged_fp16": dict(B=2, TQ=70, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                             stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=36, page=16, ext=1536, stats=True),
+    "stats_paged_decode_fp16": dict(B=2, TQ=1, T=1024, H=4, HKV=2, D=64, dtype="fp16", sink=32, sw=128, second_k=128,
+                                    stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=37, page=16, ext=1536, stats=True),
     # benchmark configuration 1 shape (fp32, 4096 x 4096, 8/2 heads, D 64)
     "config1_fp32": dict(B=1, TQ=4096, T=4096, H=8, HKV=2, D=64, dtype="fp32", sink=64, sw=256,
                          second_k=512, stages=[(64, 4, 32, None), (64, 1, 8, 1024)], seed=101,

@@ -132,6 +132,10 @@ def main():
             ks_start_end=md.ks_start_end.numpy(), out=out.float().numpy()[:, ::rs],
             n_stage_caches=np.int64(len(md.stage_caches)),
         )
+        for nm, st in (("mask", md.mask_cache_statistics), ("sa", md.sa_cache_statistics)):
+            if c.get("stats") and st is not None and st.access_counter is not None:
+                save[f"{nm}_access"] = st.access_counter.numpy()
+                save[f"{nm}_miss"] = st.cache_miss_counter.numpy()
         for i, sc in enumerate(md.stage_caches):
             if sc.indices_left is not None:
                 save[f"stage{i}_left"] = sc.indices_left.numpy()

@@ -307,6 +307,63 @@ def test_fp8_cache_on_the_benchmark_shape():
     assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3
 
 
+STATS = ["stats_prefill_fp16", "stats_decode_fp16", "stats_paged_fp16", "stats_paged_decode_fp16"]
+
+
+@pytest.mark.parametrize("name", STATS)
+def test_access_statistics_match_the_reference(name):
+    """require_cache_statistics: the positions (dense K) or pages (paged K) the estimator and the attention loaded,
+    as recorded from the reference; no offload cache exists, so nothing is ever a miss.  A call on the cached mask
+    reports the attention's accesses only."""
+    from hip_attention_b200 import hip_attention_12
+    g = np.load(os.path.join(GOLD, f"{name}.npz"))
+    q, k, v, pos, c, cfg, paged = case_inputs(name)
+    out, md = run_gpu(q, k, v, pos, c, paged)
+    for nm, st in (("mask", md.mask_cache_statistics), ("sa", md.sa_cache_statistics)):
+        assert st.access_counter.dtype == torch.int32 and st.cache_miss_counter.dtype == torch.int32
+        assert np.array_equal(st.access_counter.cpu().numpy(), g[f"{nm}_access"]), f"{nm} access counter"
+        assert int(st.cache_miss_counter.sum()) == 0 and st.cache_miss_counter.shape == st.access_counter.shape
+    import os as _os
+    _os.environ["HIP_DISABLE_COMPUTE_STATISTICS"] = "0"
+    try:
+        got = md.sa_cache_statistics.compute_statistics()
+        assert int(got["access_count"]) == int(g["sa_access"].sum()) and int(got["cache_miss_count"]) == 0
+    finally:
+        del _os.environ["HIP_DISABLE_COMPUTE_STATISTICS"]
+    if paged is None:
+        _, md2 = hip_attention_12(q.cuda(), k.cuda(), v.cuda(), make_args(c, pos.cuda()), cached_metadata=md)
+        assert md2.mask_cache_statistics is None
+        assert torch.equal(md2.sa_cache_statistics.access_counter, md.sa_cache_statistics.access_counter)
+        a2 = make_args(c, pos.cuda())
+        a2.require_cache_statistics = False
+        _, md3 = hip_attention_12(q.cuda(), k.cuda(), v.cuda(), a2)
+        assert md3.mask_cache_statistics.access_counter is None and md3.sa_cache_statistics.access_counter is None
+
+
+@pytest.mark.parametrize("name", ["stats_prefill_fp16", "stats_decode_fp16", "stats_paged_fp16"])
+def test_access_statistics_match_the_oracle_in_bf16(name):
+    """The same sets from every scan kernel that can run the case (tensor-core rounds with row skipping, strict rounds,
+    whole chunks in decode): a skipped row was marked when it was first fetched, a whole-chunk pass marks the rows the
+    rounds would have asked for."""
+    q, k, v, pos, c, cfg, paged = case_inputs(name, torch.bfloat16)
+    if paged is not None:
+        kc, vc, table, seq, ext = paged
+        ksrc = O.PagedKV(kc, table, seq, ext)
+    else:
+        ksrc = O.DenseKV(k)
+    m = O.estimate_mask(q, ksrc, pos, cfg, statistics=True)
+    sw_attn = max(0, cfg.sw - cfg.stages[0].chunk_size) + cfg.stages[0].chunk_size
+    sa = O.attention_access(m, pos, ksrc, c["H"], sink=cfg.sink, sw=sw_attn, decode=c["TQ"] == 1)
+    for mode in ("auto", "strict"):
+        os.environ["HIPATTN_SCAN_MODE"] = mode
+        try:
+            out, md = run_gpu(q, k, v, pos, c, paged)
+        finally:
+            del os.environ["HIPATTN_SCAN_MODE"]
+        assert torch.equal(md.mask_cache_statistics.access_counter.cpu(), m.mask_access), mode
+        assert torch.equal(md.sa_cache_statistics.access_counter.cpu(), sa), mode
+
+
 def test_unbuilt_stage_flags_are_refused():
     """A stage that switches off realignment, score reset or the position sort selects a branch the kernels do not
     have: the call must say so instead of returning a different mask."""
