@@ -168,16 +168,17 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     }
     s_rowpos[tid] = pv;
   }
+  // the query tile: one batch of asynchronous 16-byte copies per thread (rows beyond the block are zero-filled), so that
+  // the tile costs one trip to memory instead of one per loop iteration
   for (int i = tid; i < 128 * 16; i += NT) {
     const int r = i >> 4, pc = i & 15;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if ((r % BQ) < rows_here) {
-      const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(row_t0 + r % BQ) * p.q_stride_t +
-                    (int64_t)(h0 + r / BQ) * p.q_stride_h + pc * 8;
-      v = *reinterpret_cast<const uint4*>(qp);
-    }
-    *reinterpret_cast<uint4*>(sQ + (pc >> 3) * (128 * 128) + sw128(r, pc & 7)) = v;
+    const bool live = (r % BQ) < rows_here;
+    const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(row_t0 + (live ? r % BQ : 0)) * p.q_stride_t +
+                  (int64_t)(h0 + r / BQ) * p.q_stride_h + pc * 8;
+    cp_async16_zfill(smem_u32(sQ) + (pc >> 3) * (128 * 128) + sw128(r, pc & 7), qp, live);
   }
+  cp_async_commit();
+  cp_async_wait<0>();
   fence_async_smem();
   __syncthreads();
   const int pmin = s_mm[0], pmax = s_mm[1];

@@ -52,6 +52,34 @@ __device__ __forceinline__ void pooled_query_piece(const hipattn_scan_params_t& 
   }
 }
 
+// The same piece from a copy of the query block's rows in shared memory (row i of the block at staged + i * row_bytes):
+// identical arithmetic, but the rows were fetched with one batch of asynchronous copies instead of one dependent
+// global load per row.  `r0` = first row of the group inside the block, `rows` = rows the block holds.
+template <int DT>
+__device__ __forceinline__ void pooled_query_piece_staged(const hipattn_scan_params_t& p, const unsigned char* staged, int row_bytes,
+                                                          int r0, int rows, int piece, float* out) {
+  constexpr int VEC = 16 / Elem<DT>::bytes;
+  float sum[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) sum[e] = 0.f;
+  float cnt = 0.f;
+  for (int o = 0; o < p.stride_q; ++o) {
+    if (r0 + o < rows) {
+      float v[VEC];
+      widen_piece<DT>(*reinterpret_cast<const uint4*>(staged + (size_t)(r0 + o) * row_bytes + piece * 16), v);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) sum[e] = __fadd_rn(sum[e], v[e]);
+      cnt += 1.f;
+    }
+  }
+  const float den = __fadd_rn(cnt, 1e-12f);
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    const float m = Elem<DT>::round(__fdiv_rn(sum[e], den));
+    out[e] = Elem<DT>::round(__fmul_rn(m, p.q_scale));
+  }
+}
+
 // Smallest position among the strided rows of a query block (computed by one warp).
 __device__ __forceinline__ int block_min_position(const hipattn_scan_params_t& p, int b, int t0, int Rv, int lane) {
   long long m = 0x7fffffffffffffffLL;

@@ -93,10 +93,27 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
     sh.g[1][3] = 0;
     sh.fetched[0] = sh.fetched[1] = sh.fetched[2] = 0;
   }
+  // The block's query rows go to shared memory (the key tile is free until the first round) with one batch of
+  // asynchronous copies, issued before the TMEM allocation so that the trip to DRAM overlaps it: the pooled queries are
+  // then computed from shared memory instead of through one dependent global load per row.
+  const int rows_here = max(0, min(p.block_size_q, p.TQ - t0));
+  const bool staged = (size_t)p.block_size_q * ROWB <= (size_t)KB * K_BLOCK_BYTES;
+  if (staged) {
+    using T = typename Elem<DT>::type;
+    const T* qb = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)h * p.q_stride_h;
+    for (int i = tid; i < rows_here * PIECES; i += 128) {
+      const int r = i / PIECES, pc = i % PIECES;
+      cp_async16(sK + (size_t)r * ROWB + pc * 16, qb + (int64_t)(t0 + r) * p.q_stride_t + pc * 8);
+    }
+    cp_async_commit();
+  }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    const int m = block_min_position(p, b, t0, Rv, lane);
+    if (lane == 0) sh.g[1][2] = m;
   }
+  cp_async_wait<0>();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -108,7 +125,10 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = 0.f;
-    if (r < Rv) pooled_query_piece<DT>(p, b, h, t0 + r * p.stride_q, pc, v);
+    if (r < Rv) {
+      if (staged) pooled_query_piece_staged<DT>(p, sK, ROWB, r * p.stride_q, rows_here, pc, v);
+      else pooled_query_piece<DT>(p, b, h, t0 + r * p.stride_q, pc, v);
+    }
     uint4 w;
     w.x = pack2<DT>(v[0], v[1]); w.y = pack2<DT>(v[2], v[3]); w.z = pack2<DT>(v[4], v[5]); w.w = pack2<DT>(v[6], v[7]);
     *reinterpret_cast<uint4*>(sQ + (pc >> 3) * Q_BLOCK_BYTES + sw128(r, pc & 7)) = w;
@@ -118,10 +138,6 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) qmax_local = fmaxf(qmax_local, __shfl_xor_sync(0xffffffffu, qmax_local, o));
   if (lane == 0) atomicMax(&sh.g[1][3], __float_as_int(qmax_local));  // non-negative floats order as ints
-  if (warp == 0) {
-    const int m = block_min_position(p, b, t0, Rv, lane);
-    if (lane == 0) sh.g[1][2] = m;
-  }
   fence_async_smem();
   __syncthreads();
 
