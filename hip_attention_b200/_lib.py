@@ -12,7 +12,7 @@ F32, F16, BF16 = 0, 1, 2
 STATUS_PAGE_RANGE, STATUS_TOKEN_RANGE, STATUS_TIMEOUT, STATUS_CHUNK_SIZE = 1, 2, 4, 8
 MAX_CHUNKS = 16384
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
-ABI_VERSION = 8
+ABI_VERSION = 9
 SCAN_AUTO, SCAN_STRICT, SCAN_CHECK = 0, 1, 2
 ROPE_NONE, ROPE_RELATIVE, ROPE_STREAMING = 0, 1, 2
 
@@ -37,7 +37,7 @@ class ScanParams(C.Structure):
                 ("block_size_q", i32), ("stride_q", i32), ("n_chunks", i32), ("block_chunk", i32),
                 ("scan_window", i32), ("q_scale", f32), ("k_scale", f32), ("mode", i32), ("chunk_size", i32),
                 ("rope_cos", vp), ("rope_sin", vp), ("rope_stride", i64), ("rope_rows", i32), ("rope_mode", i32),
-                ("access_counter", vp), ("access_stride_b", i64), ("access_stride_h", i64), ("access_n", i32), ("reserved_", i32)]
+                ("access_counter", vp), ("access_stride_b", i64), ("access_stride_h", i64), ("access_n", i32), ("k_scaled_sides", i32)]
 
 
 class BsaParams(C.Structure):
@@ -59,6 +59,7 @@ SYMBOLS = {
     "hipattn_scan_stage": (i32, [C.POINTER(ScanParams), vp]),
     "hipattn_key_abs_sum": (i32, [C.POINTER(Tokens), i32, i32, i32, i32, i32, f32, vp, vp, vp]),
     "hipattn_scan_prepare_keys": (i32, [C.POINTER(Tokens), i32, i32, i32, i32, i32, f32, vp, vp, vp, vp]),
+    "hipattn_scan_prepare_keys_rope": (i32, [C.POINTER(Tokens), i32, i32, i32, i32, i32, f32, vp, vp, i64, i32, i32, vp, vp, vp, vp]),
     "hipattn_init_chunks": (i32, [vp, vp, vp, i64, i32, i32, i32, i32, i32, vp]),
     "hipattn_select_stage": (i32, [vp, vp, i64, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     "hipattn_finalize_indices": (i32, [vp, vp, i64, i64, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]),

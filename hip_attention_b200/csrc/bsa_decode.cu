@@ -263,6 +263,7 @@ constexpr int kStages = 3;
 struct DecodeMeta {
   long long koff[TKD];  // byte offsets from the base pointers, -1 = key not admitted
   long long voff[TKD];
+  int rpos[TKD];        // in-kernel RoPE: table position the key is rotated to (-1: no key)
 };
 
 template <int DT, int D>
@@ -312,16 +313,19 @@ __global__ void __launch_bounds__(128) bsa_decode_mma_kernel(const hipattn_bsa_p
       DecodeMeta& m = meta[tile % (kStages + 1)];
       const int j = j_begin + tile * TKD + tid;
       long long ko = -1, vo = -1;
+      int rp = -1;
       if (j < j_end) {
         bool w = false;
         const int t = key_position(kl, j, &w);
         if (admits(pq, t, w, p.window)) {
           ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
           vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
+          if (p.rope_cos) rp = rope_key_position(kl, j, t, p.window);
         }
       }
       m.koff[tid] = ko;
       m.voff[tid] = vo;
+      m.rpos[tid] = rp;
     }
   };
   auto gather = [&](int tile) {
@@ -352,6 +356,10 @@ __global__ void __launch_bounds__(128) bsa_decode_mma_kernel(const hipattn_bsa_p
   if (n_tiles > 0) make_meta(0);
   if (n_tiles > 1) make_meta(1);
   __syncthreads();  // Q tile and the first addresses are visible
+  if (p.rope_cos) {   // in-kernel RoPE: the query rows at the query's position (attention_decode_bsa.py:174-215)
+    rope_rotate_tile<DT, D>(sQ, 0, 16, p, tid, 128, [&](int r) { return r < G ? pq : -1; });
+    __syncthreads();
+  }
   uint32_t qf[KSTEPS][4];
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks)
@@ -376,6 +384,10 @@ __global__ void __launch_bounds__(128) bsa_decode_mma_kernel(const hipattn_bsa_p
     if (it + 3 < n_tiles) make_meta(it + 3);
 
     const DecodeMeta& mt = meta[it % (kStages + 1)];
+    if (p.rope_cos) {   // in-kernel RoPE: this warp rotates the 16 key rows it is about to multiply
+      rope_rotate_tile<DT, D>(sK + (it % kStages) * TILE_BYTES, warp * 16, 16, p, lane, 32, [&](int r) { return mt.rpos[r]; });
+      __syncwarp();
+    }
     const unsigned char* kb = sK + (it % kStages) * TILE_BYTES;
     const unsigned char* vb = sV + (it % kStages) * TILE_BYTES;
     // ---- S = Q K^T for this warp's 16 keys ----
@@ -548,6 +560,7 @@ int bsa_decode(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handled
     if (p.dtype == HIPATTN_BF16) return p.D == 128 ? launch_mma<HIPATTN_BF16, 128>(p, stream) : launch_mma<HIPATTN_BF16, 64>(p, stream);
     return p.D == 128 ? launch_mma<HIPATTN_F16, 128>(p, stream) : launch_mma<HIPATTN_F16, 64>(p, stream);
   }
+  if (p.rope_cos) return HIPATTN_OK;   // in-kernel RoPE: only the tensor-core variant above rotates; the rest is the general kernel's
   switch (p.dtype) {
     case HIPATTN_F32: return dispatch_row<HIPATTN_F32>(p, stream, handled);
     case HIPATTN_F16: return dispatch_row<HIPATTN_F16>(p, stream, handled);

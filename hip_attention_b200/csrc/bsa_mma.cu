@@ -10,6 +10,7 @@
 // admitted for every row skip the per-element admission test.
 #include "bsa_common.cuh"
 #include "mma_common.cuh"
+#include "rope.cuh"
 
 namespace hipattn {
 namespace {
@@ -24,6 +25,7 @@ struct TileMeta {
   long long voff[TKM];
   int far_ok[2];       // per half tile: every key valid, far rule, admitted by every row
   int win_ok[2];       // per half tile: every key valid, window rule, admitted by every row
+  int rpos[TKM];       // in-kernel RoPE: table position the key is rotated to (-1: no key)
 };
 
 template <int DT, int D, int M>
@@ -94,6 +96,10 @@ __global__ void __launch_bounds__(M * 2) bsa_mma_kernel(const hipattn_bsa_params
     *reinterpret_cast<uint4*>(sQ + swz<D>(r, pc)) = v;
   }
   __syncthreads();
+  if (p.rope_cos) {   // in-kernel RoPE: every query row at its own position (attention_extend_bsa.py:797-856)
+    rope_rotate_tile<DT, D>(sQ, 0, M, p, tid, NT, [&](int r) { return s_rowpos[r]; });
+    __syncthreads();
+  }
   const int pmin = s_mm[0], pmax = s_mm[1];
   const int rmin = s_mm[2], rmax = s_mm[3];
   const KeyList kl = make_key_list(p, b, h0, d, pmin, pmax);
@@ -122,6 +128,7 @@ __global__ void __launch_bounds__(M * 2) bsa_mma_kernel(const hipattn_bsa_params
       }
       m.koff[tid] = ko;
       m.voff[tid] = vo;
+      m.rpos[tid] = (t >= 0 && p.rope_cos) ? rope_key_position(kl, j, t, p.window) : -1;
       const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
       const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
       const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
@@ -173,6 +180,10 @@ __global__ void __launch_bounds__(M * 2) bsa_mma_kernel(const hipattn_bsa_params
     __syncthreads();
 
     const TileMeta& mt = meta[it % 3];
+    if (p.rope_cos) {   // in-kernel RoPE: the tile's keys at the positions their places in the list map to
+      rope_rotate_tile<DT, D>(sK + (it & 1) * TILE_BYTES, 0, TKM, p, tid, NT, [&](int r) { return mt.rpos[r]; });
+      __syncthreads();
+    }
     const unsigned char* kb = sK + (it & 1) * TILE_BYTES;
     const unsigned char* vb = sV + (it & 1) * TILE_BYTES;
     // ---- S = Q K^T (16 rows x 64 keys per warp) ----

@@ -167,11 +167,17 @@ extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream
     return bsa_generic(*p, (cudaStream_t)stream);
   }
   if (p->rope_cos || p->rope_sin) {
-    // in-kernel RoPE is built into the general kernel only (prefill and decode, key splits included)
+    // in-kernel RoPE is built into the mma.sync decode and prefill kernels (16-bit, head dim 64 / 128) and the general
+    // kernel (everything else)
     HIPATTN_REQUIRE(p->rope_cos && p->rope_sin && p->rope_rows > 0, HIPATTN_ERR_INVALID, "attention: cos and sin tables go together");
     HIPATTN_REQUIRE(((uintptr_t)p->rope_cos % 16) == 0 && ((uintptr_t)p->rope_sin % 16) == 0 && p->rope_stride % ra == 0 &&
                         p->rope_stride >= p->D / 2,
                     HIPATTN_ERR_INVALID, "attention: cos / sin rows must start on 16-byte boundaries and hold D / 2 columns");
+    bool done = false;
+    rc = bsa_decode(*p, (cudaStream_t)stream, &done);
+    if (done) return rc;
+    rc = bsa_mma(*p, (cudaStream_t)stream, &done);
+    if (done) return rc;
     return bsa_generic(*p, (cudaStream_t)stream);
   }
   bool handled = false;
@@ -228,4 +234,4 @@ extern "C" int hipattn_debug_bounded_wait(uint32_t* status, void* stream) {
 
 extern "C" uint64_t hipattn_launch_count(void) { return hipattn::g_launches.load(std::memory_order_relaxed); }
 extern "C" const char* hipattn_error_string(void) { return g_error; }
-extern "C" int hipattn_abi_version(void) { return 8; }
+extern "C" int hipattn_abi_version(void) { return 9; }

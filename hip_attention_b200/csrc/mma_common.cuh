@@ -1,6 +1,7 @@
 // Warp-level tensor-core helpers (mma.sync m16n8k16, ldmatrix) shared by the attention and scan kernels.
 #pragma once
 #include "common.cuh"
+#include "rope.cuh"
 
 namespace hipattn {
 
@@ -29,6 +30,34 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& 
 template <int D>
 __device__ __forceinline__ int swz(int row, int piece) {
   return row * (D * 2) + ((piece ^ (row & 7)) << 4);
+}
+
+
+// In-kernel RoPE on a swizzled [rows][D] tile of 16-bit elements in shared memory: rows row0 .. row0 + rows - 1 are
+// rotated to table position pos(r) (rows with a negative position are left alone).  The work is dealt to `nthreads`
+// threads numbered `tid`; the caller synchronises them around the call.
+template <int DT, int D, typename PosFn>
+__device__ __forceinline__ void rope_rotate_tile(unsigned char* tile, int row0, int rows, const hipattn_bsa_params_t& p, int tid,
+                                                 int nthreads, PosFn pos) {
+  constexpr int HALF = D / 16;   // 16-byte pieces per half row
+  for (int i = tid; i < rows * HALF; i += nthreads) {
+    const int r = row0 + i / HALF, pc = i % HALF;
+    const int t = pos(r);
+    if (t < 0) continue;
+    uint4* plo = reinterpret_cast<uint4*>(tile + swz<D>(r, pc));
+    uint4* phi = reinterpret_cast<uint4*>(tile + swz<D>(r, pc + HALF));
+    float lo[8], hi[8], lo0[8], tc[8], ts[8];
+    widen_piece<DT>(*plo, lo);
+    widen_piece<DT>(*phi, hi);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) lo0[e] = lo[e];
+    rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, t, pc, tc);
+    rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, t, pc, ts);
+    rope_rotate_piece<DT, 8>(lo, hi, tc, ts, true);
+    rope_rotate_piece<DT, 8>(hi, lo0, tc, ts, false);
+    *plo = make_uint4(pack2<DT>(lo[0], lo[1]), pack2<DT>(lo[2], lo[3]), pack2<DT>(lo[4], lo[5]), pack2<DT>(lo[6], lo[7]));
+    *phi = make_uint4(pack2<DT>(hi[0], hi[1]), pack2<DT>(hi[2], hi[3]), pack2<DT>(hi[4], hi[5]), pack2<DT>(hi[6], hi[7]));
+  }
 }
 
 }  // namespace hipattn

@@ -57,16 +57,30 @@ __device__ __forceinline__ void pooled_query_piece(const hipattn_scan_params_t& 
 // global load per row.  `r0` = first row of the group inside the block, `rows` = rows the block holds.
 template <int DT>
 __device__ __forceinline__ void pooled_query_piece_staged(const hipattn_scan_params_t& p, const unsigned char* staged, int row_bytes,
-                                                          int r0, int rows, int piece, float* out) {
+                                                          int r0, int rows, int piece, float* out, int b, int t0) {
   constexpr int VEC = 16 / Elem<DT>::bytes;
   float sum[VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) sum[e] = 0.f;
   float cnt = 0.f;
+  float tc[VEC], ts[VEC];
+  const int pieces = p.D / VEC, half = pieces / 2;
+  if (p.rope_mode != HIPATTN_ROPE_NONE) {   // as in pooled_query_piece: the position comes from the group's first row
+    long long pv = p.pos[(int64_t)b * p.pos_stride_b + (int64_t)(t0 + r0) * p.pos_stride_t];
+    const long long cap = (long long)p.n_chunks + p.scan_window;
+    const int new_t = p.rope_mode == HIPATTN_ROPE_RELATIVE ? 1 + p.scan_window : (int)(pv < cap ? (pv < 0 ? 0 : pv) : cap);
+    rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, new_t, piece % half, tc);
+    rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, new_t, piece % half, ts);
+  }
   for (int o = 0; o < p.stride_q; ++o) {
     if (r0 + o < rows) {
       float v[VEC];
       widen_piece<DT>(*reinterpret_cast<const uint4*>(staged + (size_t)(r0 + o) * row_bytes + piece * 16), v);
+      if (p.rope_mode != HIPATTN_ROPE_NONE) {
+        float vr[VEC];
+        widen_piece<DT>(*reinterpret_cast<const uint4*>(staged + (size_t)(r0 + o) * row_bytes + (piece < half ? piece + half : piece - half) * 16), vr);
+        rope_rotate_piece<DT, VEC>(v, vr, tc, ts, piece < half);
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) sum[e] = __fadd_rn(sum[e], v[e]);
       cnt += 1.f;

@@ -340,7 +340,8 @@ int scan_stage_mma(const hipattn_scan_params_t& p, cudaStream_t stream, bool* ha
 int scan_stage_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
 int scan_chunks_strict(const hipattn_scan_params_t& p, cudaStream_t stream, bool* handled);
 int scan_prepare_keys(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* key_abs,
-                      void* k_scaled, uint32_t* status, cudaStream_t stream);
+                      void* k_scaled, uint32_t* status, cudaStream_t stream, const void* rope_cos = nullptr,
+                      const void* rope_sin = nullptr, int64_t rope_stride = 0, int rope_rows = 0, int rope_position = 0);
 
 }  // namespace hipattn
 
@@ -368,13 +369,18 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
   HIPATTN_REQUIRE(p->mode >= HIPATTN_SCAN_AUTO && p->mode <= HIPATTN_SCAN_CHECK, HIPATTN_ERR_INVALID, "scan stage: unknown mode %d", p->mode);
   bool handled = false;
   if (p->rope_mode != HIPATTN_ROPE_NONE) {
-    // in-kernel RoPE is built into the strict kernel only
+    // in-kernel RoPE is built into the strict kernel and, for backend "relative" with two prepared key copies, into the
+    // tcgen05 kernel
     HIPATTN_REQUIRE(p->rope_mode == HIPATTN_ROPE_RELATIVE || p->rope_mode == HIPATTN_ROPE_STREAMING, HIPATTN_ERR_INVALID,
                     "scan stage: unknown rope_mode %d", p->rope_mode);
     HIPATTN_REQUIRE(p->rope_cos && p->rope_sin && p->rope_rows > 0, HIPATTN_ERR_INVALID, "scan stage: rope_mode without cos / sin tables");
     HIPATTN_REQUIRE(((uintptr_t)p->rope_cos % 16) == 0 && ((uintptr_t)p->rope_sin % 16) == 0 && p->rope_stride % ra == 0 &&
                         p->rope_stride >= p->D / 2,
                     HIPATTN_ERR_INVALID, "scan stage: cos / sin rows must start on 16-byte boundaries and hold D / 2 columns");
+    if (p->rope_mode == HIPATTN_ROPE_RELATIVE && p->k_scaled_sides == 2) {
+      rc = scan_stage_tcgen05(*p, s, &handled);
+      if (handled) return rc;
+    }
   } else {
   rc = scan_chunks_strict(*p, s, &handled);
   if (handled) return rc;
@@ -399,6 +405,23 @@ extern "C" int hipattn_key_abs_sum(const hipattn_tokens_t* k, int32_t dtype, int
   int rc = validate_tokens(*k, dtype == HIPATTN_F32 ? 4 : 2, D, "k");
   if (rc) return rc;
   return scan_prepare_keys(*k, dtype, D, B, T, HKV, k_scale, out, nullptr, status, (cudaStream_t)stream);
+}
+
+extern "C" int hipattn_scan_prepare_keys_rope(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
+                                              float k_scale, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
+                                              int32_t rope_rows, int32_t position, float* key_abs, void* k_scaled, uint32_t* status,
+                                              void* stream) {
+  using namespace hipattn;
+  HIPATTN_REQUIRE(k && status && key_abs && k_scaled && rope_cos && rope_sin, HIPATTN_ERR_INVALID, "scan_prepare_keys_rope: null pointer");
+  HIPATTN_REQUIRE(B > 0 && T > 0 && HKV > 0 && rope_rows > 0 && position >= 0 && position < rope_rows, HIPATTN_ERR_INVALID,
+                  "scan_prepare_keys_rope: bad shape or position");
+  HIPATTN_REQUIRE(((uintptr_t)k_scaled % 16) == 0 && ((uintptr_t)rope_cos % 16) == 0 && ((uintptr_t)rope_sin % 16) == 0 &&
+                      rope_stride % 8 == 0 && rope_stride >= D / 2,
+                  HIPATTN_ERR_INVALID, "scan_prepare_keys_rope: k_scaled and the cos / sin rows must be 16-byte aligned");
+  int rc = validate_tokens(*k, 2, D, "k");
+  if (rc) return rc;
+  return scan_prepare_keys(*k, dtype, D, B, T, HKV, k_scale, key_abs, k_scaled, status, (cudaStream_t)stream, rope_cos, rope_sin,
+                           rope_stride, rope_rows, position);
 }
 
 extern "C" int hipattn_scan_prepare_keys(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,

@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = 0.f;
     if (r < Rv) {
-      if (staged) pooled_query_piece_staged<DT>(p, sK, ROWB, r * p.stride_q, rows_here, pc, v);
+      if (staged) pooled_query_piece_staged<DT>(p, sK, ROWB, r * p.stride_q, rows_here, pc, v, b, t0);
       else pooled_query_piece<DT>(p, b, h, t0 + r * p.stride_q, pc, v);
     }
     uint4 w;
@@ -150,6 +150,10 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
   const uint32_t idesc = make_idesc(DT == HIPATTN_BF16 ? 1 : 0, 128, NR, 0);
   const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);
   const int side = tid & 1;
+  // in-kernel RoPE, backend "relative": the prepared keys come in two copies (rotated to position 0 / 1 for the left /
+  // right candidate), and a key's score depends on the side it is proposed for, so no score is carried over
+  const bool roped = p.rope_mode != HIPATTN_ROPE_NONE;
+  const int side_rows = roped ? p.B * p.HKV * p.T : 0;
   unsigned long long st_keys = 0, st_fb = 0, st_wrong = 0;
   float st_ratio = 0.f;
   uint32_t phase = 0;
@@ -240,14 +244,14 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
       const int mid = (left + right) >> 1;
       int tk = side ? ((mid + right) >> 1) : ((left + mid) >> 1);
       const int tk_asked = tk;
-      const bool known = act && tk == won_t;
+      const bool known = act && !roped && tk == won_t;
       int idx = -1;
       if (act && !known) {
         if (tk < 0 || tk >= p.T) {
           atomicOr(p.status, HIPATTN_STATUS_TOKEN_RANGE);
           tk = min(max(tk, 0), p.T - 1);
         }
-        idx = (b * p.HKV + hkv) * p.T + tk;
+        idx = (b * p.HKV + hkv) * p.T + tk + side * side_rows;   // (second copy: keys rotated for the right candidate)
         if (p.access_counter) mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, tk);
       }
       // the key's magnitude is needed only after the MMA: requested here, its latency hides behind the row copies
@@ -407,9 +411,16 @@ int dispatch_rows(const hipattn_scan_params_t& p, cudaStream_t stream) {
 }
 
 // Scaled copy of the keys and their absolute sums: 16 / 8 lanes per row of 256 / 128 bytes.
+struct PrepareRope {      // rotate every key to one fixed table position before scaling (scan backend "relative")
+  const void* cos;
+  const void* sin;
+  int64_t stride;
+  int rows, position;
+};
+
 template <int DT>
 __global__ void scan_prepare_keys_kernel(const hipattn_tokens_t k, int D, int B, int T, int HKV, float k_scale, float* key_abs,
-                                         unsigned char* k_scaled, uint32_t* status) {
+                                         unsigned char* k_scaled, uint32_t* status, const PrepareRope rope) {
   const int pieces = D * 2 / 16;
   const int rows_per_block = blockDim.x / pieces;
   const int sub = threadIdx.x / pieces, piece = threadIdx.x % pieces;
@@ -423,6 +434,19 @@ __global__ void scan_prepare_keys_kernel(const hipattn_tokens_t k, int D, int B,
     const uint4 w = k.fp8_e5m2 ? widen_fp8_e5m2<DT>(*reinterpret_cast<const uint2*>(src + piece * 8))
                                : *reinterpret_cast<const uint4*>(src + piece * 16);
     uint32_t v[4] = {w.x, w.y, w.z, w.w};
+    if (rope.cos != nullptr) {
+      const int half = pieces >> 1, pr = piece < half ? piece + half : piece - half;
+      const uint4 wr = k.fp8_e5m2 ? widen_fp8_e5m2<DT>(*reinterpret_cast<const uint2*>(src + pr * 8))
+                                  : *reinterpret_cast<const uint4*>(src + pr * 16);
+      float x[8], xr[8], tc[8], ts[8];
+      widen_piece<DT>(w, x);
+      widen_piece<DT>(wr, xr);
+      rope_table_piece<DT>(rope.cos, rope.stride, rope.rows, rope.position, piece % half, tc);
+      rope_table_piece<DT>(rope.sin, rope.stride, rope.rows, rope.position, piece % half, ts);
+      rope_rotate_piece<DT, 8>(x, xr, tc, ts, piece < half);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = pack2<DT>(x[2 * i], x[2 * i + 1]);
+    }
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -440,7 +464,9 @@ __global__ void scan_prepare_keys_kernel(const hipattn_tokens_t k, int D, int B,
 }  // namespace
 
 int scan_prepare_keys(const hipattn_tokens_t& k, int dtype, int D, int B, int T, int HKV, float k_scale, float* key_abs,
-                      void* k_scaled, uint32_t* status, cudaStream_t stream) {
+                      void* k_scaled, uint32_t* status, cudaStream_t stream, const void* rope_cos, const void* rope_sin,
+                      int64_t rope_stride, int rope_rows, int rope_position) {
+  const PrepareRope rope{rope_cos, rope_sin, rope_stride, rope_rows, rope_position};
   HIPATTN_REQUIRE(dtype == HIPATTN_BF16 || dtype == HIPATTN_F16, HIPATTN_ERR_UNSUPPORTED, "scan_prepare_keys: 16-bit element types only");
   HIPATTN_REQUIRE(D == 64 || D == 128, HIPATTN_ERR_UNSUPPORTED, "scan_prepare_keys: head dimension %d is not built (64, 128)", D);
   const int64_t total = (int64_t)B * T * HKV;
@@ -448,9 +474,9 @@ int scan_prepare_keys(const hipattn_tokens_t& k, int dtype, int D, int B, int T,
   int64_t grid = (total + rows_per_block - 1) / rows_per_block;
   if (grid > 148 * 32) grid = 148 * 32;
   if (dtype == HIPATTN_BF16)
-    scan_prepare_keys_kernel<HIPATTN_BF16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, key_abs, (unsigned char*)k_scaled, status);
+    scan_prepare_keys_kernel<HIPATTN_BF16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, key_abs, (unsigned char*)k_scaled, status, rope);
   else
-    scan_prepare_keys_kernel<HIPATTN_F16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, key_abs, (unsigned char*)k_scaled, status);
+    scan_prepare_keys_kernel<HIPATTN_F16><<<(unsigned)grid, 256, 0, stream>>>(k, D, B, T, HKV, k_scale, key_abs, (unsigned char*)k_scaled, status, rope);
   return check_launch("scan_prepare_keys_kernel");
 }
 
@@ -462,7 +488,8 @@ int scan_stage_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool
   const int rows = min(R, cdiv(p.TQ, p.stride_q));
   if (p.mode == HIPATTN_SCAN_STRICT || p.dtype == HIPATTN_F32 || rows <= 1 || (R % 16) != 0 || R > 128 || (p.D != 64 && p.D != 128)) return HIPATTN_OK;
   if (p.key_abs == nullptr || p.k_scaled == nullptr) return HIPATTN_OK;
-  if ((int64_t)p.B * p.T * p.HKV >= 0x7fffffffLL) return HIPATTN_OK;
+  if ((int64_t)p.B * p.T * p.HKV * (p.rope_mode != HIPATTN_ROPE_NONE ? 2 : 1) >= 0x7fffffffLL) return HIPATTN_OK;
+  if (p.rope_mode != HIPATTN_ROPE_NONE && !(p.rope_mode == HIPATTN_ROPE_RELATIVE && p.k_scaled_sides == 2)) return HIPATTN_OK;
   const char* v = getenv("HIPATTN_SCAN_KERNEL");
   if (v && strcmp(v, "mma") == 0) return HIPATTN_OK;
   *handled = true;

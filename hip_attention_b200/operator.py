@@ -263,17 +263,34 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
     if n > L.MAX_CHUNKS:
         raise NotImplementedError(f"{n} chunks per query block exceed the on-chip selection limit of {L.MAX_CHUNKS}")
 
-    # scaled keys and their magnitudes (error radius) for the tensor-core scan (16-bit prefill only), once per call
+    # scaled keys and their magnitudes (error radius) for the tensor-core scan (16-bit prefill only), once per call.
+    # With in-kernel RoPE the stages whose backend is "relative" get two copies (keys rotated to table position 0 / 1 for
+    # the left / right candidate); "streaming" stages rotate every key to its chunk's index and stay on the strict kernel.
     key_abs = k_scaled = None
+    rope_modes = [None] * len(stages)
+    if rope is not None:
+        rope_modes = [_ROPE_MODES[getattr(s_, "stage_extend_backend", None) or args.scan_extend_backend] for s_ in stages]
     R_min = min(bq // s_.stage_block_stride_q for s_ in stages)
-    if (q.dtype != torch.float32 and D in (64, 128) and min(TQ, bq) > 1 and _scan_mode() != L.SCAN_STRICT and rope is None
-            and all((bq // s_.stage_block_stride_q) % 16 == 0 for s_ in stages) and R_min >= 16 and n > 0):
+    tensor_scan = (q.dtype != torch.float32 and D in (64, 128) and min(TQ, bq) > 1 and _scan_mode() != L.SCAN_STRICT
+                   and all((bq // s_.stage_block_stride_q) % 16 == 0 for s_ in stages) and R_min >= 16 and n > 0)
+    sides = 1
+    if tensor_scan and rope is not None:
+        sides = 2
+        tensor_scan = L.ROPE_RELATIVE in rope_modes[first:] and 2 * B * T * HKV < 2 ** 31 - 1
+    if tensor_scan:
         if timer: timer.mark("start")
-        key_abs = torch.empty((B, HKV, T), dtype=torch.float32, device=dev)
-        if B * T * HKV < 2 ** 31 - 1:
-            k_scaled = torch.empty((B, HKV, T, D), dtype=q.dtype, device=dev)
-        L.check(lib.hipattn_scan_prepare_keys(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, _ptr(key_abs),
-                                              _ptr(k_scaled), status.data_ptr(), st), "scan_prepare_keys")
+        key_abs = torch.empty((sides, B, HKV, T), dtype=torch.float32, device=dev)
+        if sides * B * T * HKV < 2 ** 31 - 1:
+            k_scaled = torch.empty((sides, B, HKV, T, D), dtype=q.dtype, device=dev)
+        if rope is None:
+            L.check(lib.hipattn_scan_prepare_keys(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, _ptr(key_abs),
+                                                  _ptr(k_scaled), status.data_ptr(), st), "scan_prepare_keys")
+        else:
+            for side in range(2):
+                L.check(lib.hipattn_scan_prepare_keys_rope(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, rope[0].data_ptr(),
+                                                           rope[1].data_ptr(), rope[0].stride(0), rope[0].shape[0], side,
+                                                           key_abs[side].data_ptr(), k_scaled[side].data_ptr(), status.data_ptr(), st),
+                        "scan_prepare_keys_rope")
         if timer: timer.mark("prep")
 
     block_chunk = args.block_size_k
@@ -301,8 +318,10 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         sp.left, sp.right, sp.score_max = _ptr(left), _ptr(right), _ptr(score)
         sp.left_out, sp.right_out, sp.score_out = _ptr(left_out), _ptr(right_out), _ptr(score_out)
         sp.status = status.data_ptr()
-        sp.key_abs = _ptr(key_abs)
-        sp.k_scaled = _ptr(k_scaled)
+        if rope is None or rope_modes[i] == L.ROPE_RELATIVE:
+            sp.key_abs = _ptr(key_abs)
+            sp.k_scaled = _ptr(k_scaled)
+            sp.k_scaled_sides = sides if k_scaled is not None else 0
         sp.dtype, sp.D, sp.B, sp.TQ, sp.H, sp.HKV, sp.T = _DT[q.dtype], D, B, TQ, H, HKV, T
         sp.block_size_q, sp.stride_q = bq, s_i.stage_block_stride_q
         sp.n_chunks, sp.block_chunk, sp.scan_window = n, block_chunk, scan_window
@@ -315,7 +334,7 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
         if rope is not None:
             sp.rope_cos, sp.rope_sin = rope[0].data_ptr(), rope[1].data_ptr()
             sp.rope_stride, sp.rope_rows = rope[0].stride(0), rope[0].shape[0]
-            sp.rope_mode = _ROPE_MODES[getattr(s_i, "stage_extend_backend", None) or args.scan_extend_backend]
+            sp.rope_mode = rope_modes[i]
         if debug is not None and "scan_stats" in debug:
             sp.stats = debug["scan_stats"].data_ptr()
         if timer: timer.mark("start")

@@ -129,7 +129,10 @@ typedef struct hipattn_scan_params {
   int32_t* access_counter;
   int64_t access_stride_b, access_stride_h;
   int32_t access_n;
-  int32_t reserved_;
+  int32_t k_scaled_sides;    /* 0 / 1: one prepared copy.  2 (rope_mode RELATIVE only): k_scaled and key_abs hold two
+                                consecutive copies, the keys rotated to table position 0 (left candidates) and 1 (right
+                                candidates), written by hipattn_scan_prepare_keys_rope: the tensor-core scan then runs
+                                with in-kernel RoPE */
 } hipattn_scan_params_t;
 
 int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);
@@ -150,6 +153,17 @@ int hipattn_key_abs_sum(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int
  */
 int hipattn_scan_prepare_keys(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
                               float k_scale, float* key_abs, void* k_scaled, uint32_t* status, void* stream);
+
+/*
+ * As hipattn_scan_prepare_keys, for the scan's in-kernel RoPE with backend "relative": every key is first rotated to
+ * the fixed table position `position` (x * cos + rotate_half(x) * sin in the element type, attention_extend.py:290-407),
+ * then scaled.  Two calls (position 0 into the first copy, position 1 into the second, each copy [B, HKV, T, D] resp.
+ * [B, HKV, T]) give what hipattn_scan_stage expects with k_scaled_sides = 2.
+ */
+int hipattn_scan_prepare_keys_rope(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
+                                   float k_scale, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
+                                   int32_t rope_rows, int32_t position, float* key_abs, void* k_scaled, uint32_t* status,
+                                   void* stream);
 
 /*
  * Initial chunk list of stage 0 (attention_extend.py:2027-2046): left[c] = sink + c * chunk,
