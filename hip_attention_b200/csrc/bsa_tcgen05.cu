@@ -23,6 +23,7 @@
 
 #include "bsa_common.cuh"
 #include "tcgen05_common.cuh"
+#include "rope.cuh"
 
 namespace hipattn {
 namespace {
@@ -76,6 +77,47 @@ struct Meta5 {
   long long start[TK5];   // warp-specialised kernel: block starts of the tile's selected entries, fetched a tile ahead
   int far_ok[2];
   int win_ok[2];
+  int rpos[TK5];          // in-kernel RoPE: table position the key is rotated to (-1: no key)
+};
+
+// In-kernel RoPE on an operand tile of two 128-byte-swizzled K-blocks ([2][rows][128 B], head dim 128): row r is rotated
+// to table position pos(r) (negative: left alone).  Thread `tid` of `nthreads` takes piece tid & 7 of rows (tid >> 3) +
+// i * nthreads / 8; the table pieces of up to ITEMS rows are requested together (fetch), so that their latency is paid
+// once and can overlap with whatever the caller waits for before it rotates (apply).  The caller synchronises the threads
+// around apply and fences towards the tensor cores afterwards.
+template <int DT, int ITEMS>
+struct RopeTile {
+  uint4 c[ITEMS], s[ITEMS];
+  uint32_t live;
+  template <typename PosFn>
+  __device__ __forceinline__ void fetch(const hipattn_bsa_params_t& p, int row0, int rows, int tid, int nthreads, PosFn pos) {
+    live = 0;
+    const int pc = tid & 7;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int r = row0 + (tid >> 3) + i * (nthreads >> 3);
+      const int t = r < rows ? pos(r) : -1;
+      if (t >= 0) {
+        live |= 1u << i;
+        c[i] = rope_table_raw(p.rope_cos, p.rope_stride, p.rope_rows, t, pc);
+        s[i] = rope_table_raw(p.rope_sin, p.rope_stride, p.rope_rows, t, pc);
+      }
+    }
+  }
+  __device__ __forceinline__ void apply(unsigned char* tile, int kblock_bytes, int row0, int tid, int nthreads) {
+    const int pc = tid & 7;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      if (!(live >> i & 1)) continue;
+      const int r = row0 + (tid >> 3) + i * (nthreads >> 3);
+      uint4* plo = reinterpret_cast<uint4*>(tile + sw128(r, pc));
+      uint4* phi = reinterpret_cast<uint4*>(tile + kblock_bytes + sw128(r, pc));
+      uint4 lo = *plo, hi = *phi;
+      rope_rotate_packed<DT>(lo, hi, c[i], s[i]);
+      *plo = lo;
+      *phi = hi;
+    }
+  }
 };
 
 
@@ -97,7 +139,7 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64
       ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u));
 }
 
-template <int DT>
+template <int DT, bool ROPE>
 __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bsa_params_t p, int BQ, int n_sub) {
   using T = typename Elem<DT>::type;
   constexpr int NT = 224;
@@ -179,6 +221,12 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   }
   cp_async_commit();
   cp_async_wait<0>();
+  if (ROPE) {   // in-kernel RoPE: every query row at its own position (attention_extend_bsa.py:797-856)
+    __syncthreads();
+    RopeTile<DT, 5> rq;   // 128 rows x 8 pieces over 224 threads: 28 rows per pass
+    rq.fetch(p, 0, 128, tid, NT, [&](int r) { return s_rowpos[r]; });
+    rq.apply(sQ, 128 * 128, 0, tid, NT);
+  }
   fence_async_smem();
   __syncthreads();
   const int pmin = s_mm[0], pmax = s_mm[1];
@@ -215,6 +263,7 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     }
     m.koff[e] = ko;
     m.voff[e] = vo;
+    m.rpos[e] = (ROPE && t >= 0) ? rope_key_position(kl, j, t, p.window) : -1;
     const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
     const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
     const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
@@ -251,6 +300,14 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     prefetch_start(3, ptid);
     cp_async_commit();
     cp_async_wait<0>();
+    if (ROPE) {   // in-kernel RoPE: the keys of the first two tiles at the positions their places in the list map to
+      producer_sync();
+      for (int t = 0; t < 2 && t < n_tiles; ++t) {
+        RopeTile<DT, 8> rk;
+        rk.fetch(p, 0, TK5, ptid, 64, [&](int r) { return meta[t].rpos[r]; });
+        rk.apply(sK + t * KT_BYTES, TK5 * 128, 0, ptid, 64);
+      }
+    }
     fence_async_smem();
     __syncthreads();  // B0: Q, K(0), K(1), V(0) are in place
     for (int it = 0; it < n_tiles; ++it) {
@@ -270,6 +327,14 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       // with both copies of this tile on their way, resolve the key positions and addresses of tile it + 3
       // (one entry per thread; its block start arrived with the copies of the previous tile)
       if (it + 3 < n_tiles) make_meta(it + 3, ptid, true);
+      if (ROPE && it + 2 < n_tiles) {
+        // in-kernel RoPE: the table pieces of K(it + 2) travel while its rows land; rotate once all pieces are in place
+        RopeTile<DT, 8> rk;
+        rk.fetch(p, 0, TK5, ptid, 64, [&](int r) { return meta[(it + 2) & 3].rpos[r]; });
+        cp_async_wait<1>();
+        producer_sync();
+        rk.apply(sK + (it & 1) * KT_BYTES, TK5 * 128, 0, ptid, 64);
+      }
       cp_async_wait<1>();   // K(it + 2) and V(it) have landed; V(it + 1) may still be in flight
       fence_async_smem();
       if (__syncthreads_or(s_abort)) break;  // B1(it)
@@ -439,14 +504,14 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   }
 }
 
-template <int DT>
+template <int DT, bool ROPE>
 int launch5_ws(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t stream) {
   const size_t smem = 1024 + 2 * 128 * 128 + 4 * (2 * TK5 * 128) + 4 * sizeof(Meta5);
   const int NH = 128 / BQ;
   const int NBLK = cdiv(p.TQ, p.block_size_q);
   const int64_t grid = (int64_t)p.B * (p.H / NH) * NBLK * n_sub;
   HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "attention grid of %lld blocks", (long long)grid);
-  auto kern = bsa_tcgen05_ws_kernel<DT>;
+  auto kern = bsa_tcgen05_ws_kernel<DT, ROPE>;
   HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<(unsigned)grid, 224, smem, stream>>>(p, BQ, n_sub);
   return check_launch("bsa_tcgen05_ws_kernel");
@@ -486,7 +551,9 @@ int bsa_tcgen05(const hipattn_bsa_params_t& p, cudaStream_t stream, bool* handle
   else if (p.block_size_q % 128 == 0) { BQ = 128; n_sub = p.block_size_q / 128; }
   else return HIPATTN_OK;
   *handled = true;
-  return p.dtype == HIPATTN_BF16 ? launch5_ws<HIPATTN_BF16>(p, BQ, n_sub, stream) : launch5_ws<HIPATTN_F16>(p, BQ, n_sub, stream);
+  if (p.rope_cos)
+    return p.dtype == HIPATTN_BF16 ? launch5_ws<HIPATTN_BF16, true>(p, BQ, n_sub, stream) : launch5_ws<HIPATTN_F16, true>(p, BQ, n_sub, stream);
+  return p.dtype == HIPATTN_BF16 ? launch5_ws<HIPATTN_BF16, false>(p, BQ, n_sub, stream) : launch5_ws<HIPATTN_F16, false>(p, BQ, n_sub, stream);
 }
 
 }  // namespace hipattn

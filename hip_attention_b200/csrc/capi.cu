@@ -167,8 +167,8 @@ extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream
     return bsa_generic(*p, (cudaStream_t)stream);
   }
   if (p->rope_cos || p->rope_sin) {
-    // in-kernel RoPE is built into the mma.sync decode and prefill kernels (16-bit, head dim 64 / 128) and the general
-    // kernel (everything else)
+    // in-kernel RoPE is built into the tcgen05 prefill kernel (head dim 128), the mma.sync decode and prefill kernels
+    // (16-bit, head dim 64 / 128) and the general kernel (everything else)
     HIPATTN_REQUIRE(p->rope_cos && p->rope_sin && p->rope_rows > 0, HIPATTN_ERR_INVALID, "attention: cos and sin tables go together");
     HIPATTN_REQUIRE(((uintptr_t)p->rope_cos % 16) == 0 && ((uintptr_t)p->rope_sin % 16) == 0 && p->rope_stride % ra == 0 &&
                         p->rope_stride >= p->D / 2,
@@ -176,6 +176,11 @@ extern "C" int hipattn_bsa_attention(const hipattn_bsa_params_t* p, void* stream
     bool done = false;
     rc = bsa_decode(*p, (cudaStream_t)stream, &done);
     if (done) return rc;
+    const char* pk_ = getenv("HIPATTN_PREFILL_KERNEL");
+    if (!(pk_ && strcmp(pk_, "mma") == 0)) {
+      rc = bsa_tcgen05(*p, (cudaStream_t)stream, &done);
+      if (done) return rc;
+    }
     rc = bsa_mma(*p, (cudaStream_t)stream, &done);
     if (done) return rc;
     return bsa_generic(*p, (cudaStream_t)stream);

@@ -46,17 +46,11 @@ __device__ __forceinline__ void rope_rotate_tile(unsigned char* tile, int row0, 
     if (t < 0) continue;
     uint4* plo = reinterpret_cast<uint4*>(tile + swz<D>(r, pc));
     uint4* phi = reinterpret_cast<uint4*>(tile + swz<D>(r, pc + HALF));
-    float lo[8], hi[8], lo0[8], tc[8], ts[8];
-    widen_piece<DT>(*plo, lo);
-    widen_piece<DT>(*phi, hi);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) lo0[e] = lo[e];
-    rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, t, pc, tc);
-    rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, t, pc, ts);
-    rope_rotate_piece<DT, 8>(lo, hi, tc, ts, true);
-    rope_rotate_piece<DT, 8>(hi, lo0, tc, ts, false);
-    *plo = make_uint4(pack2<DT>(lo[0], lo[1]), pack2<DT>(lo[2], lo[3]), pack2<DT>(lo[4], lo[5]), pack2<DT>(lo[6], lo[7]));
-    *phi = make_uint4(pack2<DT>(hi[0], hi[1]), pack2<DT>(hi[2], hi[3]), pack2<DT>(hi[4], hi[5]), pack2<DT>(hi[6], hi[7]));
+    uint4 lo = *plo, hi = *phi;
+    rope_rotate_packed<DT>(lo, hi, rope_table_raw(p.rope_cos, p.rope_stride, p.rope_rows, t, pc),
+                           rope_table_raw(p.rope_sin, p.rope_stride, p.rope_rows, t, pc));
+    *plo = lo;
+    *phi = hi;
   }
 }
 

@@ -79,6 +79,13 @@ CASES = {
     "rope_mixed_fp32": dict(B=1, TQ=192, T=2048, H=4, HKV=2, D=64, dtype="fp32", sink=32, sw=128, second_k=128,
                             stages=[(64, 4, 64, None), (64, 2, 16, 512), (64, 1, 4, 256)], seed=30, rope_in_kernel="relative",
                             stage_backends=[None, "streaming", None], rope_theta=500000.0),
+    # head dim 128: the tcgen05 scan (two rotated key copies) and the tcgen05 attention kernel with rotation in the tile
+    "rope_d128_fp16": dict(B=1, TQ=192, T=2048, H=4, HKV=2, D=128, dtype="fp16", sink=32, sw=128, second_k=256,
+                           stages=[(64, 4, 64, None), (64, 4, 16, 512), (64, 1, 8, 256)], seed=41, rope_in_kernel="relative",
+                           rope_theta=10000.0),
+    "rope_d128_str_fp16": dict(B=1, TQ=200, T=2048, H=4, HKV=2, D=128, dtype="fp16", sink=32, sw=128, second_k=256,
+                               stages=[(64, 4, 64, None), (64, 1, 8, 256)], seed=42, rope_in_kernel="streaming",
+                               rope_theta=500000.0),
     "rope_str_decode_fp16": dict(B=2, TQ=1, T=1024, H=4, HKV=2, D=128, dtype="fp16", sink=32, sw=128, second_k=128,
                                  stages=[(64, 4, 32, None), (64, 1, 8, 256)], seed=31, rope_in_kernel="streaming",
                                  rope_theta=10000.0),

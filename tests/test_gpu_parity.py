@@ -58,7 +58,8 @@ def test_matches_reference_fixture(name):
 @pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "decode_fp16", "square_fp16", "oddsink_fp16",
                                   "shortwin_fp16", "paged_decode_fp16", "shard_nosink_fp16", "positions_fp16",
                                   "softcap_fp16", "softcap_decode_fp16", "rope_rel_fp16", "rope_str_fp16", "rope_decode_fp16",
-                                  "rope_mixed_fp32", "rope_str_decode_fp16", "fp8_prefill_fp16", "fp8_decode_fp16"])
+                                  "rope_mixed_fp32", "rope_str_decode_fp16", "rope_d128_fp16", "rope_d128_str_fp16", "fp8_prefill_fp16",
+                                  "fp8_decode_fp16"])
 def test_matches_oracle_all_dtypes(name, dtype):
     q, k, v, pos, c, cfg, paged = case_inputs(name, dtype)
     (ref, m) = _oracle(q, k, v, pos, cfg, paged)
