@@ -152,7 +152,9 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   unsigned char* sK = sQ + Q_BYTES;           // 2 buffers
   unsigned char* sV = sK + 2 * KT_BYTES;      // 2 buffers
   Meta5* meta = reinterpret_cast<Meta5*>(sV + 2 * KT_BYTES);  // 4 entries
-  __shared__ __align__(8) unsigned long long s_mbar[3];   // S buffer 0 ready, S buffer 1 ready, PV done
+  // S buffer 0 / 1 ready, PV done (tensor-core commits, one arrival each); P buffer 0 / 1 written (128 softmax threads);
+  // K buffer 0 / 1 filled, V buffer 0 / 1 filled (64 copy threads)
+  __shared__ __align__(8) unsigned long long s_mbar[9];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_rowpos[128];
@@ -175,9 +177,12 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   const int row_t0 = blk_t0 + sub * BQ;
   const int rows_here = max(0, min(BQ, blk_rows - sub * BQ));
   const uint32_t mbar_s0 = smem_u32(&s_mbar[0]), mbar_o = smem_u32(&s_mbar[2]);
+  const uint32_t mbar_p0 = smem_u32(&s_mbar[3]), mbar_k0 = smem_u32(&s_mbar[5]), mbar_v0 = smem_u32(&s_mbar[7]);
 
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar_s0 + 8 * i));
+    for (int i = 3; i < 5; ++i) mbar_init(mbar_s0 + 8 * i, 128);
+    for (int i = 5; i < 9; ++i) mbar_init(mbar_s0 + 8 * i, 64);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     s_abort = 0;
   }
@@ -293,6 +298,12 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
     };
     auto producer_sync = [&]() { asm volatile("bar.sync 1, 64;\n" ::: "memory"); };
+    auto producer_sync_or = [&](bool v) -> bool {
+      uint32_t r;
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 64, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                   : "=r"(r) : "r"((uint32_t)v) : "memory");
+      return r != 0;
+    };
     for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t, ptid, false);
     producer_sync();
     if (n_tiles > 0) { gather_rows(meta[0].koff, kbase, sK); gather_rows(meta[0].voff, vbase, sV); }
@@ -337,7 +348,10 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
       cp_async_wait<1>();   // K(it + 2) and V(it) have landed; V(it + 1) may still be in flight
       fence_async_smem();
-      if (__syncthreads_or(s_abort)) break;  // B1(it)
+      mbar_arrive(mbar_v0 + 8 * (it & 1));                      // V(it) is in place
+      if (it + 2 < n_tiles) mbar_arrive(mbar_k0 + 8 * (it & 1));   // K(it + 2) is in place
+      // the records of tile it + 3 are complete before the next round's copies read them; all copy threads leave together
+      if (producer_sync_or(s_abort != 0)) break;
     }
     cp_async_wait<0>();
   } else if (warp == 4) {
@@ -362,9 +376,13 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       if (n_tiles > 0) issue_s(0);
       if (n_tiles > 1) issue_s(1);
     }
-    for (int it = 0; it < n_tiles; ++it) {
-      if (__syncthreads_or(s_abort)) break;  // B1(it): P(it) is in TMEM, V(it) and K(it + 2) have landed
-      if (lane == 0) {
+    if (lane == 0) {
+      // The roles meet on mbarriers only: the softmax warps run ahead to S(it + 1) as soon as P(it) is written, and the
+      // copies of K(it + 2) have that whole tile to land.
+      for (int it = 0; it < n_tiles; ++it) {
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(mbar_p0 + 8 * (it & 1), ph, &s_abort, p.status)) break;   // P(it) is in TMEM
+        if (!mbar_wait(mbar_v0 + 8 * (it & 1), ph, &s_abort, p.status)) break;   // V(it) has landed
         tc_fence_after();
         const uint32_t tp = tmem + (it & 1) * 64;                        // P(it): 32 columns of packed pairs
         const uint32_t vb = v_lo + (it & 1) * (KT_BYTES >> 4);
@@ -372,10 +390,14 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(tmem_o, tp + kk * 8, dv | (uint64_t)((vb + kk * 128) & 0x3fffu), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(mbar_o);
-        if (it + 2 < n_tiles) issue_s(it + 2);
+        if (it + 2 < n_tiles) {
+          if (!mbar_wait(mbar_k0 + 8 * (it & 1), ph, &s_abort, p.status)) break;   // K(it + 2) has landed
+          tc_fence_after();
+          issue_s(it + 2);
+        }
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ================================ softmax: thread = row = TMEM lane ================================
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
@@ -456,7 +478,8 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       }
       tmem_st32(ts, pk);        // P(it) over the first half of S(it)
       tc_fence_before();
-      if (__syncthreads_or(s_abort)) break;  // B1(it)
+      if (__any_sync(0xffffffffu, s_abort != 0)) break;   // warp-uniform: the TMEM accesses are warp-collective
+      mbar_arrive(mbar_p0 + 8 * (it & 1));
     }
     // ---- epilogue for this thread's row ----
     bool ok = n_tiles > 0;
