@@ -1,6 +1,6 @@
 // Block-sparse attention, prefill, 16-bit types, head dim 128: warp-specialised tcgen05 / TMEM kernel.
 //
-// One CTA (7 warps) owns 128 query rows -- two heads of a KV group x 64 rows, or one head x 128
+// One CTA (8 warps: four softmax, one MMA issuer, three copy warps) owns 128 query rows -- two heads of a KV group x 64 rows, or one head x 128
 // rows -- and walks the key list [sink | selected blocks | window] in tiles of 64 keys.  Two CTAs
 // are resident per SM, so one CTA's softmax overlaps the other's tensor-core work.
 //
@@ -14,7 +14,7 @@
 // K / V rows are gathered with 16-byte cp.async through the page table directly into the swizzled
 // operand layouts.  O stays in TMEM for the whole key list: the running maximum used for the
 // exponentials is only raised (and O rescaled in TMEM) when the true maximum has grown by more than
-// 2^8, which keeps P within bf16 / fp16 range and makes rescaling rare.
+// 2^13 (fp16) or 2^24 (bf16), which keeps P within the element type's range and makes rescaling rare.
 // Every wait on an mbarrier is bounded; a wait that runs out sets HIPATTN_STATUS_TIMEOUT and the CTA
 // leaves through the normal exit (TMEM freed), so a fault in the pipeline cannot hang the device.
 #include <cstdio>
@@ -31,7 +31,9 @@ namespace {
 constexpr int TK5 = 64;            // keys per tile
 constexpr int D5 = 128;            // head dimension
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kRescaleThreshold = 8.f;  // log2 of the growth that triggers a rescale
+// log2 of the growth of a row's maximum that triggers a rescale of O: P = 2^(s - m) stays below 2^13 in fp16 (largest
+// finite value 2^16) and 2^24 in bf16; O and the row sums are fp32
+template <int DT> constexpr float kRescaleThreshold = DT == HIPATTN_BF16 ? 24.f : 13.f;
 
 // 2^x on the special-function unit alone (ex2.approx: about 2 ulp, flushes denormal results, 2^-inf = 0).
 // The probabilities are rounded to 8 or 11 significant bits right after, so the exact exp2f sequence
@@ -140,9 +142,9 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64
 }
 
 template <int DT, bool ROPE>
-__global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bsa_params_t p, int BQ, int n_sub) {
+__global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bsa_params_t p, int BQ, int n_sub) {
   using T = typename Elem<DT>::type;
-  constexpr int NT = 224;
+  constexpr int NT = 256;
   constexpr int Q_BYTES = 2 * 128 * 128;
   constexpr int KT_BYTES = 2 * TK5 * 128;
   extern __shared__ unsigned char smem_raw[];
@@ -152,9 +154,12 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   unsigned char* sK = sQ + Q_BYTES;           // 2 buffers
   unsigned char* sV = sK + 2 * KT_BYTES;      // 2 buffers
   Meta5* meta = reinterpret_cast<Meta5*>(sV + 2 * KT_BYTES);  // 4 entries
-  // S buffer 0 / 1 ready, PV done (tensor-core commits, one arrival each); P buffer 0 / 1 written (128 softmax threads);
-  // K buffer 0 / 1 filled, V buffer 0 / 1 filled (64 copy threads)
-  __shared__ __align__(8) unsigned long long s_mbar[9];
+  // S buffer 0 / 1 ready, PV of an even tile done (tensor-core commits, one arrival each); P buffer 0 / 1 written (128
+  // softmax threads);
+  // K buffer 0 / 1 filled (64 key-copy threads), V buffer 0 / 1 filled (32 value-copy threads); PV of an odd
+  // tile done.  PV completions alternate between two barriers because a waiter may look for PV(t - 1) after PV(t) has
+  // completed: with one barrier its phase bit would have wrapped by then.
+  __shared__ __align__(8) unsigned long long s_mbar[10];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_rowpos[128];
@@ -176,13 +181,18 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   const int blk_rows = min(p.block_size_q, p.TQ - blk_t0);
   const int row_t0 = blk_t0 + sub * BQ;
   const int rows_here = max(0, min(BQ, blk_rows - sub * BQ));
-  const uint32_t mbar_s0 = smem_u32(&s_mbar[0]), mbar_o = smem_u32(&s_mbar[2]);
+  const uint32_t mbar_s0 = smem_u32(&s_mbar[0]);
+  // barrier and phase bit of "PV(t) has completed"
+  auto mbar_o = [&](int t) { return smem_u32(&s_mbar[(t & 1) ? 9 : 2]); };
+  auto phase_o = [](int t) { return (uint32_t)((t >> 1) & 1); };
   const uint32_t mbar_p0 = smem_u32(&s_mbar[3]), mbar_k0 = smem_u32(&s_mbar[5]), mbar_v0 = smem_u32(&s_mbar[7]);
 
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar_s0 + 8 * i));
     for (int i = 3; i < 5; ++i) mbar_init(mbar_s0 + 8 * i, 128);
-    for (int i = 5; i < 9; ++i) mbar_init(mbar_s0 + 8 * i, 64);
+    for (int i = 5; i < 7; ++i) mbar_init(mbar_s0 + 8 * i, 64);
+    for (int i = 7; i < 9; ++i) mbar_init(mbar_s0 + 8 * i, 32);
+    mbar_init(mbar_s0 + 8 * 9, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     s_abort = 0;
   }
@@ -228,7 +238,7 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   cp_async_wait<0>();
   if (ROPE) {   // in-kernel RoPE: every query row at its own position (attention_extend_bsa.py:797-856)
     __syncthreads();
-    RopeTile<DT, 5> rq;   // 128 rows x 8 pieces over 224 threads: 28 rows per pass
+    RopeTile<DT, 4> rq;   // 128 rows x 8 pieces over 256 threads: 32 rows per pass
     rq.fetch(p, 0, 128, tid, NT, [&](int r) { return s_rowpos[r]; });
     rq.apply(sQ, 128 * 128, 0, tid, NT);
   }
@@ -280,76 +290,107 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
 
   if (warp >= 5) {
     // ================================ producers: addresses + gathers ================================
-    const int ptid = tid - 160;  // 0..63
-    // thread ptid copies piece ptid & 15 of rows (ptid >> 4) + 4 i
+    // Warps 5 and 7 (64 threads) resolve the records of the tiles and copy the K tiles (and rotate them under in-kernel
+    // RoPE); warp 6 copies the V tiles.  With four softmax warps and four helper warps every scheduler of the
+    // multiprocessor carries one of each per CTA.
+    const bool k_role = warp != 6;
+    const int ptid = warp == 5 ? lane : (warp == 7 ? 32 + lane : lane);   // 0..63 in the K group, 0..31 in the V warp
+    // K group: thread ptid copies piece ptid & 15 of rows (ptid >> 4) + 4 i, i < 16;
+    // V warp:  thread ptid copies piece ptid & 15 of rows (ptid >> 4) + 2 i, i < 32 (two batches of sixteen)
     const int g_pc = ptid & 15, g_r0 = ptid >> 4;
-    // All sixteen offsets are read first and the copies follow without a branch between them: a row that no
+    // All sixteen offsets of a batch are read first and the copies follow without a branch between them: a row that no
     // query admits (offset -1) is a copy of zero source bytes, which fills its sixteen bytes with zeros.
-    auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst) {
+    auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst, int row0, int rstep) {
       const char* src = base + g_pc * 16;
       const uint32_t d0 = smem_u32(dst) + (g_pc >> 3) * (TK5 * 128);
       long long o[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) o[i] = off[g_r0 + 4 * i];
+      for (int i = 0; i < 16; ++i) o[i] = off[row0 + rstep * i];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const bool live = o[i] >= 0;
-        cp_async16_zfill(d0 + sw128(g_r0 + 4 * i, g_pc & 7), src + (live ? o[i] : 0), live);
+        cp_async16_zfill(d0 + sw128(row0 + rstep * i, g_pc & 7), src + (live ? o[i] : 0), live);
       }
     };
-    auto producer_sync = [&]() { asm volatile("bar.sync 1, 64;\n" ::: "memory"); };
+    auto gather_k = [&](int tile) { gather_rows(meta[tile & 3].koff, kbase, sK + (tile & 1) * KT_BYTES, g_r0, 4); };
+    auto gather_v = [&](int tile) {
+      gather_rows(meta[tile & 3].voff, vbase, sV + (tile & 1) * KT_BYTES, g_r0, 4);
+      gather_rows(meta[tile & 3].voff, vbase, sV + (tile & 1) * KT_BYTES, g_r0 + 2, 4);
+    };
+    auto k_sync = [&]() { asm volatile("bar.sync 2, 64;\n" ::: "memory"); };
+    // all 96 producer threads; returns the OR of the arguments
     auto producer_sync_or = [&](bool v) -> bool {
       uint32_t r;
-      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 64, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 96, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
                    : "=r"(r) : "r"((uint32_t)v) : "memory");
       return r != 0;
     };
-    for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t, ptid, false);
-    producer_sync();
-    if (n_tiles > 0) { gather_rows(meta[0].koff, kbase, sK); gather_rows(meta[0].voff, vbase, sV); }
-    if (n_tiles > 1) gather_rows(meta[1].koff, kbase, sK + KT_BYTES);
-    prefetch_start(3, ptid);
-    cp_async_commit();
-    cp_async_wait<0>();
-    if (ROPE) {   // in-kernel RoPE: the keys of the first two tiles at the positions their places in the list map to
-      producer_sync();
-      for (int t = 0; t < 2 && t < n_tiles; ++t) {
-        RopeTile<DT, 8> rk;
-        rk.fetch(p, 0, TK5, ptid, 64, [&](int r) { return meta[t].rpos[r]; });
-        rk.apply(sK + t * KT_BYTES, TK5 * 128, 0, ptid, 64);
-      }
+    // in-kernel RoPE on a key tile whose copies the K group has waited for
+    auto rotate_k = [&](int tile) {
+      RopeTile<DT, 8> rk;
+      rk.fetch(p, 0, TK5, ptid, 64, [&](int r) { return meta[tile & 3].rpos[r]; });
+      k_sync();
+      rk.apply(sK + (tile & 1) * KT_BYTES, TK5 * 128, 0, ptid, 64);
+    };
+    if (k_role) {
+      for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t, ptid, false);
     }
-    fence_async_smem();
-    __syncthreads();  // B0: Q, K(0), K(1), V(0) are in place
-    for (int it = 0; it < n_tiles; ++it) {
-      // K(it + 2) goes where K(it) was: wait until S(it) has been computed
-      if (it + 2 < n_tiles) {
-        mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
-        gather_rows(meta[(it + 2) & 3].koff, kbase, sK + (it & 1) * KT_BYTES);
-      }
-      prefetch_start(it + 4, ptid);   // block start of this thread's entry of tile it + 4, used one tile from now
+    producer_sync_or(false);
+    if (k_role) {
+      for (int t = 0; t < 2 && t < n_tiles; ++t) gather_k(t);
+      prefetch_start(3, ptid);
       cp_async_commit();
-      // V(it + 1) goes where V(it - 1) was: wait until PV(it - 1) has completed
-      if (it + 1 < n_tiles) {
-        if (it >= 1) mbar_wait(mbar_o, (it - 1) & 1, &s_abort, p.status);
-        gather_rows(meta[(it + 1) & 3].voff, vbase, sV + ((it + 1) & 1) * KT_BYTES);
+      cp_async_wait<0>();
+      if (ROPE) {   // in-kernel RoPE: the keys of the first two tiles at the positions their places in the list map to
+        for (int t = 0; t < 2 && t < n_tiles; ++t) rotate_k(t);
       }
-      cp_async_commit();
-      // with both copies of this tile on their way, resolve the key positions and addresses of tile it + 3
-      // (one entry per thread; its block start arrived with the copies of the previous tile)
-      if (it + 3 < n_tiles) make_meta(it + 3, ptid, true);
-      if (ROPE && it + 2 < n_tiles) {
-        // in-kernel RoPE: the table pieces of K(it + 2) travel while its rows land; rotate once all pieces are in place
-        RopeTile<DT, 8> rk;
-        rk.fetch(p, 0, TK5, ptid, 64, [&](int r) { return meta[(it + 2) & 3].rpos[r]; });
-        cp_async_wait<1>();
-        producer_sync();
-        rk.apply(sK + (it & 1) * KT_BYTES, TK5 * 128, 0, ptid, 64);
-      }
-      cp_async_wait<1>();   // K(it + 2) and V(it) have landed; V(it + 1) may still be in flight
       fence_async_smem();
-      mbar_arrive(mbar_v0 + 8 * (it & 1));                      // V(it) is in place
-      if (it + 2 < n_tiles) mbar_arrive(mbar_k0 + 8 * (it & 1));   // K(it + 2) is in place
+      for (int t = 0; t < 2 && t < n_tiles; ++t) mbar_arrive(mbar_k0 + 8 * t);
+    } else {
+      if (n_tiles > 0) gather_v(0);
+      cp_async_commit();
+    }
+    __syncthreads();  // B0: Q is in place
+    for (int it = 0; it < n_tiles; ++it) {
+      if (k_role) {
+        // K(it + 2) goes where K(it) was: wait until S(it) has been computed
+        if (it + 2 < n_tiles) {
+          mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
+          gather_k(it + 2);
+        }
+        prefetch_start(it + 4, ptid);   // block start of this thread's entry of tile it + 4, used one tile from now
+        cp_async_commit();
+        // The record of tile it + 3 takes the place of that of tile it - 1, which the softmax warps read until P(it - 1)
+        // is written: PV(it - 1) completes after that.  (The block start of tile it + 3 arrived with the copies of the
+        // previous round.)
+        if (it + 3 < n_tiles) {
+          if (it >= 1) mbar_wait(mbar_o(it - 1), phase_o(it - 1), &s_abort, p.status);
+          make_meta(it + 3, ptid, true);
+        }
+        if (ROPE && it + 2 < n_tiles) {
+          // in-kernel RoPE: the table pieces of K(it + 2) travel while its rows land; rotate once all pieces are in place
+          RopeTile<DT, 8> rk;
+          rk.fetch(p, 0, TK5, ptid, 64, [&](int r) { return meta[(it + 2) & 3].rpos[r]; });
+          cp_async_wait<0>();
+          k_sync();
+          rk.apply(sK + (it & 1) * KT_BYTES, TK5 * 128, 0, ptid, 64);
+        }
+        cp_async_wait<0>();   // K(it + 2) has landed
+        fence_async_smem();
+        if (it + 2 < n_tiles) mbar_arrive(mbar_k0 + 8 * (it & 1));   // K(it + 2) is in place
+      } else {
+        // V(it), requested one round ago, is reported before anything else is waited for: PV(it) needs it as soon as
+        // P(it) is written
+        cp_async_wait<0>();
+        fence_async_smem();
+        mbar_arrive(mbar_v0 + 8 * (it & 1));   // V(it) is in place
+        // V(it + 1) goes where V(it - 1) was: wait until PV(it - 1) has completed
+        if (it + 1 < n_tiles) {
+          if (it >= 1) mbar_wait(mbar_o(it - 1), phase_o(it - 1), &s_abort, p.status);
+          gather_v(it + 1);
+        }
+        cp_async_commit();
+      }
       // the records of tile it + 3 are complete before the next round's copies read them; all copy threads leave together
       if (producer_sync_or(s_abort != 0)) break;
     }
@@ -372,9 +413,11 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     };
     __syncthreads();  // B0
     if (lane == 0) {
-      tc_fence_after();
-      if (n_tiles > 0) issue_s(0);
-      if (n_tiles > 1) issue_s(1);
+      for (int t = 0; t < 2 && t < n_tiles; ++t) {
+        if (!mbar_wait(mbar_k0 + 8 * t, 0, &s_abort, p.status)) break;   // K(t) is in place
+        tc_fence_after();
+        issue_s(t);
+      }
     }
     if (lane == 0) {
       // The roles meet on mbarriers only: the softmax warps run ahead to S(it + 1) as soon as P(it) is written, and the
@@ -389,9 +432,9 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(tmem_o, tp + kk * 8, dv | (uint64_t)((vb + kk * 128) & 0x3fffu), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(mbar_o);
+        umma_commit(mbar_o(it));
         if (it + 2 < n_tiles) {
-          if (!mbar_wait(mbar_k0 + 8 * (it & 1), ph, &s_abort, p.status)) break;   // K(it + 2) has landed
+          if (!mbar_wait(mbar_k0 + 8 * (it & 1), ((it + 2) >> 1) & 1, &s_abort, p.status)) break;   // K(it + 2) is in place
           tc_fence_after();
           issue_s(it + 2);
         }
@@ -415,14 +458,16 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       tmem_ld32(ts, s);
       tmem_ld32(ts + 32, s + 32);
       const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
-      if (!(full && !(cap > 0.f))) {   // CTA-uniform slow path: soft-cap and / or per-element admission
+      // CTA-uniform slow paths, each behind its own branch (in one loop the compiler evaluates the soft-cap's tanh for
+      // every element, wanted or not)
+      if (cap > 0.f) {
 #pragma unroll
-        for (int j = 0; j < TK5; ++j) {
-          float x = s[j];
-          if (cap > 0.f) x = tanhf(x / cap) * cap;
-          if (!full && !admits(prow, mt.tpos[j], mt.twin[j] != 0, p.window)) x = -INFINITY;
-          s[j] = x;
-        }
+        for (int j = 0; j < TK5; ++j) s[j] = tanhf(s[j] / cap) * cap;
+      }
+      if (!full) {   // per-element admission
+#pragma unroll
+        for (int j = 0; j < TK5; ++j)
+          if (!admits(prow, mt.tpos[j], mt.twin[j] != 0, p.window)) s[j] = -INFINITY;
       }
       // row maximum with the three-input maximum: four chains of eight instructions instead of sixteen
       float mx4[4] = {s[0], s[1], s[2], s[3]};
@@ -436,11 +481,11 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
 #pragma unroll
       for (int j = TK5 - 4; j < TK5; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kLog2e;
-      const bool need = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
+      const bool need = mx > m_ref + kRescaleThreshold<DT> || (m_ref == -INFINITY && mx > -INFINITY);
       if (__any_sync(0xffffffffu, need)) {   // warp-uniform: tcgen05.ld / st are warp-collective
         const float alpha = !need ? 1.f : (m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx));
         if (it > 0) {
-          mbar_wait(mbar_o, (it - 1) & 1, &s_abort, p.status);   // O is stable once PV(it - 1) is done
+          mbar_wait(mbar_o(it - 1), phase_o(it - 1), &s_abort, p.status);   // O is stable once PV(it - 1) is done
           __syncwarp();
           tc_fence_after();
 #pragma unroll 1
@@ -484,7 +529,7 @@ __global__ void __launch_bounds__(224, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     // ---- epilogue for this thread's row ----
     bool ok = n_tiles > 0;
     if (ok) {
-      ok = mbar_wait(mbar_o, (n_tiles - 1) & 1, &s_abort, p.status);
+      ok = mbar_wait(mbar_o(n_tiles - 1), phase_o(n_tiles - 1), &s_abort, p.status);
       __syncwarp();
       tc_fence_after();
     }
@@ -536,7 +581,7 @@ int launch5_ws(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t st
   HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "attention grid of %lld blocks", (long long)grid);
   auto kern = bsa_tcgen05_ws_kernel<DT, ROPE>;
   HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)grid, 224, smem, stream>>>(p, BQ, n_sub);
+  kern<<<(unsigned)grid, 256, smem, stream>>>(p, BQ, n_sub);
   return check_launch("bsa_tcgen05_ws_kernel");
 }
 
