@@ -21,6 +21,7 @@ struct KeyList {
   const int64_t* idx;  // selected block starts of this query block
   int block_k, sink, T;
   int block_k_shift;   // log2(block_k) when it is a power of two, else -1
+  int sink_floor;      // sink rounded down to whole blocks: the rank of the first selected entry under in-kernel RoPE
 };
 
 __device__ __forceinline__ KeyList make_key_list(const hipattn_bsa_params_t& p, int b, int h, int d, int pmin, int pmax) {
@@ -33,6 +34,7 @@ __device__ __forceinline__ KeyList make_key_list(const hipattn_bsa_params_t& p, 
   kl.block_k = p.block_size_k;
   kl.block_k_shift = (p.block_size_k & (p.block_size_k - 1)) == 0 ? 31 - __clz(p.block_size_k) : -1;
   kl.sink = p.sink;
+  kl.sink_floor = (p.sink / p.block_size_k) * p.block_size_k;
   kl.T = p.T;
   kl.pmax = pmax;
   kl.pmin = pmin;
@@ -87,14 +89,9 @@ __device__ __forceinline__ int key_position(const KeyList& kl, int j, bool* is_w
 __device__ __forceinline__ int rope_key_position(const KeyList& kl, int j, int t, int window) {
   if (j >= kl.n_sink + kl.n_sel) return t;
   const int shift = kl.pmin - window - kl.sink - kl.n_sel + 1;
-  int rank;
-  if (j < kl.n_sink) {
-    rank = t;
-  } else {
-    const int jj = j - kl.n_sink;
-    const int blk = kl.block_k_shift >= 0 ? (jj >> kl.block_k_shift) : (jj / kl.block_k);
-    rank = (blk + kl.sink / kl.block_k) * kl.block_k + (jj - blk * kl.block_k);
-  }
+  // a selected entry's rank is (its block + sink / block_k) * block_k + its place in the block = its place among the
+  // selected entries + the sink rounded down to whole blocks
+  const int rank = j < kl.n_sink ? t : (j - kl.n_sink) + kl.sink_floor;
   return max(0, rank + shift);
 }
 

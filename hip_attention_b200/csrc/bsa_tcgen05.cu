@@ -71,14 +71,19 @@ __device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, un
   return r;
 }
 
-struct Meta5 {
+// Record of a tile for the softmax warps (ring of eight: the copy warps run at most three tiles ahead of the softmax
+// warps, so a slot is rewritten long after its readers have left it) ...
+struct MetaS {
   int tpos[TK5];
-  int twin[TK5];
+  unsigned char twin[TK5];
+  int far_ok[2];
+  int win_ok[2];
+};
+// ... and for the copy warps (ring of four)
+struct Meta5 {
   long long koff[TK5];
   long long voff[TK5];
   long long start[TK5];   // warp-specialised kernel: block starts of the tile's selected entries, fetched a tile ahead
-  int far_ok[2];
-  int win_ok[2];
   int rpos[TK5];          // in-kernel RoPE: table position the key is rotated to (-1: no key)
 };
 
@@ -154,6 +159,7 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   unsigned char* sK = sQ + Q_BYTES;           // 2 buffers
   unsigned char* sV = sK + 2 * KT_BYTES;      // 2 buffers
   Meta5* meta = reinterpret_cast<Meta5*>(sV + 2 * KT_BYTES);  // 4 entries
+  MetaS* metas = reinterpret_cast<MetaS*>(meta + 4);            // 8 entries
   // S buffer 0 / 1 ready, PV of an even tile done (tensor-core commits, one arrival each); P buffer 0 / 1 written (128
   // softmax threads);
   // K buffer 0 / 1 filled (64 key-copy threads), V buffer 0 / 1 filled (32 value-copy threads); PV of an odd
@@ -255,6 +261,9 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
 
   const char* kbase = (const char*)(p.k.cache ? p.k.cache : p.k.dense);
   const char* vbase = (const char*)(p.v.cache ? p.v.cache : p.v.dense);
+  const bool dense_kv = p.k.cache == nullptr && p.v.cache == nullptr;
+  const long long k_base_off = ((long long)b * p.k.stride_b + (long long)hkv * p.k.stride_h) * 2, k_step = p.k.stride_t * 2;
+  const long long v_base_off = ((long long)b * p.v.stride_b + (long long)hkv * p.v.stride_h) * 2, v_step = p.v.stride_t * 2;
   // requests the block start of entry e of `tile` (if it is a selected entry) into the tile's record; the copy joins
   // the calling thread's next commit group and must be consumed by the same thread
   auto prefetch_start = [&](int tile, int e) {
@@ -266,15 +275,21 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   // position, addresses and admission summary of entry e of `tile`; all 32 lanes of a warp call it with e = 32 h + lane
   auto make_meta = [&](int tile, int e, bool prefetched) {
     Meta5& m = meta[tile & 3];
+    MetaS& ms = metas[tile & 7];
     bool w;
     const int j = tile * TK5 + e;
     const int t = prefetched ? key_position_at(kl, j, m.start[e], &w) : key_position(kl, j, &w);
-    m.tpos[e] = t;
-    m.twin[e] = (t >= 0 && w) ? 1 : 0;
+    ms.tpos[e] = t;
+    ms.twin[e] = (t >= 0 && w) ? 1 : 0;
     long long ko = -1, vo = -1;
     if (t >= 0) {
-      ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
-      vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
+      if (dense_kv) {   // dense tensors: one multiply-add per tensor on top of the CTA's own base
+        ko = k_base_off + (long long)t * k_step;
+        vo = v_base_off + (long long)t * v_step;
+      } else {
+        ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
+        vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
+      }
     }
     m.koff[e] = ko;
     m.voff[e] = vo;
@@ -283,8 +298,8 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
     const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
     if (lane == 0) {
-      m.far_ok[e >> 5] = f;
-      m.win_ok[e >> 5] = g;
+      ms.far_ok[e >> 5] = f;
+      ms.win_ok[e >> 5] = g;
     }
   };
 
@@ -360,13 +375,8 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         }
         prefetch_start(it + 4, ptid);   // block start of this thread's entry of tile it + 4, used one tile from now
         cp_async_commit();
-        // The record of tile it + 3 takes the place of that of tile it - 1, which the softmax warps read until P(it - 1)
-        // is written: PV(it - 1) completes after that.  (The block start of tile it + 3 arrived with the copies of the
-        // previous round.)
-        if (it + 3 < n_tiles) {
-          if (it >= 1) mbar_wait(mbar_o(it - 1), phase_o(it - 1), &s_abort, p.status);
-          make_meta(it + 3, ptid, true);
-        }
+        // the record of tile it + 3 (its block start arrived with the copies of the previous round)
+        if (it + 3 < n_tiles) make_meta(it + 3, ptid, true);
         if (ROPE && it + 2 < n_tiles) {
           // in-kernel RoPE: the table pieces of K(it + 2) travel while its rows land; rotate once all pieces are in place
           RopeTile<DT, 8> rk;
@@ -449,7 +459,7 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     float m_ref = -INFINITY, l_run = 0.f;
     __syncthreads();  // B0
     for (int it = 0; it < n_tiles; ++it) {
-      const Meta5& mt = meta[it & 3];
+      const MetaS& mt = metas[it & 7];
       const uint32_t ts = tmem + (it & 1) * 64 + lane_base;
       mbar_wait(mbar_s0 + 8 * (it & 1), (it >> 1) & 1, &s_abort, p.status);
       __syncwarp();
@@ -574,7 +584,7 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
 
 template <int DT, bool ROPE>
 int launch5_ws(const hipattn_bsa_params_t& p, int BQ, int n_sub, cudaStream_t stream) {
-  const size_t smem = 1024 + 2 * 128 * 128 + 4 * (2 * TK5 * 128) + 4 * sizeof(Meta5);
+  const size_t smem = 1024 + 2 * 128 * 128 + 4 * (2 * TK5 * 128) + 4 * sizeof(Meta5) + 8 * sizeof(MetaS);
   const int NH = 128 / BQ;
   const int NBLK = cdiv(p.TQ, p.block_size_q);
   const int64_t grid = (int64_t)p.B * (p.H / NH) * NBLK * n_sub;

@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
   const char* kbase = reinterpret_cast<const char*>(p.k_scaled);
   const uint32_t sK_u32 = smem_u32(sK), sQ_u32 = smem_u32(sQ);
   const uint32_t idesc = make_idesc(DT == HIPATTN_BF16 ? 1 : 0, 128, NR, 0);
+  const uint64_t da0 = make_desc(sK_u32, 16, 1024), db0 = make_desc(sQ_u32, 16, 1024);
   const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);
   const int side = tid & 1;
   // in-kernel RoPE, backend "relative": the prepared keys come in two copies (rotated to position 0 / 1 for the left /
@@ -284,12 +285,12 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_s
       ++rr;
       if (scored && tid == 0) {
         tc_fence_after();
+        // the descriptors of the K-steps differ from the first one's in the start-address field only (shared-memory
+        // addresses stay below 2^18, so the 14-bit field does not carry): one add each instead of building them anew
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t da = make_desc(sK_u32 + (k >> 2) * K_BLOCK_BYTES + (k & 3) * 32, 16, 1024);
-          const uint64_t db = make_desc(sQ_u32 + (k >> 2) * Q_BLOCK_BYTES + (k & 3) * 32, 16, 1024);
-          umma(tmem, da, db, idesc, k > 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          umma(tmem, da0 + (uint64_t)(((k >> 2) * K_BLOCK_BYTES + (k & 3) * 32) >> 4),
+               db0 + (uint64_t)(((k >> 2) * Q_BLOCK_BYTES + (k & 3) * 32) >> 4), idesc, k > 0 ? 1u : 0u);
         umma_commit(mbar);
       }
       __syncwarp();
