@@ -465,8 +465,7 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       __syncwarp();
       tc_fence_after();
       float s[TK5];
-      tmem_ld32(ts, s);
-      tmem_ld32(ts + 32, s + 32);
+      tmem_ld64(ts, s);   // one instruction: the two halves' latencies overlap
       const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
       // CTA-uniform slow paths, each behind its own branch (in one loop the compiler evaluates the soft-cap's tanh for
       // every element, wanted or not)
