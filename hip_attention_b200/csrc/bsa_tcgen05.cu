@@ -14,7 +14,7 @@
 // K / V rows are gathered with 16-byte cp.async through the page table directly into the swizzled
 // operand layouts.  O stays in TMEM for the whole key list: the running maximum used for the
 // exponentials is only raised (and O rescaled in TMEM) when the true maximum has grown by more than
-// 2^13 (fp16) or 2^24 (bf16), which keeps P within the element type's range and makes rescaling rare.
+// 2^13, which keeps P within the range of fp16 and makes rescaling rare.
 // Every wait on an mbarrier is bounded; a wait that runs out sets HIPATTN_STATUS_TIMEOUT and the CTA
 // leaves through the normal exit (TMEM freed), so a fault in the pipeline cannot hang the device.
 #include <cstdio>
@@ -31,9 +31,10 @@ namespace {
 constexpr int TK5 = 64;            // keys per tile
 constexpr int D5 = 128;            // head dimension
 constexpr float kLog2e = 1.4426950408889634f;
-// log2 of the growth of a row's maximum that triggers a rescale of O: P = 2^(s - m) stays below 2^13 in fp16 (largest
-// finite value 2^16) and 2^24 in bf16; O and the row sums are fp32
-template <int DT> constexpr float kRescaleThreshold = DT == HIPATTN_BF16 ? 24.f : 13.f;
+// log2 of the growth of a row's maximum that triggers a rescale of O: P = 2^(s - m) stays below 2^13 (fp16's largest
+// finite value is 2^16); O and the row sums are fp32.  A larger bound for bf16 (2^24 was tried) costs accuracy: the
+// largest output error against an fp32 recompute grew from 0.019 to 0.025 on the 128k prefill workload.
+template <int DT> constexpr float kRescaleThreshold = 13.f;
 
 // 2^x on the special-function unit alone (ex2.approx: about 2 ulp, flushes denormal results, 2^-inf = 0).
 // The probabilities are rounded to 8 or 11 significant bits right after, so the exact exp2f sequence
