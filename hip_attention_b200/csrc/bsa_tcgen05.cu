@@ -504,8 +504,9 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
             tmem_ld32(tmem_o + lane_base + c, o);
 #pragma unroll
             for (int j = 0; j < 32; ++j) o[j] *= alpha;
-            tmem_st32(tmem_o + lane_base + c, o);
+            tmem_st32<false>(tmem_o + lane_base + c, o);   // the four stores are waited for together
           }
+          tmem_wait_st();
         }
         if (need) {
           l_run *= alpha;
