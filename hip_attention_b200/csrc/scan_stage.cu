@@ -89,9 +89,12 @@ __device__ __forceinline__ float mac(float q, float k, float acc) {
   return fmaf(q, k, acc);                                         // 16-bit inputs: the product is exact
 }
 
-// RT = pooled query rows processed per pass over a staged key pair
-template <int DT, int D, int RT>
-__global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int NW) {
+// RT = pooled query rows processed per pass over a staged key pair; EXT = the call uses in-kernel RoPE, an fp8 cache or
+// the access counters (the plain instantiation carries none of their branches: in decode they cost 60 % of the time)
+template <int DT, int D, int RT, bool EXT>
+// (decode, one pooled row: the kernel is bound by random row reads from HBM and lives on resident warps, so the
+// register allocation aims at seven CTAs per multiprocessor)
+__global__ void __launch_bounds__(128, RT == 1 ? 7 : 1) scan_stage_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int NW) {
   using G = RowGeom<DT, D>;
   using T = typename Elem<DT>::type;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -172,7 +175,7 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
     int tl = (left + mid) >> 1, tr = (mid + right) >> 1;
     const int tl_asked = tl, tr_asked = tr;
     // (with in-kernel RoPE a key's score depends on the side it is proposed for: nothing is reused)
-    const bool reuse = p.rope_mode == HIPATTN_ROPE_NONE;
+    const bool reuse = !EXT || p.rope_mode == HIPATTN_ROPE_NONE;
     const bool known_l = act && reuse && tl == won_t, known_r = act && reuse && tr == won_t;
     const char* src_l = nullptr;
     const char* src_r = nullptr;
@@ -184,7 +187,7 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
       }
       if (!known_l) src_l = token_row(p.k, b, tl, hkv, Elem<DT>::bytes, p.status);
       if (!known_r) src_r = token_row(p.k, b, tr, hkv, Elem<DT>::bytes, p.status);
-      if (p.access_counter) {   // (a candidate whose score is known was marked when it was fetched)
+      if (EXT && p.access_counter) {   // (a candidate whose score is known was marked when it was fetched)
         if (!known_l) mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, tl);
         if (!known_r) mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, tr);
       }
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
         const int owner = rr & 31, side = rr >> 5;
         const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)(side ? src_r : src_l), owner);
         if (a != 0ull && sub < kRowsPerIter) {
-          if (DT != HIPATTN_F32 && p.k.fp8_e5m2)   // an fp8 cache: 8 bytes become one 16-byte piece of the element type
+          if (EXT && DT != HIPATTN_F32 && p.k.fp8_e5m2)   // an fp8 cache: 8 bytes become one 16-byte piece of the element type
             *reinterpret_cast<uint4*>(wstage + (size_t)rr * G::kRowStride + piece * 16) =
                 widen_fp8_e5m2<DT == HIPATTN_F32 ? HIPATTN_F16 : DT>(__ldg(reinterpret_cast<const uint2*>((const char*)a + piece * 8)));
           else
@@ -235,7 +238,7 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
 #pragma unroll 2
         for (int pc = 0; pc < G::kPieces; ++pc) {
           float kl[G::kVec], kr[G::kVec];
-          if (p.rope_mode == HIPATTN_ROPE_NONE) {
+          if (!EXT || p.rope_mode == HIPATTN_ROPE_NONE) {
             unpack_scaled<DT>(*reinterpret_cast<const uint4*>(my_l + pc * 16), p.k_scale, kl);
             unpack_scaled<DT>(*reinterpret_cast<const uint4*>(my_r + pc * 16), p.k_scale, kr);
           } else {   // keys at their chunk's index (streaming) or at 0 / 1 for the left / right candidate (relative)
@@ -287,7 +290,7 @@ __global__ void __launch_bounds__(128) scan_stage_kernel(const hipattn_scan_para
   }  // chunk blocks
 }
 
-template <int DT, int D, int RT>
+template <int DT, int D, int RT, bool EXT>
 int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
   using G = RowGeom<DT, D>;
   const int R = p.block_size_q / p.stride_q;
@@ -305,7 +308,7 @@ int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
   const int nblk = scan_ctas_per_unit(units, nblk_total);
   const int64_t grid = units * nblk;
   HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
-  auto kern = scan_stage_kernel<DT, D, RT>;
+  auto kern = scan_stage_kernel<DT, D, RT, EXT>;
   HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<(unsigned)grid, 32 * NW, smem, stream>>>(p, nblk, nblk_total, NW);
   return check_launch("scan_stage_kernel");
@@ -316,10 +319,11 @@ int dispatch_rows(const hipattn_scan_params_t& p, cudaStream_t stream) {
   const int R = p.block_size_q / p.stride_q;
   // rows that can be valid: a single query row (decode) needs one accumulator pair only
   const int rows = min(R, cdiv(p.TQ, p.stride_q));
-  if (rows <= 1) return launch<DT, D, 1>(p, stream);
-  if (R <= 16) return launch<DT, D, 16>(p, stream);
-  if (R <= 32) return launch<DT, D, 32>(p, stream);
-  return launch<DT, D, 64>(p, stream);
+  const bool ext = p.rope_mode != HIPATTN_ROPE_NONE || p.k.fp8_e5m2 || p.access_counter != nullptr;
+  if (rows <= 1) return ext ? launch<DT, D, 1, true>(p, stream) : launch<DT, D, 1, false>(p, stream);
+  if (R <= 16) return ext ? launch<DT, D, 16, true>(p, stream) : launch<DT, D, 16, false>(p, stream);
+  if (R <= 32) return ext ? launch<DT, D, 32, true>(p, stream) : launch<DT, D, 32, false>(p, stream);
+  return ext ? launch<DT, D, 64, true>(p, stream) : launch<DT, D, 64, false>(p, stream);
 }
 
 template <int DT>
