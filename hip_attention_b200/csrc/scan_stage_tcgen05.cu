@@ -43,10 +43,11 @@ struct ScanShared {
 };
 constexpr uint32_t kScanSlack = 896;   // padding reserved in front of the tiles
 
-// Resident CTAs per multiprocessor the register allocation aims at: five with 16 or 32 pooled rows (measured faster
-// than six CTAs squeezed into 80 registers), four with 64, three with 128 (shared memory).
+// Resident CTAs per multiprocessor the register allocation aims at: six with 16 or 32 pooled rows (80 registers; shared
+// memory holds six 37 KB CTAs; at 92 registers only five are resident and stages 0 and 1 of the 128k prefill take 8 %
+// longer), four with 64, three with 128 (shared memory).
 template <int DT, int D, int NR>
-__global__ void __launch_bounds__(128, NR <= 32 ? 5 : (NR <= 64 ? 4 : 3)) scan_stage_tcgen05_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int check) {
+__global__ void __launch_bounds__(128, NR <= 32 ? 6 : (NR <= 64 ? 4 : 3)) scan_stage_tcgen05_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int check) {
   constexpr int ROWB = D * 2;                 // bytes per key / query row
   constexpr int PIECES = ROWB / 16;
   constexpr int KB = D / 64;                  // 128-byte K-blocks per row
