@@ -102,12 +102,13 @@ def test_config1_fixture():
 
 
 @pytest.mark.parametrize("page", [1, 16, 64])
-@pytest.mark.parametrize("tq", [1, 100])
-def test_paged_equals_dense(page, tq):
-    """Paging is pure addressing: a permuted page pool gives the dense result (any page size)."""
+@pytest.mark.parametrize("tq,case", [(1, "paged_prefill_fp16"), (100, "paged_prefill_fp16"), (200, "d128_fp16"), (200, "rope_d128_fp16")])
+def test_paged_equals_dense(page, tq, case):
+    """Paging is pure addressing: a permuted page pool gives the dense result (any page size); head dim 128 takes the
+    tcgen05 scan and attention kernels, with and without in-kernel RoPE."""
     import cases as cs
     from cases import make_paged
-    base = dict(cs.CASES["paged_prefill_fp16"], TQ=tq, dtype="bf16")
+    base = dict(cs.CASES[case], TQ=tq, dtype="bf16")
     cs.CASES["_tmp_paged"] = {k_: v_ for k_, v_ in base.items() if k_ not in ("page", "ext")}
     try:
         q, k, v, pos, c, cfg, _ = case_inputs("_tmp_paged")
