@@ -405,12 +405,18 @@ __global__ void __launch_bounds__(128) bsa_decode_mma_kernel(const hipattn_bsa_p
     }
     // ---- admission + online softmax (rows lane / 4 < G; rows 8..15 are padding) ----
     float mx = -INFINITY;
+    if (cap > 0.f) {   // soft-cap behind its own uniform branch: inside the loop the tanh is evaluated under a predicate
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) s[nt][e] = tanhf(s[nt][e] / cap) * cap;
+      }
+    }
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         float x = s[nt][e];
-        if (cap > 0.f) x = tanhf(x / cap) * cap;
         x *= kLog2e;
         const int col = warp * 16 + nt * 8 + (lane & 3) * 2 + e;
         if (mt.koff[col] < 0) x = -INFINITY;

@@ -205,12 +205,18 @@ __global__ void __launch_bounds__(M * 2) bsa_mma_kernel(const hipattn_bsa_params
     // ---- admission + online softmax ----
     const bool full = (mt.far_ok[0] && mt.far_ok[1]) || (mt.win_ok[0] && mt.win_ok[1]);
     float mx0 = -INFINITY, mx1 = -INFINITY;
+    if (cap > 0.f) {   // soft-cap behind its own uniform branch: inside the loop the tanh is evaluated under a predicate
+#pragma unroll
+      for (int nt = 0; nt < TKM / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = tanhf(s[nt][e] / cap) * cap;
+      }
+    }
 #pragma unroll
     for (int nt = 0; nt < TKM / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float x = s[nt][e];
-        if (cap > 0.f) x = tanhf(x / cap) * cap;
         x *= kLog2e;
         if (!full) {
           const int col = nt * 8 + (lane & 3) * 2 + (e & 1);
