@@ -74,6 +74,10 @@ __device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, un
 
 // Record of a tile for the softmax warps (ring of eight: the copy warps run at most three tiles ahead of the softmax
 // warps, so a slot is rewritten long after its readers have left it) ...
+// 256 zero bytes in device memory: the row address of a key that no query admits, so that the copy loops carry neither
+// a predicate nor a source size
+__device__ __align__(256) unsigned char g_zero_row[256];
+
 struct MetaS {
   int tpos[TK5];
   unsigned char twin[TK5];
@@ -82,8 +86,8 @@ struct MetaS {
 };
 // ... and for the copy warps (ring of four)
 struct Meta5 {
-  long long koff[TK5];
-  long long voff[TK5];
+  const char* kptr[TK5];   // address of the K / V row (the zero row when the entry has none)
+  const char* vptr[TK5];
   long long start[TK5];   // warp-specialised kernel: block starts of the tile's selected entries, fetched a tile ahead
   int rpos[TK5];          // in-kernel RoPE: table position the key is rotated to (-1: no key)
 };
@@ -292,8 +296,8 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;
       }
     }
-    m.koff[e] = ko;
-    m.voff[e] = vo;
+    m.kptr[e] = ko >= 0 ? kbase + ko : reinterpret_cast<const char*>(g_zero_row);
+    m.vptr[e] = vo >= 0 ? vbase + vo : reinterpret_cast<const char*>(g_zero_row);
     m.rpos[e] = (ROPE && t >= 0) ? rope_key_position(kl, j, t, p.window) : -1;
     const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
     const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
@@ -314,24 +318,20 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     // K group: thread ptid copies piece ptid & 15 of rows (ptid >> 4) + 4 i, i < 16;
     // V warp:  thread ptid copies piece ptid & 15 of rows (ptid >> 4) + 2 i, i < 32 (two batches of sixteen)
     const int g_pc = ptid & 15, g_r0 = ptid >> 4;
-    // All sixteen offsets of a batch are read first and the copies follow without a branch between them: a row that no
-    // query admits (offset -1) is a copy of zero source bytes, which fills its sixteen bytes with zeros.
-    auto gather_rows = [&](const long long* off, const char* base, unsigned char* dst, int row0, int rstep) {
-      const char* src = base + g_pc * 16;
+    // All sixteen row addresses of a batch are read first and the copies follow without a branch between them.
+    auto gather_rows = [&](const char* const* rowp, unsigned char* dst, int row0, int rstep) {
       const uint32_t d0 = smem_u32(dst) + (g_pc >> 3) * (TK5 * 128);
-      long long o[16];
+      const char* o[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) o[i] = off[row0 + rstep * i];
+      for (int i = 0; i < 16; ++i) o[i] = rowp[row0 + rstep * i];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const bool live = o[i] >= 0;
-        cp_async16_zfill(d0 + sw128(row0 + rstep * i, g_pc & 7), src + (live ? o[i] : 0), live);
-      }
+      for (int i = 0; i < 16; ++i)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d0 + sw128(row0 + rstep * i, g_pc & 7)), "l"(o[i] + g_pc * 16));
     };
-    auto gather_k = [&](int tile) { gather_rows(meta[tile & 3].koff, kbase, sK + (tile & 1) * KT_BYTES, g_r0, 4); };
+    auto gather_k = [&](int tile) { gather_rows(meta[tile & 3].kptr, sK + (tile & 1) * KT_BYTES, g_r0, 4); };
     auto gather_v = [&](int tile) {
-      gather_rows(meta[tile & 3].voff, vbase, sV + (tile & 1) * KT_BYTES, g_r0, 4);
-      gather_rows(meta[tile & 3].voff, vbase, sV + (tile & 1) * KT_BYTES, g_r0 + 2, 4);
+      gather_rows(meta[tile & 3].vptr, sV + (tile & 1) * KT_BYTES, g_r0, 4);
+      gather_rows(meta[tile & 3].vptr, sV + (tile & 1) * KT_BYTES, g_r0 + 2, 4);
     };
     auto k_sync = [&]() { asm volatile("bar.sync 2, 64;\n" ::: "memory"); };
     // all 96 producer threads; returns the OR of the arguments
