@@ -14,7 +14,7 @@
 // K / V rows are gathered with 16-byte cp.async through the page table directly into the swizzled
 // operand layouts.  O stays in TMEM for the whole key list: the running maximum used for the
 // exponentials is only raised (and O rescaled in TMEM) when the true maximum has grown by more than
-// 2^13, which keeps P within the range of fp16 and makes rescaling rare.
+// 2^13 (fp16) / 2^24 (bf16), which keeps P within the element type's range and makes rescaling rare.
 // Every wait on an mbarrier is bounded; a wait that runs out sets HIPATTN_STATUS_TIMEOUT and the CTA
 // leaves through the normal exit (TMEM freed), so a fault in the pipeline cannot hang the device.
 #include <cstdio>
@@ -31,10 +31,12 @@ namespace {
 constexpr int TK5 = 64;            // keys per tile
 constexpr int D5 = 128;            // head dimension
 constexpr float kLog2e = 1.4426950408889634f;
-// log2 of the growth of a row's maximum that triggers a rescale of O: P = 2^(s - m) stays below 2^13 (fp16's largest
-// finite value is 2^16); O and the row sums are fp32.  A larger bound for bf16 (2^24 was tried) costs accuracy: the
-// largest output error against an fp32 recompute grew from 0.019 to 0.025 on the 128k prefill workload.
-template <int DT> constexpr float kRescaleThreshold = 13.f;
+// log2 of the growth of a row's maximum that triggers a rescale of O: P = 2^(s - m) stays below 2^13 in fp16 (largest
+// finite value 2^16) and 2^24 in bf16; O and the row sums are fp32.  A reference maximum that lags the true one costs no
+// accuracy because the row sums are taken from the rounded P (see the softmax loop): with sums of the unrounded values
+// the largest output error against an fp32 recompute grew from 0.019 (threshold 2^8) to 0.025 (2^24) on the 128k
+// prefill workload; with rounded sums it is 0.012 at every threshold, the figure of the exact-maximum kernel.
+template <int DT> constexpr float kRescaleThreshold = DT == HIPATTN_BF16 ? 24.f : 13.f;
 
 // 2^x on the special-function unit alone (ex2.approx: about 2 ulp, flushes denormal results, 2^-inf = 0).
 // The probabilities are rounded to 8 or 11 significant bits right after, so the exact exp2f sequence
@@ -44,6 +46,18 @@ __device__ __forceinline__ float exp2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
+}
+
+// the two 16-bit elements of a packed pair as floats (exact)
+template <int DT>
+__device__ __forceinline__ float pair_lo(uint32_t w) {
+  if (DT == HIPATTN_BF16) return __uint_as_float(w << 16);
+  return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
+}
+template <int DT>
+__device__ __forceinline__ float pair_hi(uint32_t w) {
+  if (DT == HIPATTN_BF16) return __uint_as_float(w & 0xffff0000u);
+  return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
 }
 
 // two-wide fp32 arithmetic (one instruction for a pair of lanes' values): the softmax is bound by instruction issue
@@ -523,8 +537,11 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         float x0, x1;
         f32x2_split(fma_f32x2(f32x2(s[j], s[j + 1]), scale2, nbase2), x0, x1);
         const float e0 = exp2_approx(x0), e1 = exp2_approx(x1);
-        sum2[(j >> 1) & 3] = add_f32x2(sum2[(j >> 1) & 3], f32x2(e0, e1));
-        pk[j >> 1] = __uint_as_float(pack2<DT>(e0, e1));
+        const uint32_t w = pack2<DT>(e0, e1);
+        pk[j >> 1] = __uint_as_float(w);
+        // the row sum takes the ROUNDED weights, the ones P V is computed with: numerator and denominator then carry the
+        // same rounding of a row's largest terms and it cancels in O / l
+        sum2[(j >> 1) & 3] = add_f32x2(sum2[(j >> 1) & 3], f32x2(pair_lo<DT>(w), pair_hi<DT>(w)));
       }
       {
         float a0, a1, b0, b1;
