@@ -97,13 +97,13 @@ struct MetaS {
   unsigned char twin[TK5];
   int far_ok[2];
   int win_ok[2];
+  int rpos[TK5];          // in-kernel RoPE: table position the key is rotated to (-1: no key)
 };
 // ... and for the copy warps (ring of four)
 struct Meta5 {
   const char* kptr[TK5];   // address of the K / V row (the zero row when the entry has none)
   const char* vptr[TK5];
   long long start[TK5];   // warp-specialised kernel: block starts of the tile's selected entries, fetched a tile ahead
-  int rpos[TK5];          // in-kernel RoPE: table position the key is rotated to (-1: no key)
 };
 
 // In-kernel RoPE on an operand tile of two 128-byte-swizzled K-blocks ([2][rows][128 B], head dim 128): row r is rotated
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   // K buffer 0 / 1 filled (64 key-copy threads), V buffer 0 / 1 filled (32 value-copy threads); PV of an odd
   // tile done.  PV completions alternate between two barriers because a waiter may look for PV(t - 1) after PV(t) has
   // completed: with one barrier its phase bit would have wrapped by then.
-  __shared__ __align__(8) unsigned long long s_mbar[10];
+  __shared__ __align__(8) unsigned long long s_mbar[12];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_rowpos[128];
@@ -211,11 +211,24 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   auto mbar_o = [&](int t) { return smem_u32(&s_mbar[(t & 1) ? 9 : 2]); };
   auto phase_o = [](int t) { return (uint32_t)((t >> 1) & 1); };
   const uint32_t mbar_p0 = smem_u32(&s_mbar[3]), mbar_k0 = smem_u32(&s_mbar[5]), mbar_v0 = smem_u32(&s_mbar[7]);
+  // in-kernel RoPE: K buffer 0 / 1 has landed, not yet rotated (64 key-copy threads); the softmax warps rotate it between
+  // two of their tiles - they wait for S there anyway - and report the buffer ready (128 arrivals instead of 64)
+  const uint32_t mbar_kraw0 = smem_u32(&s_mbar[10]);
+  // rotates K(tile) in place; called by the 128 softmax threads
+  auto rotate_k_tile = [&](int tile) {
+    RopeTile<DT, 4> rk;
+    rk.fetch(p, 0, TK5, tid, 128, [&](int r) { return metas[tile & 7].rpos[r]; });
+    mbar_wait(mbar_kraw0 + 8 * (tile & 1), (tile >> 1) & 1, &s_abort, p.status);
+    rk.apply(sK + (tile & 1) * KT_BYTES, TK5 * 128, 0, tid, 128);
+    fence_async_smem();
+    mbar_arrive(mbar_k0 + 8 * (tile & 1));
+  };
 
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(mbar_s0 + 8 * i));
     for (int i = 3; i < 5; ++i) mbar_init(mbar_s0 + 8 * i, 128);
-    for (int i = 5; i < 7; ++i) mbar_init(mbar_s0 + 8 * i, 64);
+    for (int i = 5; i < 7; ++i) mbar_init(mbar_s0 + 8 * i, ROPE ? 128 : 64);
+    for (int i = 10; i < 12; ++i) mbar_init(mbar_s0 + 8 * i, 64);
     for (int i = 7; i < 9; ++i) mbar_init(mbar_s0 + 8 * i, 32);
     mbar_init(mbar_s0 + 8 * 9, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -312,7 +325,7 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     }
     m.kptr[e] = ko >= 0 ? kbase + ko : reinterpret_cast<const char*>(g_zero_row);
     m.vptr[e] = vo >= 0 ? vbase + vo : reinterpret_cast<const char*>(g_zero_row);
-    m.rpos[e] = (ROPE && t >= 0) ? rope_key_position(kl, j, t, p.window) : -1;
+    if (ROPE) ms.rpos[e] = t >= 0 ? rope_key_position(kl, j, t, p.window) : -1;
     const bool far_ok = t >= 0 && !w && t <= rmin - p.window;
     const bool win_ok = t >= 0 && w && t > rmax - p.window && t <= rmin;
     const int f = __all_sync(0xffffffffu, far_ok), g = __all_sync(0xffffffffu, win_ok);
@@ -347,20 +360,12 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       gather_rows(meta[tile & 3].vptr, sV + (tile & 1) * KT_BYTES, g_r0, 4);
       gather_rows(meta[tile & 3].vptr, sV + (tile & 1) * KT_BYTES, g_r0 + 2, 4);
     };
-    auto k_sync = [&]() { asm volatile("bar.sync 2, 64;\n" ::: "memory"); };
     // all 96 producer threads; returns the OR of the arguments
     auto producer_sync_or = [&](bool v) -> bool {
       uint32_t r;
       asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 96, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
                    : "=r"(r) : "r"((uint32_t)v) : "memory");
       return r != 0;
-    };
-    // in-kernel RoPE on a key tile whose copies the K group has waited for
-    auto rotate_k = [&](int tile) {
-      RopeTile<DT, 8> rk;
-      rk.fetch(p, 0, TK5, ptid, 64, [&](int r) { return meta[tile & 3].rpos[r]; });
-      k_sync();
-      rk.apply(sK + (tile & 1) * KT_BYTES, TK5 * 128, 0, ptid, 64);
     };
     if (k_role) {
       for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t, ptid, false);
@@ -371,11 +376,8 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       prefetch_start(3, ptid);
       cp_async_commit();
       cp_async_wait<0>();
-      if (ROPE) {   // in-kernel RoPE: the keys of the first two tiles at the positions their places in the list map to
-        for (int t = 0; t < 2 && t < n_tiles; ++t) rotate_k(t);
-      }
       fence_async_smem();
-      for (int t = 0; t < 2 && t < n_tiles; ++t) mbar_arrive(mbar_k0 + 8 * t);
+      for (int t = 0; t < 2 && t < n_tiles; ++t) mbar_arrive((ROPE ? mbar_kraw0 : mbar_k0) + 8 * t);
     } else {
       if (n_tiles > 0) gather_v(0);
       cp_async_commit();
@@ -392,17 +394,10 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         cp_async_commit();
         // the record of tile it + 3 (its block start arrived with the copies of the previous round)
         if (it + 3 < n_tiles) make_meta(it + 3, ptid, true);
-        if (ROPE && it + 2 < n_tiles) {
-          // in-kernel RoPE: the table pieces of K(it + 2) travel while its rows land; rotate once all pieces are in place
-          RopeTile<DT, 8> rk;
-          rk.fetch(p, 0, TK5, ptid, 64, [&](int r) { return meta[(it + 2) & 3].rpos[r]; });
-          cp_async_wait<0>();
-          k_sync();
-          rk.apply(sK + (it & 1) * KT_BYTES, TK5 * 128, 0, ptid, 64);
-        }
         cp_async_wait<0>();   // K(it + 2) has landed
         fence_async_smem();
-        if (it + 2 < n_tiles) mbar_arrive(mbar_k0 + 8 * (it & 1));   // K(it + 2) is in place
+        // K(it + 2) is in place (under in-kernel RoPE: has landed, for the softmax warps to rotate)
+        if (it + 2 < n_tiles) mbar_arrive((ROPE ? mbar_kraw0 : mbar_k0) + 8 * (it & 1));
       } else {
         // V(it), requested one round ago, is reported before anything else is waited for: PV(it) needs it as soon as
         // P(it) is written
@@ -473,6 +468,9 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
     const float cap = p.logit_softcap;
     float m_ref = -INFINITY, l_run = 0.f;
     __syncthreads();  // B0
+    if (ROPE) {
+      for (int t = 0; t < 2 && t < n_tiles; ++t) rotate_k_tile(t);
+    }
     for (int it = 0; it < n_tiles; ++it) {
       const MetaS& mt = metas[it & 7];
       const uint32_t ts = tmem + (it & 1) * 64 + lane_base;
@@ -553,6 +551,7 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       tc_fence_before();
       if (__any_sync(0xffffffffu, s_abort != 0)) break;   // warp-uniform: the TMEM accesses are warp-collective
       mbar_arrive(mbar_p0 + 8 * (it & 1));
+      if (ROPE && it + 2 < n_tiles) rotate_k_tile(it + 2);   // K(it + 2) landed while this tile was worked on
     }
     // ---- epilogue for this thread's row ----
     bool ok = n_tiles > 0;
