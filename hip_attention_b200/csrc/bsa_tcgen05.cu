@@ -294,6 +294,15 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   const char* kbase = (const char*)(p.k.cache ? p.k.cache : p.k.dense);
   const char* vbase = (const char*)(p.v.cache ? p.v.cache : p.v.dense);
   const bool dense_kv = p.k.cache == nullptr && p.v.cache == nullptr;
+  // paged K and V that share block table, sequence lengths and page size (what a serving pool hands over)
+  const bool paged_fast = p.k.cache != nullptr && p.v.cache != nullptr && p.k.block_table == p.v.block_table &&
+                          p.k.table_stride_b == p.v.table_stride_b && p.k.table_width == p.v.table_width &&
+                          p.k.table_is_i64 == p.v.table_is_i64 && p.k.cache_seq_lens == p.v.cache_seq_lens &&
+                          p.k.seq_lens_is_i64 == p.v.seq_lens_is_i64 && p.k.page_size == p.v.page_size && p.k.page_size > 0;
+  const int page_shift = (paged_fast && (p.k.page_size & (p.k.page_size - 1)) == 0) ? 31 - __clz(p.k.page_size) : -1;
+  long long seq_len = 0;
+  if (paged_fast)
+    seq_len = p.k.seq_lens_is_i64 ? ((const int64_t*)p.k.cache_seq_lens)[b] : (long long)((const int32_t*)p.k.cache_seq_lens)[b];
   const long long k_base_off = ((long long)b * p.k.stride_b + (long long)hkv * p.k.stride_h) * 2, k_step = p.k.stride_t * 2;
   const long long v_base_off = ((long long)b * p.v.stride_b + (long long)hkv * p.v.stride_h) * 2, v_step = p.v.stride_t * 2;
   // requests the block start of entry e of `tile` (if it is a selected entry) into the tile's record; the copy joins
@@ -318,6 +327,22 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       if (dense_kv) {   // dense tensors: one multiply-add per tensor on top of the CTA's own base
         ko = k_base_off + (long long)t * k_step;
         vo = v_base_off + (long long)t * v_step;
+      } else if (paged_fast) {
+        // paged K and V behind one block table: one look-up in 32-bit arithmetic (token_row's rules: a position beyond
+        // the sequence or the table reads page 0; a page id outside the pool is reported and reads page 0)
+        const int pi = page_shift >= 0 ? (t >> page_shift) : (t / p.k.page_size);
+        const int off = t - pi * p.k.page_size;
+        long long page = 0;
+        if (t < seq_len && pi < p.k.table_width) {
+          const int64_t o = (int64_t)b * p.k.table_stride_b + pi;
+          page = p.k.table_is_i64 ? ((const int64_t*)p.k.block_table)[o] : (long long)((const int32_t*)p.k.block_table)[o];
+          if (page < 0 || page >= p.k.n_pages || page >= p.v.n_pages) {
+            atomicOr(p.status, HIPATTN_STATUS_PAGE_RANGE);
+            page = 0;
+          }
+        }
+        ko = (page * p.k.stride_page + (long long)off * p.k.stride_off + (long long)hkv * p.k.stride_ch) * 2;
+        vo = (page * p.v.stride_page + (long long)off * p.v.stride_off + (long long)hkv * p.v.stride_ch) * 2;
       } else {
         ko = token_row(p.k, b, t, hkv, 2, p.status) - kbase;
         vo = token_row(p.v, b, t, hkv, 2, p.status) - vbase;

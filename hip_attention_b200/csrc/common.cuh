@@ -109,7 +109,17 @@ __device__ __forceinline__ const char* token_row(const hipattn_tokens_t& tk, int
   }
   int64_t seq = tk.seq_lens_is_i64 ? ((const int64_t*)tk.cache_seq_lens)[b] : (int64_t)((const int32_t*)tk.cache_seq_lens)[b];
   int64_t page = 0;
-  int64_t pi = t / tk.page_size;
+  // page index and offset in 32-bit arithmetic (positions are below 2^31), by a shift when the page size is a power of
+  // two: a 64-bit division costs about a hundred instructions, and this sits in the decode kernels' row loops
+  const int ti = (int)t, ps = tk.page_size;
+  int pi, poff;
+  if ((ps & (ps - 1)) == 0) {
+    pi = ti >> (31 - __clz(ps));
+    poff = ti & (ps - 1);
+  } else {
+    pi = ti / ps;
+    poff = ti - pi * ps;
+  }
   if (t >= 0 && t < seq && pi < tk.table_width) {
     int64_t o = (int64_t)b * tk.table_stride_b + pi;
     page = tk.table_is_i64 ? ((const int64_t*)tk.block_table)[o] : (int64_t)((const int32_t*)tk.block_table)[o];
@@ -118,7 +128,7 @@ __device__ __forceinline__ const char* token_row(const hipattn_tokens_t& tk, int
       page = 0;
     }
   }
-  int64_t off = page * tk.stride_page + (t % tk.page_size) * tk.stride_off + (int64_t)hkv * tk.stride_ch;
+  int64_t off = page * tk.stride_page + (int64_t)poff * tk.stride_off + (int64_t)hkv * tk.stride_ch;
   return (const char*)tk.cache + off * elem_bytes;
 }
 
@@ -129,7 +139,7 @@ __device__ __forceinline__ void mark_access(int32_t* counter, int64_t stride_b, 
   int64_t i = t;
   if (tk.cache != nullptr) {
     const int64_t seq = tk.seq_lens_is_i64 ? ((const int64_t*)tk.cache_seq_lens)[b] : (int64_t)((const int32_t*)tk.cache_seq_lens)[b];
-    const int64_t pi = t / tk.page_size;
+    const int64_t pi = (int)t / tk.page_size;
     i = 0;
     if (t >= 0 && t < seq && pi < tk.table_width) {
       const int64_t o = (int64_t)b * tk.table_stride_b + pi;
