@@ -1,7 +1,7 @@
 // Block-sparse attention, prefill, 16-bit types, head dim 128: warp-specialised tcgen05 / TMEM kernel.
 //
-// One CTA (8 warps: four softmax, one MMA issuer, three copy warps) owns 128 query rows -- two heads of a KV group x 64 rows, or one head x 128
-// rows -- and walks the key list [sink | selected blocks | window] in tiles of 64 keys.  Two CTAs
+// One CTA (8 warps: four softmax, one MMA issuer, three copy warps) owns 128 query rows -- two heads
+// of a KV group x 64 rows, or one head x 128 rows -- and walks the key list [sink | selected blocks | window] in tiles of 64 keys.  Two CTAs
 // are resident per SM, so one CTA's softmax overlaps the other's tensor-core work.
 //
 //   S = Q K^T   tcgen05.mma (M 128, N 64, K 16) x 8, operands in shared memory (128-byte-swizzled
@@ -148,15 +148,15 @@ struct RopeTile {
 
 
 // ---------------------------------------------------------------------------------------------------
-// Warp-specialised variant (7 warps): warps 0-3 run the softmax (thread = query row = TMEM lane),
-// warp 4 issues the MMAs, warps 5-6 resolve key addresses and gather K / V rows.
+// Roles (8 warps): warps 0-3 run the softmax (thread = query row = TMEM lane), warp 4 issues the MMAs, warps 5 and 7
+// resolve the tile records and gather the K rows, warp 6 gathers the V rows.
 //   TMEM: S buffers at columns [0, 64) and [64, 128) (S(it) in buffer it & 1), O at [128, 256).
 //   P(it) is written back over the first 32 columns of S(it)'s buffer as packed 16-bit pairs and is
 //   the A operand of O += P V straight from TMEM, so no shared memory is needed for P.
-//   S runs two tiles ahead of the softmax: at the per-tile barrier the issuer launches PV(it) and
-//   S(it + 2), so the tensor pipe computes S(it + 1) / S(it + 2) while the softmax of tile it / it + 1 runs.
+//   S runs two tiles ahead of the softmax: once P(it) is written and V(it) / K(it + 2) are in place the issuer launches
+//   PV(it) and S(it + 2), so the tensor pipe computes S(it + 1) / S(it + 2) while the softmax of tile it / it + 1 runs.
 //   K and V tiles are double buffered.
-// One CTA-wide barrier per tile; every mbarrier wait is bounded.
+// The roles meet on mbarriers only; every mbarrier wait is bounded.
 // ---------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
