@@ -403,7 +403,9 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
     HIPATTN_REQUIRE(((uintptr_t)p->rope_cos % 16) == 0 && ((uintptr_t)p->rope_sin % 16) == 0 && p->rope_stride % ra == 0 &&
                         p->rope_stride >= p->D / 2,
                     HIPATTN_ERR_INVALID, "scan stage: cos / sin rows must start on 16-byte boundaries and hold D / 2 columns");
-    if (p->rope_mode == HIPATTN_ROPE_RELATIVE && p->k_scaled_sides == 2) {
+    // the tensor-core scan takes "relative" with the two rotated copies and "streaming" with the plain copy
+    if ((p->rope_mode == HIPATTN_ROPE_RELATIVE && p->k_scaled_sides == 2) ||
+        (p->rope_mode == HIPATTN_ROPE_STREAMING && p->k_scaled_sides == 1)) {
       rc = scan_stage_tcgen05(*p, s, &handled);
       if (handled) return rc;
     }

@@ -46,8 +46,11 @@ constexpr uint32_t kScanSlack = 896;   // padding reserved in front of the tiles
 // Resident CTAs per multiprocessor the register allocation aims at: six with 16 or 32 pooled rows (80 registers; shared
 // memory holds six 37 KB CTAs; at 92 registers only five are resident and stages 0 and 1 of the 128k prefill take 8 %
 // longer), four with 64, three with 128 (shared memory).
-template <int DT, int D, int NR>
-__global__ void __launch_bounds__(128, NR <= 32 ? 6 : (NR <= 64 ? 4 : 3)) scan_stage_tcgen05_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int check) {
+// STREAM = in-kernel RoPE, backend "streaming": the prepared copy holds the keys as they are (head-major, neither scaled
+// nor rotated); every thread rotates the row it asked for to its chunk's index, scales it and sums its magnitude in the
+// operand tile, between the landing of the copies and the round's barrier.
+template <int DT, int D, int NR, bool STREAM>
+__global__ void __launch_bounds__(128, NR <= 32 ? (STREAM ? 5 : 6) : (NR <= 64 ? 4 : 3)) scan_stage_tcgen05_kernel(const hipattn_scan_params_t p, int nblk, int nblk_total, int check) {
   constexpr int ROWB = D * 2;                 // bytes per key / query row
   constexpr int PIECES = ROWB / 16;
   constexpr int KB = D / 64;                  // 128-byte K-blocks per row
@@ -155,7 +158,7 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 6 : (NR <= 64 ? 4 : 3)) scan_s
   // in-kernel RoPE, backend "relative": the prepared keys come in two copies (rotated to position 0 / 1 for the left /
   // right candidate), and a key's score depends on the side it is proposed for, so no score is carried over
   const bool roped = p.rope_mode != HIPATTN_ROPE_NONE;
-  const int side_rows = roped ? p.B * p.HKV * p.T : 0;
+  const int side_rows = (roped && !STREAM) ? p.B * p.HKV * p.T : 0;
   unsigned long long st_keys = 0, st_fb = 0, st_wrong = 0;
   float st_ratio = 0.f;
   uint32_t phase = 0;
@@ -257,7 +260,7 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 6 : (NR <= 64 ? 4 : 3)) scan_s
         if (p.access_counter) mark_access(p.access_counter, p.access_stride_b, p.access_stride_h, p.access_n, p.k, b, hkv, tk);
       }
       // the key's magnitude is needed only after the MMA: requested here, its latency hides behind the row copies
-      const float s_abs = idx >= 0 ? __ldg(p.key_abs + idx) : 0.f;
+      float s_abs = (!STREAM && idx >= 0) ? __ldg(p.key_abs + idx) : 0.f;
       // ---- gather this warp's 32 rows: 8 lanes per row, 128 contiguous bytes per row and instruction ----
       if (__any_sync(0xffffffffu, idx >= 0)) {   // a warp whose scores are all known (or inactive) copies nothing
       if (lane == 0) *(volatile unsigned char*)&sh.fetched[rr % 3] = 1;
@@ -275,6 +278,31 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 6 : (NR <= 64 ? 4 : 3)) scan_s
       }
       cp_async_commit();
       cp_async_wait<0>();
+      if (STREAM) {
+        // the 16 pieces of a row were copied by eight lanes: all of the warp's copies are visible after this point
+        __syncwarp();
+        if (idx >= 0) {
+          if constexpr (D == 128) {
+            const int r = warp * 32 + lane;
+            const uint32_t s2 = pack_scalar2<DT>(p.k_scale);
+#pragma unroll 2
+            for (int pp = 0; pp < 8; ++pp) {
+              const uint32_t a_lo = sK_u32 + sw128(r, pp), a_hi = a_lo + K_BLOCK_BYTES;
+              uint4 lo = lds128(a_lo), hi = lds128(a_hi);
+              rope_rotate_packed<DT>(lo, hi, rope_table_raw(p.rope_cos, p.rope_stride, p.rope_rows, c, pp),
+                                     rope_table_raw(p.rope_sin, p.rope_stride, p.rope_rows, c, pp));
+              uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                w[i] = mul2<DT>(w[i], s2);
+                s_abs += fabsf(lo_f32<DT>(w[i])) + fabsf(hi_f32<DT>(w[i]));
+              }
+              sts128(a_lo, make_uint4(w[0], w[1], w[2], w[3]));
+              sts128(a_hi, make_uint4(w[4], w[5], w[6], w[7]));
+            }
+          }
+        }
+      }
       fence_async_smem();
       tc_fence_before();
       // the barrier's result is one bit (any predicate non-zero): "somebody is still searching, or gave up"
@@ -388,7 +416,7 @@ __global__ void __launch_bounds__(128, NR <= 32 ? 6 : (NR <= 64 ? 4 : 3)) scan_s
   }
 }
 
-template <int DT, int D, int NR>
+template <int DT, int D, int NR, bool STREAM>
 int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
   const size_t smem = kScanSlack + (size_t)(D / 64) * (128 * 128 + NR * 128) + sizeof(ScanShared);
   const int BDST = cdiv(p.TQ, p.block_size_q);
@@ -397,7 +425,7 @@ int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
   const int nblk = scan_ctas_per_unit(units, nblk_total);
   const int64_t grid = units * nblk;
   HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
-  auto kern = scan_stage_tcgen05_kernel<DT, D, NR>;
+  auto kern = scan_stage_tcgen05_kernel<DT, D, NR, STREAM>;
   HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<(unsigned)grid, 128, smem, stream>>>(p, nblk, nblk_total, p.mode == HIPATTN_SCAN_CHECK ? 1 : 0);
   return check_launch("scan_stage_tcgen05_kernel");
@@ -406,10 +434,18 @@ int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
 template <int DT, int D>
 int dispatch_rows(const hipattn_scan_params_t& p, cudaStream_t stream) {
   const int R = p.block_size_q / p.stride_q;
-  if (R <= 16) return launch<DT, D, 16>(p, stream);
-  if (R <= 32) return launch<DT, D, 32>(p, stream);
-  if (R <= 64) return launch<DT, D, 64>(p, stream);
-  return launch<DT, D, 128>(p, stream);
+  if constexpr (D == 128) {
+    if (p.rope_mode == HIPATTN_ROPE_STREAMING) {
+      if (R <= 16) return launch<DT, D, 16, true>(p, stream);
+      if (R <= 32) return launch<DT, D, 32, true>(p, stream);
+      if (R <= 64) return launch<DT, D, 64, true>(p, stream);
+      return launch<DT, D, 128, true>(p, stream);
+    }
+  }
+  if (R <= 16) return launch<DT, D, 16, false>(p, stream);
+  if (R <= 32) return launch<DT, D, 32, false>(p, stream);
+  if (R <= 64) return launch<DT, D, 64, false>(p, stream);
+  return launch<DT, D, 128, false>(p, stream);
 }
 
 // Scaled copy of the keys and their absolute sums: 16 / 8 lanes per row of 256 / 128 bytes.
@@ -491,7 +527,10 @@ int scan_stage_tcgen05(const hipattn_scan_params_t& p, cudaStream_t stream, bool
   if (p.mode == HIPATTN_SCAN_STRICT || p.dtype == HIPATTN_F32 || rows <= 1 || (R % 16) != 0 || R > 128 || (p.D != 64 && p.D != 128)) return HIPATTN_OK;
   if (p.key_abs == nullptr || p.k_scaled == nullptr) return HIPATTN_OK;
   if ((int64_t)p.B * p.T * p.HKV * (p.rope_mode != HIPATTN_ROPE_NONE ? 2 : 1) >= 0x7fffffffLL) return HIPATTN_OK;
-  if (p.rope_mode != HIPATTN_ROPE_NONE && !(p.rope_mode == HIPATTN_ROPE_RELATIVE && p.k_scaled_sides == 2)) return HIPATTN_OK;
+  // in-kernel RoPE: "relative" with the two rotated copies, "streaming" (head dim 128) with the plain head-major copy
+  // (hipattn_scan_prepare_keys with k_scale = 1, k_scaled_sides = 1): the kernel rotates and scales in the operand tile
+  if (p.rope_mode == HIPATTN_ROPE_RELATIVE && p.k_scaled_sides != 2) return HIPATTN_OK;
+  if (p.rope_mode == HIPATTN_ROPE_STREAMING && !(p.k_scaled_sides == 1 && p.D == 128)) return HIPATTN_OK;
   const char* v = getenv("HIPATTN_SCAN_KERNEL");
   if (v && strcmp(v, "mma") == 0) return HIPATTN_OK;
   *handled = true;

@@ -265,8 +265,10 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
 
     # scaled keys and their magnitudes (error radius) for the tensor-core scan (16-bit prefill only), once per call.
     # With in-kernel RoPE the stages whose backend is "relative" get two copies (keys rotated to table position 0 / 1 for
-    # the left / right candidate); "streaming" stages rotate every key to its chunk's index and stay on the strict kernel.
-    key_abs = k_scaled = None
+    # the left / right candidate); "streaming" stages (a key is rotated to its chunk's index, which changes from stage to
+    # stage) get the keys as they are in a head-major copy, and the scan kernel rotates and scales them in its operand
+    # tile (head dim 128; other shapes stay on the strict kernel).
+    key_abs = k_scaled = key_abs_plain = k_plain = None
     rope_modes = [None] * len(stages)
     if rope is not None:
         rope_modes = [_ROPE_MODES[getattr(s_, "stage_extend_backend", None) or args.scan_extend_backend] for s_ in stages]
@@ -274,23 +276,31 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
     tensor_scan = (q.dtype != torch.float32 and D in (64, 128) and min(TQ, bq) > 1 and _scan_mode() != L.SCAN_STRICT
                    and all((bq // s_.stage_block_stride_q) % 16 == 0 for s_ in stages) and R_min >= 16 and n > 0)
     sides = 1
+    want_plain = False
     if tensor_scan and rope is not None:
         sides = 2
+        want_plain = D == 128 and L.ROPE_STREAMING in rope_modes[first:] and B * T * HKV < 2 ** 31 - 1
         tensor_scan = L.ROPE_RELATIVE in rope_modes[first:] and 2 * B * T * HKV < 2 ** 31 - 1
-    if tensor_scan:
+    if tensor_scan or want_plain:
         if timer: timer.mark("start")
-        key_abs = torch.empty((sides, B, HKV, T), dtype=torch.float32, device=dev)
-        if sides * B * T * HKV < 2 ** 31 - 1:
-            k_scaled = torch.empty((sides, B, HKV, T, D), dtype=q.dtype, device=dev)
-        if rope is None:
-            L.check(lib.hipattn_scan_prepare_keys(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, _ptr(key_abs),
-                                                  _ptr(k_scaled), status.data_ptr(), st), "scan_prepare_keys")
-        else:
-            for side in range(2):
-                L.check(lib.hipattn_scan_prepare_keys_rope(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, rope[0].data_ptr(),
-                                                           rope[1].data_ptr(), rope[0].stride(0), rope[0].shape[0], side,
-                                                           key_abs[side].data_ptr(), k_scaled[side].data_ptr(), status.data_ptr(), st),
-                        "scan_prepare_keys_rope")
+        if tensor_scan:
+            key_abs = torch.empty((sides, B, HKV, T), dtype=torch.float32, device=dev)
+            if sides * B * T * HKV < 2 ** 31 - 1:
+                k_scaled = torch.empty((sides, B, HKV, T, D), dtype=q.dtype, device=dev)
+            if rope is None:
+                L.check(lib.hipattn_scan_prepare_keys(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, _ptr(key_abs),
+                                                      _ptr(k_scaled), status.data_ptr(), st), "scan_prepare_keys")
+            else:
+                for side in range(2):
+                    L.check(lib.hipattn_scan_prepare_keys_rope(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, rope[0].data_ptr(),
+                                                               rope[1].data_ptr(), rope[0].stride(0), rope[0].shape[0], side,
+                                                               key_abs[side].data_ptr(), k_scaled[side].data_ptr(), status.data_ptr(), st),
+                            "scan_prepare_keys_rope")
+        if want_plain:   # scale 1: the copy holds the keys' own values
+            key_abs_plain = torch.empty((B, HKV, T), dtype=torch.float32, device=dev)
+            k_plain = torch.empty((B, HKV, T, D), dtype=q.dtype, device=dev)
+            L.check(lib.hipattn_scan_prepare_keys(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, 1.0, _ptr(key_abs_plain),
+                                                  _ptr(k_plain), status.data_ptr(), st), "scan_prepare_keys")
         if timer: timer.mark("prep")
 
     block_chunk = args.block_size_k
@@ -322,6 +332,10 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
             sp.key_abs = _ptr(key_abs)
             sp.k_scaled = _ptr(k_scaled)
             sp.k_scaled_sides = sides if k_scaled is not None else 0
+        elif k_plain is not None:   # streaming: the plain copy, rotated and scaled inside the scan kernel
+            sp.key_abs = _ptr(key_abs_plain)
+            sp.k_scaled = _ptr(k_plain)
+            sp.k_scaled_sides = 1
         sp.dtype, sp.D, sp.B, sp.TQ, sp.H, sp.HKV, sp.T = _DT[q.dtype], D, B, TQ, H, HKV, T
         sp.block_size_q, sp.stride_q = bq, s_i.stage_block_stride_q
         sp.n_chunks, sp.block_chunk, sp.scan_window = n, block_chunk, scan_window

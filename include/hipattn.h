@@ -132,7 +132,9 @@ typedef struct hipattn_scan_params {
   int32_t k_scaled_sides;    /* 0 / 1: one prepared copy.  2 (rope_mode RELATIVE only): k_scaled and key_abs hold two
                                 consecutive copies, the keys rotated to table position 0 (left candidates) and 1 (right
                                 candidates), written by hipattn_scan_prepare_keys_rope: the tensor-core scan then runs
-                                with in-kernel RoPE */
+                                with in-kernel RoPE.  1 with rope_mode STREAMING (head dim 128): k_scaled holds the keys
+                                as they are (hipattn_scan_prepare_keys with k_scale = 1); the tensor-core scan rotates
+                                every key it fetches to its chunk's index and applies k_scale itself */
 } hipattn_scan_params_t;
 
 int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream);

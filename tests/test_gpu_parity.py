@@ -69,7 +69,7 @@ def test_matches_oracle_all_dtypes(name, dtype):
 
 
 @pytest.mark.parametrize("name", ["prefill_fp32", "ragged_fp16", "oddsink_fp16", "shortwin_fp16", "rope_rel_fp16",
-                                  "rope_mixed_fp32"])
+                                  "rope_mixed_fp32", "rope_d128_fp16", "rope_d128_str_fp16"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_scan_stage_outputs(name, dtype):
     """Per-head narrowed bounds and scores of every scan stage equal the oracle's, bit for bit."""
@@ -395,14 +395,20 @@ def test_bad_page_table_is_clamped_and_flagged():
     assert torch.isfinite(out.float()).all()
 
 
-def _scan_check_run(dtype, TQ=512, T=16384):
+def _scan_check_run(dtype, TQ=512, T=16384, rope_backend=None):
     """Run the estimator in check mode on a bench-shaped problem; returns (stats, indices)."""
     import bench
     from hip_attention_b200 import hip_attention_impl
     w = dict(bench.WORKLOADS["prefill_128k"], TQ=TQ, T=T, keep=[4096, 2048, 1024],
              dtype={torch.bfloat16: "bf16", torch.float16: "fp16"}[dtype])
     q, k, v = bench.make_qkv(w, "cuda")
-    args = bench.make_args(w)
+    kw = {}
+    if rope_backend is not None:
+        from cases import rope_tables
+        cos, sin = rope_tables(T + 8, w["D"], w["theta"])
+        kw = dict(using_extend=True, need_apply_rope=True, rope_cos=torch.from_numpy(cos).cuda(), rope_sin=torch.from_numpy(sin).cuda(),
+                  scan_extend_backend=rope_backend)
+    args = bench.make_args(w, **kw)
     stats = torch.zeros(4, dtype=torch.int64, device="cuda")
     out, md = hip_attention_impl(q, k, v, args, debug={"scan_stats": stats})
     torch.cuda.synchronize()
@@ -433,6 +439,29 @@ def test_scan_tensor_core_path_is_exact(dtype, scan_kernel, monkeypatch):
     assert torch.equal(md_auto.indices, md_strict.indices) and torch.equal(md_auto.ks, md_strict.ks)
     assert torch.equal(md_check.indices, md_strict.indices)
     print(f"scan check {scan_kernel} {dtype}: keys {keys} fallbacks {fallbacks} ({100 * fallbacks / keys:.2f} %) max ratio {ratio:.4f}")
+
+
+@pytest.mark.parametrize("backend", ["relative", "streaming"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scan_tensor_core_path_is_exact_with_rope(dtype, backend, monkeypatch):
+    """The same with in-kernel RoPE: "relative" (two rotated key copies) and "streaming" (keys rotated and scaled inside
+    the operand tile, their magnitudes summed there) on the tcgen05 scan against the strict kernel."""
+    import numpy as np
+    monkeypatch.setenv("HIPATTN_SCAN_MODE", "check")
+    stats, md_check, _ = _scan_check_run(dtype, rope_backend=backend)
+    keys, fallbacks, wrong = int(stats[0]), int(stats[1]), int(stats[2])
+    ratio = float(np.array([int(stats[3]) & 0xffffffff], dtype=np.uint32).view(np.float32)[0])
+    assert keys > 800_000
+    assert wrong == 0, f"{wrong} shortcuts disagree with the strict score"
+    assert ratio < 0.5, f"deviation reached {ratio:.3f} of the assumed radius"
+    assert fallbacks / keys < 0.25
+    monkeypatch.setenv("HIPATTN_SCAN_MODE", "strict")
+    _, md_strict, _ = _scan_check_run(dtype, rope_backend=backend)
+    monkeypatch.setenv("HIPATTN_SCAN_MODE", "auto")
+    _, md_auto, _ = _scan_check_run(dtype, rope_backend=backend)
+    assert torch.equal(md_auto.indices, md_strict.indices) and torch.equal(md_auto.ks, md_strict.ks)
+    assert torch.equal(md_check.indices, md_strict.indices)
+    print(f"scan check rope {backend} {dtype}: keys {keys} fallbacks {fallbacks} ({100 * fallbacks / keys:.2f} %) max ratio {ratio:.4f}")
 
 
 @pytest.mark.parametrize("shape", [
