@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(128, NR <= 32 ? (STREAM ? 5 : 6) : (NR <= 64 ?
       const int mid = (left + right) >> 1;
       int tk = side ? ((mid + right) >> 1) : ((left + mid) >> 1);
       const int tk_asked = tk;
-      const bool known = act && !roped && tk == won_t;
+      const bool known = act && (!roped || STREAM) && tk == won_t;   // (streaming: a chunk's keys keep their rotation from round to round)
       int idx = -1;
       if (act && !known) {
         if (tk < 0 || tk >= p.T) {
