@@ -66,7 +66,9 @@ __device__ __forceinline__ float mac_s(float q, float k, float acc) {
   return fmaf(q, k, acc);                                         // 16-bit inputs: the product is exact
 }
 
-template <int DT, int D, int HB>
+// ROPE_S = in-kernel RoPE, backend "streaming": every token of a chunk is rotated to the chunk's index before the key
+// scale (a token's score then does not depend on the side it is proposed for, so one score per token serves the search)
+template <int DT, int D, int HB, bool ROPE_S>
 __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_scan_params_t p, int c_log2, int n_split, int passes_total) {
   constexpr int EB = Elem<DT>::bytes;
   constexpr int ROWB = D * EB;
@@ -207,7 +209,8 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
 #pragma unroll 2
       for (int pc = 0; pc < PIECES; ++pc) {
         float kv[VEC];
-        unpack_scaled_s<DT>(*reinterpret_cast<const uint4*>(my_row + pc * 16), p.k_scale, kv);
+        if (ROPE_S) unpack_rope_scaled<DT, D>(my_row, pc, c, p, kv);
+        else unpack_scaled_s<DT>(*reinterpret_cast<const uint4*>(my_row + pc * 16), p.k_scale, kv);
 #pragma unroll
         for (int hh = 0; hh < HB; ++hh) {
 #pragma unroll
@@ -262,7 +265,7 @@ __global__ void __launch_bounds__(128) scan_chunks_strict_kernel(const hipattn_s
   }
 }
 
-template <int DT, int D, int HB>
+template <int DT, int D, int HB, bool ROPE_S>
 int launch(const hipattn_scan_params_t& p, int c_log2, cudaStream_t stream) {
   constexpr int EB = Elem<DT>::bytes;
   const size_t smem = (size_t)HB * D * sizeof(float) + (size_t)4 * 32 * (D * EB + kPadS);
@@ -278,7 +281,7 @@ int launch(const hipattn_scan_params_t& p, int c_log2, cudaStream_t stream) {
   if (n_split < 1) n_split = 1;
   const int64_t grid = units * n_split;
   HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
-  auto kern = scan_chunks_strict_kernel<DT, D, HB>;
+  auto kern = scan_chunks_strict_kernel<DT, D, HB, ROPE_S>;
   HIPATTN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<(unsigned)grid, 128, smem, stream>>>(p, c_log2, n_split, passes_total);
   return check_launch("scan_chunks_strict_kernel");
@@ -286,10 +289,17 @@ int launch(const hipattn_scan_params_t& p, int c_log2, cudaStream_t stream) {
 
 template <int DT, int D>
 int dispatch_heads(const hipattn_scan_params_t& p, int c_log2, int HB, cudaStream_t stream) {
+  if (p.rope_mode == HIPATTN_ROPE_STREAMING) {
+    switch (HB) {
+      case 4: return launch<DT, D, 4, true>(p, c_log2, stream);
+      case 2: return launch<DT, D, 2, true>(p, c_log2, stream);
+      default: return launch<DT, D, 1, true>(p, c_log2, stream);
+    }
+  }
   switch (HB) {
-    case 4: return launch<DT, D, 4>(p, c_log2, stream);
-    case 2: return launch<DT, D, 2>(p, c_log2, stream);
-    default: return launch<DT, D, 1>(p, c_log2, stream);
+    case 4: return launch<DT, D, 4, false>(p, c_log2, stream);
+    case 2: return launch<DT, D, 2, false>(p, c_log2, stream);
+    default: return launch<DT, D, 1, false>(p, c_log2, stream);
   }
 }
 
@@ -313,6 +323,8 @@ int scan_chunks_strict(const hipattn_scan_params_t& p, cudaStream_t stream, bool
   const int rows = min(R, cdiv(p.TQ, p.stride_q));
   if (rows > 1 || (p.D != 64 && p.D != 128 && p.D != 256)) return HIPATTN_OK;
   if (p.k.fp8_e5m2) return HIPATTN_OK;   // an fp8 cache goes through the round-by-round kernel
+  // in-kernel RoPE: "streaming" rotates a chunk's tokens alike; "relative" scores a token by the side it is proposed for
+  if (p.rope_mode != HIPATTN_ROPE_NONE && p.rope_mode != HIPATTN_ROPE_STREAMING) return HIPATTN_OK;
   const int C = p.chunk_size;
   if (C < 4 || C > 32 || (C & (C - 1)) != 0) return HIPATTN_OK;
   const char* v = getenv("HIPATTN_DECODE_SCAN");

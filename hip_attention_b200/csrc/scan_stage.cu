@@ -66,45 +66,6 @@ __device__ __forceinline__ void unpack_scaled<HIPATTN_F16>(const uint4& w, float
   }
 }
 
-// the same for a staged key row that is first rotated to table position `new_t` (in-kernel RoPE,
-// attention_extend.py:248-407): piece `pc` of the row at `row`, its partner half a row away, cos / sin of new_t
-template <int DT, int D>
-__device__ __forceinline__ void unpack_rope_scaled(const unsigned char* row, int pc, int new_t, const hipattn_scan_params_t& p,
-                                                   float* out) {
-  constexpr int VEC = 16 / Elem<DT>::bytes;
-  constexpr int PIECES = D / VEC, HALF = PIECES / 2;
-  if constexpr (DT != HIPATTN_F32) {
-    // 16-bit types: rotation and key scale on packed pairs (the packed multiply and add round once to the element type,
-    // which is what the scalar path does product by product: see rope_rotate_packed)
-    using P = typename Pair16<DT>::type;
-    const uint4 x = *reinterpret_cast<const uint4*>(row + pc * 16);
-    const uint4 xr = *reinterpret_cast<const uint4*>(row + (pc < HALF ? pc + HALF : pc - HALF) * 16);
-    const uint4 c = rope_table_raw(p.rope_cos, p.rope_stride, p.rope_rows, new_t, pc % HALF);
-    const uint4 sn = rope_table_raw(p.rope_sin, p.rope_stride, p.rope_rows, new_t, pc % HALF);
-    const uint32_t xv[4] = {x.x, x.y, x.z, x.w}, rv[4] = {xr.x, xr.y, xr.z, xr.w};
-    const uint32_t cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
-    const uint32_t s2 = pack_scalar2<DT>(p.k_scale);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const P xp = *reinterpret_cast<const P*>(&xv[i]), rp = *reinterpret_cast<const P*>(&rv[i]);
-      const P cp = *reinterpret_cast<const P*>(&cv[i]), sp = *reinterpret_cast<const P*>(&sv[i]);
-      const P rot = __hadd2_rn(__hmul2_rn(xp, cp), __hmul2_rn(pc < HALF ? __hneg2(rp) : rp, sp));
-      const uint32_t m = mul2<DT>(*reinterpret_cast<const uint32_t*>(&rot), s2);
-      out[2 * i] = lo_f32<DT>(m);
-      out[2 * i + 1] = hi_f32<DT>(m);
-    }
-  } else {
-    float xr[VEC], tc[VEC], ts[VEC];
-    widen_piece<DT>(*reinterpret_cast<const uint4*>(row + pc * 16), out);
-    widen_piece<DT>(*reinterpret_cast<const uint4*>(row + (pc < HALF ? pc + HALF : pc - HALF) * 16), xr);
-    rope_table_piece<DT>(p.rope_cos, p.rope_stride, p.rope_rows, new_t, pc % HALF, tc);
-    rope_table_piece<DT>(p.rope_sin, p.rope_stride, p.rope_rows, new_t, pc % HALF, ts);
-    rope_rotate_piece<DT, VEC>(out, xr, tc, ts, pc < HALF);
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) out[e] = Elem<DT>::round(__fmul_rn(out[e], p.k_scale));
-  }
-}
-
 template <int DT>
 __device__ __forceinline__ float mac(float q, float k, float acc) {
   if (DT == HIPATTN_F32) return __fadd_rn(acc, __fmul_rn(q, k));  // two roundings, reproducible on a CPU
@@ -403,6 +364,10 @@ extern "C" int hipattn_scan_stage(const hipattn_scan_params_t* p, void* stream) 
     HIPATTN_REQUIRE(((uintptr_t)p->rope_cos % 16) == 0 && ((uintptr_t)p->rope_sin % 16) == 0 && p->rope_stride % ra == 0 &&
                         p->rope_stride >= p->D / 2,
                     HIPATTN_ERR_INVALID, "scan stage: cos / sin rows must start on 16-byte boundaries and hold D / 2 columns");
+    if (p->rope_mode == HIPATTN_ROPE_STREAMING) {   // decode: every token of a chunk is rotated to the chunk's index
+      rc = scan_chunks_strict(*p, s, &handled);
+      if (handled) return rc;
+    }
     // the tensor-core scan takes "relative" with the two rotated copies and "streaming" with the plain copy
     if ((p->rope_mode == HIPATTN_ROPE_RELATIVE && p->k_scaled_sides == 2) ||
         (p->rope_mode == HIPATTN_ROPE_STREAMING && p->k_scaled_sides == 1)) {

@@ -546,11 +546,13 @@ def test_prefill_head_dim_128_matches_oracle(kernel, bq, tq, hkv, dtype, monkeyp
     dict(B=2, H=4, HKV=2, D=64, T=4096, keep=[2048, 1024, 512]),           # two heads per KV head: only chunk 8 qualifies
     dict(B=2, H=3, HKV=3, D=128, T=5000, keep=[4096, 1024, 512]),          # one head per KV head, ragged last chunk
 ])
-def test_decode_scan_whole_chunks_equals_rounds(shape, dtype, monkeypatch):
+@pytest.mark.parametrize("rope", [False, True])
+def test_decode_scan_whole_chunks_equals_rounds(shape, dtype, rope, monkeypatch):
     """Decode: scoring whole small chunks once per KV head and replaying the search gives the per-head bounds
-    and scores of the round-by-round strict kernel at every stage, dense and paged."""
+    and scores of the round-by-round strict kernel at every stage, dense and paged; also with in-kernel RoPE, scan
+    backend "streaming" (every token of a chunk rotated to the chunk's index)."""
     import bench
-    from cases import make_paged
+    from cases import make_paged, rope_tables
     from hip_attention_b200 import hip_attention_impl, read_status
     w = dict(bench.WORKLOADS["decode_128k"], keep=[4096, 2048, 1024], **{k_: v_ for k_, v_ in shape.items() if k_ != "keep"})
     if "keep" in shape:
@@ -558,12 +560,17 @@ def test_decode_scan_whole_chunks_equals_rounds(shape, dtype, monkeypatch):
     w["dtype"] = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}[dtype]
     w["kind"] = "prefill"          # dense q / k / v tensors from the generator
     q, k, v = bench.make_qkv(w, "cuda")
+    kw = {}
+    if rope:
+        cos, sin = rope_tables(w["T"] + 8, w["D"], w["theta"])
+        kw = dict(using_extend=True, need_apply_rope=True, rope_cos=torch.from_numpy(cos).cuda(), rope_sin=torch.from_numpy(sin).cuda(),
+                  scan_extend_backend="streaming")
     results = {}
     for name in ("chunks", "rounds"):
         monkeypatch.setenv("HIPATTN_DECODE_SCAN", name)
         dbg = {}
         read_status("cuda")
-        out, md = hip_attention_impl(q, k, v, bench.make_args(w), debug=dbg)
+        out, md = hip_attention_impl(q, k, v, bench.make_args(w, **kw), debug=dbg)
         torch.cuda.synchronize()
         assert read_status("cuda") == 0
         results[name] = (dbg["stages"], md, out)
@@ -577,7 +584,7 @@ def test_decode_scan_whole_chunks_equals_rounds(shape, dtype, monkeypatch):
         kc, vc, table = make_paged(k.cpu(), v.cpu(), 16, 11)
         args = bench.make_args(w, k_cache=kc.cuda(), v_cache=vc.cuda(), block_table=table.cuda().to(torch.int32),
                                cache_seq_lens=torch.full((w["B"],), w["T"], dtype=torch.int32, device="cuda"),
-                               extend_context_length=w["T"])
+                               extend_context_length=w["T"], **kw)
         out_p, md_p = hip_attention_impl(q, None, None, args)
         assert torch.equal(md_p.indices, results["rounds"][1].indices)
         assert torch.equal(out_p, results["rounds"][2])
