@@ -406,8 +406,9 @@ extern "C" int hipattn_scan_prepare_keys_rope(const hipattn_tokens_t* k, int32_t
                                               void* stream) {
   using namespace hipattn;
   HIPATTN_REQUIRE(k && status && key_abs && k_scaled && rope_cos && rope_sin, HIPATTN_ERR_INVALID, "scan_prepare_keys_rope: null pointer");
-  HIPATTN_REQUIRE(B > 0 && T > 0 && HKV > 0 && rope_rows > 0 && position >= 0 && position < rope_rows, HIPATTN_ERR_INVALID,
-                  "scan_prepare_keys_rope: bad shape or position");
+  HIPATTN_REQUIRE(B > 0 && T > 0 && HKV > 0 && rope_rows > 0 && position >= -1 && position < rope_rows &&
+                      (position >= 0 || rope_rows >= 2),
+                  HIPATTN_ERR_INVALID, "scan_prepare_keys_rope: bad shape or position");
   HIPATTN_REQUIRE(((uintptr_t)k_scaled % 16) == 0 && ((uintptr_t)rope_cos % 16) == 0 && ((uintptr_t)rope_sin % 16) == 0 &&
                       rope_stride % 8 == 0 && rope_stride >= D / 2,
                   HIPATTN_ERR_INVALID, "scan_prepare_keys_rope: k_scaled and the cos / sin rows must be 16-byte aligned");

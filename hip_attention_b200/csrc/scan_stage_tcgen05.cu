@@ -471,31 +471,49 @@ __global__ void scan_prepare_keys_kernel(const hipattn_tokens_t k, int D, int B,
     const char* src = token_row(k, b, t, hkv, 2, status);
     const uint4 w = k.fp8_e5m2 ? widen_fp8_e5m2<DT>(*reinterpret_cast<const uint2*>(src + piece * 8))
                                : *reinterpret_cast<const uint4*>(src + piece * 16);
-    uint32_t v[4] = {w.x, w.y, w.z, w.w};
+    const int64_t ro = ((int64_t)b * HKV + hkv) * T + t;     // head-major: the tokens of a KV head are contiguous
+    // scales a piece, sums its magnitude over the row and stores both into copy `side`
+    auto emit = [&](uint32_t* v, int side) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[i] = mul2<DT>(v[i], kscale2);
+        const uint32_t m = v[i] & 0x7fff7fffu;
+        s += lo_f32<DT>(m) + hi_f32<DT>(m);
+      }
+      const int64_t rs = ro + (int64_t)side * total;
+      if (k_scaled) *reinterpret_cast<uint4*>(k_scaled + rs * (int64_t)(D * 2) + piece * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+      for (int o = pieces >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (piece == 0 && key_abs) key_abs[rs] = s;
+    };
     if (rope.cos != nullptr) {
       const int half = pieces >> 1, pr = piece < half ? piece + half : piece - half;
       const uint4 wr = k.fp8_e5m2 ? widen_fp8_e5m2<DT>(*reinterpret_cast<const uint2*>(src + pr * 8))
                                   : *reinterpret_cast<const uint4*>(src + pr * 16);
-      float x[8], xr[8], tc[8], ts[8];
-      widen_piece<DT>(w, x);
-      widen_piece<DT>(wr, xr);
-      rope_table_piece<DT>(rope.cos, rope.stride, rope.rows, rope.position, piece % half, tc);
-      rope_table_piece<DT>(rope.sin, rope.stride, rope.rows, rope.position, piece % half, ts);
-      rope_rotate_piece<DT, 8>(x, xr, tc, ts, piece < half);
+      // rotation on packed 16-bit pairs: products and sum round once to the element type, as the scalar form does
+      using P = typename Pair16<DT>::type;
+      const uint32_t xv[4] = {w.x, w.y, w.z, w.w}, rv[4] = {wr.x, wr.y, wr.z, wr.w};
+      // position -1: both copies of the "relative" backend (table positions 0 and 1) from one read of the row
+      const int n_pos = rope.position < 0 ? 2 : 1;
+      for (int sd = 0; sd < n_pos; ++sd) {
+        const int pos = rope.position < 0 ? sd : rope.position;
+        const uint4 tc = rope_table_raw(rope.cos, rope.stride, rope.rows, pos, piece % half);
+        const uint4 ts = rope_table_raw(rope.sin, rope.stride, rope.rows, pos, piece % half);
+        const uint32_t cv[4] = {tc.x, tc.y, tc.z, tc.w}, sv[4] = {ts.x, ts.y, ts.z, ts.w};
+        uint32_t v[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = pack2<DT>(x[2 * i], x[2 * i + 1]);
+        for (int i = 0; i < 4; ++i) {
+          const P xp = *reinterpret_cast<const P*>(&xv[i]), rp = *reinterpret_cast<const P*>(&rv[i]);
+          const P cp = *reinterpret_cast<const P*>(&cv[i]), sp = *reinterpret_cast<const P*>(&sv[i]);
+          const P rot = __hadd2_rn(__hmul2_rn(xp, cp), __hmul2_rn(piece < half ? __hneg2(rp) : rp, sp));
+          v[i] = *reinterpret_cast<const uint32_t*>(&rot);
+        }
+        emit(v, sd);
+      }
+    } else {
+      uint32_t v[4] = {w.x, w.y, w.z, w.w};
+      emit(v, 0);
     }
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[i] = mul2<DT>(v[i], kscale2);
-      const uint32_t m = v[i] & 0x7fff7fffu;
-      s += lo_f32<DT>(m) + hi_f32<DT>(m);
-    }
-    const int64_t ro = ((int64_t)b * HKV + hkv) * T + t;     // head-major: the tokens of a KV head are contiguous
-    if (k_scaled) *reinterpret_cast<uint4*>(k_scaled + ro * (int64_t)(D * 2) + piece * 16) = make_uint4(v[0], v[1], v[2], v[3]);
-    for (int o = pieces >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (piece == 0 && key_abs) key_abs[ro] = s;
   }
 }
 

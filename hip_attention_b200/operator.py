@@ -291,11 +291,11 @@ def _estimate_mask(q: Tensor, ktok: L.Tokens, T: int, HKV: int, pos: Tensor, arg
                 L.check(lib.hipattn_scan_prepare_keys(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, _ptr(key_abs),
                                                       _ptr(k_scaled), status.data_ptr(), st), "scan_prepare_keys")
             else:
-                for side in range(2):
-                    L.check(lib.hipattn_scan_prepare_keys_rope(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, rope[0].data_ptr(),
-                                                               rope[1].data_ptr(), rope[0].stride(0), rope[0].shape[0], side,
-                                                               key_abs[side].data_ptr(), k_scaled[side].data_ptr(), status.data_ptr(), st),
-                            "scan_prepare_keys_rope")
+                # position -1: both copies (table positions 0 and 1) from one read of the keys
+                L.check(lib.hipattn_scan_prepare_keys_rope(C.byref(ktok), _DT[q.dtype], D, B, T, HKV, k_scale, rope[0].data_ptr(),
+                                                           rope[1].data_ptr(), rope[0].stride(0), rope[0].shape[0], -1,
+                                                           _ptr(key_abs), _ptr(k_scaled), status.data_ptr(), st),
+                        "scan_prepare_keys_rope")
         if want_plain:   # scale 1: the copy holds the keys' own values
             key_abs_plain = torch.empty((B, HKV, T), dtype=torch.float32, device=dev)
             k_plain = torch.empty((B, HKV, T, D), dtype=q.dtype, device=dev)

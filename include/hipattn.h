@@ -160,7 +160,8 @@ int hipattn_scan_prepare_keys(const hipattn_tokens_t* k, int32_t dtype, int32_t 
  * As hipattn_scan_prepare_keys, for the scan's in-kernel RoPE with backend "relative": every key is first rotated to
  * the fixed table position `position` (x * cos + rotate_half(x) * sin in the element type, attention_extend.py:290-407),
  * then scaled.  Two calls (position 0 into the first copy, position 1 into the second, each copy [B, HKV, T, D] resp.
- * [B, HKV, T]) give what hipattn_scan_stage expects with k_scaled_sides = 2.
+ * [B, HKV, T]) give what hipattn_scan_stage expects with k_scaled_sides = 2; position = -1 writes both copies in one
+ * pass (k_scaled [2, B, HKV, T, D], key_abs [2, B, HKV, T]), reading every key once.
  */
 int hipattn_scan_prepare_keys_rope(const hipattn_tokens_t* k, int32_t dtype, int32_t D, int32_t B, int32_t T, int32_t HKV,
                                    float k_scale, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
