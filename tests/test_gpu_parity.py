@@ -683,3 +683,45 @@ def test_bounded_wait_times_out_and_reports():
     x = torch.ones(1024, device="cuda")
     assert float(x.sum()) == 1024.0
     assert read_status("cuda") == 0
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(H=8, HKV=2, bq=64, T=8192, TQ=300, sink=64, sw=1024, dt="bf16", rope=None),
+    dict(H=16, HKV=2, bq=128, T=12000, TQ=192, sink=256, sw=512, dt="fp16", rope="streaming"),
+    dict(H=8, HKV=1, bq=64, T=8192, TQ=64, sink=16, sw=1024, dt="bf16", rope="streaming"),
+    dict(H=4, HKV=4, bq=128, T=4096, TQ=100, sink=0, sw=1024, dt="fp16", rope="relative"),
+    dict(H=8, HKV=2, bq=64, T=4096, TQ=2048, sink=256, sw=128, dt="bf16", rope="relative"),
+    dict(H=16, HKV=2, bq=128, T=16384, TQ=192, sink=0, sw=128, dt="fp16", rope=None),
+    dict(H=8, HKV=2, bq=128, T=2048, TQ=512, sink=16, sw=1024, dt="bf16", rope=None),
+    dict(H=8, HKV=2, bq=64, T=2048, TQ=64, sink=16, sw=64, dt="fp16", rope=None),
+])
+def test_prefill_attention_kernels_agree_and_repeat(cfg, monkeypatch):
+    """The warp-specialised tcgen05 attention kernel against the mma.sync one on assorted shapes (one / two heads per
+    CTA, 64- and 128-row blocks, ragged blocks, sink-less, with and without in-kernel RoPE): outputs within two
+    element-type roundings, the status word clean, and every repeat of the call bit-identical (the kernel's roles meet
+    on mbarriers only; a missed hand-off would show as a difference between repeats)."""
+    import bench
+    from cases import rope_tables
+    from hip_attention_b200 import hip_attention_impl, read_status
+    T = cfg["T"]
+    w = dict(bench.WORKLOADS["prefill_128k"], TQ=cfg["TQ"], T=T, H=cfg["H"], HKV=cfg["HKV"], bq=cfg["bq"], sink=cfg["sink"],
+             sw=cfg["sw"], dtype=cfg["dt"], keep=[min(4096, T // 2), min(2048, T // 4), min(1024, T // 8)], seed=77,
+             strides=[4, 4, 1] if cfg["bq"] == 64 else [4, 4, 2])
+    q, k, v = bench.make_qkv(w, "cuda")
+    kw = {}
+    if cfg["rope"]:
+        cos, sin = rope_tables(T + 8, w["D"], w["theta"])
+        kw = dict(using_extend=True, need_apply_rope=True, rope_cos=torch.from_numpy(cos).cuda(), rope_sin=torch.from_numpy(sin).cuda(),
+                  scan_extend_backend=cfg["rope"])
+    args = bench.make_args(w, **kw)
+    monkeypatch.setenv("HIPATTN_PREFILL_KERNEL", "tcgen05")
+    read_status("cuda")
+    out, md = hip_attention_impl(q, k, v, args)
+    for _ in range(3):
+        again, _ = hip_attention_impl(q, k, v, args, md)
+        assert torch.equal(again, out)
+    assert read_status("cuda") == 0
+    monkeypatch.setenv("HIPATTN_PREFILL_KERNEL", "mma")
+    ref, _ = hip_attention_impl(q, k, v, args, md)
+    assert torch.isfinite(out.float()).all()
+    assert (out.float() - ref.float()).abs().max().item() <= (4e-2 if cfg["dt"] == "bf16" else 5e-3)
