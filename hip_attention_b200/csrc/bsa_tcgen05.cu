@@ -214,12 +214,13 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
   // in-kernel RoPE: K buffer 0 / 1 has landed, not yet rotated (64 key-copy threads); the softmax warps rotate it between
   // two of their tiles - they wait for S there anyway - and report the buffer ready (128 arrivals instead of 64)
   const uint32_t mbar_kraw0 = smem_u32(&s_mbar[10]);
-  // rotates K(tile) in place; called by the 128 softmax threads
+  // rotates rows 32-63 of K(tile) in place; called by the 128 softmax threads (rows 0-31 are rotated by the key-copy
+  // warps before they report the tile as landed: those warps idle for about as long as that takes)
   auto rotate_k_tile = [&](int tile) {
-    RopeTile<DT, 4> rk;
-    rk.fetch(p, 0, TK5, tid, 128, [&](int r) { return metas[tile & 7].rpos[r]; });
+    RopeTile<DT, 2> rk;
+    rk.fetch(p, 32, TK5, tid, 128, [&](int r) { return metas[tile & 7].rpos[r]; });
     mbar_wait(mbar_kraw0 + 8 * (tile & 1), (tile >> 1) & 1, &s_abort, p.status);
-    rk.apply(sK + (tile & 1) * KT_BYTES, TK5 * 128, 0, tid, 128);
+    rk.apply(sK + (tile & 1) * KT_BYTES, TK5 * 128, 32, tid, 128);
     fence_async_smem();
     mbar_arrive(mbar_k0 + 8 * (tile & 1));
   };
@@ -392,6 +393,14 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
                    : "=r"(r) : "r"((uint32_t)v) : "memory");
       return r != 0;
     };
+    // in-kernel RoPE: rows 0-31 of a key tile, by the 64 key-copy threads once all their copies have landed
+    auto rotate_k_front = [&](int tile) {
+      RopeTile<DT, 4> rk;
+      rk.fetch(p, 0, 32, ptid, 64, [&](int r) { return metas[tile & 7].rpos[r]; });
+      cp_async_wait<0>();
+      asm volatile("bar.sync 2, 64;\n" ::: "memory");
+      rk.apply(sK + (tile & 1) * KT_BYTES, TK5 * 128, 0, ptid, 64);
+    };
     if (k_role) {
       for (int t = 0; t < 3 && t < n_tiles; ++t) make_meta(t, ptid, false);
     }
@@ -401,6 +410,9 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
       prefetch_start(3, ptid);
       cp_async_commit();
       cp_async_wait<0>();
+      if (ROPE) {
+        for (int t = 0; t < 2 && t < n_tiles; ++t) rotate_k_front(t);
+      }
       fence_async_smem();
       for (int t = 0; t < 2 && t < n_tiles; ++t) mbar_arrive((ROPE ? mbar_kraw0 : mbar_k0) + 8 * t);
     } else {
@@ -419,6 +431,7 @@ __global__ void __launch_bounds__(256, 2) bsa_tcgen05_ws_kernel(const hipattn_bs
         cp_async_commit();
         // the record of tile it + 3 (its block start arrived with the copies of the previous round)
         if (it + 3 < n_tiles) make_meta(it + 3, ptid, true);
+        if (ROPE && it + 2 < n_tiles) rotate_k_front(it + 2);
         cp_async_wait<0>();   // K(it + 2) has landed
         fence_async_smem();
         // K(it + 2) is in place (under in-kernel RoPE: has landed, for the softmax warps to rotate)
