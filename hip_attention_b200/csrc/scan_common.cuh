@@ -174,9 +174,24 @@ __device__ __forceinline__ int chunk_rounds(const hipattn_scan_params_t& p, int6
 // CTAs per (batch, query block, head): enough to fill the GPU a few times over, never more than the
 // number of chunk blocks.  With many query blocks (prefill) one CTA walks all chunk blocks and the
 // pooled queries are computed once.
-inline int scan_ctas_per_unit(int64_t units, int chunk_blocks) {
+// `resident` (CTAs of the kernel the GPU holds at once; 0 = not given): with only a few waves of CTAs the last one
+// runs on a part-empty GPU (2048 units on 888 slots: three waves' time for 2.3 waves' work), so the chunk blocks of a
+// unit are split over 2 or 4 CTAs when that shortens the schedule by clearly more than the repeated prologue costs (measured:
+// 1 % per extra CTA with 256-token chunks, 5 % with 8-token chunks, whose CTAs are short).
+inline int scan_ctas_per_unit(int64_t units, int chunk_blocks, int resident = 0) {
   const int64_t want = (148 * 2 * 4 + units - 1) / units;
-  return (int)(want < 1 ? 1 : (want > chunk_blocks ? chunk_blocks : want));
+  int k = (int)(want < 1 ? 1 : (want > chunk_blocks ? chunk_blocks : want));
+  if (resident > 0 && k == 1 && units < 8LL * resident) {
+    auto cost = [&](int n) { return (double)((units * n + resident - 1) / resident) / n * (1.0 + 0.02 * (n - 1)); };
+    double best = cost(1);
+    for (int n = 2; n <= 4 && n <= chunk_blocks; n *= 2) {
+      if (cost(n) < best * 0.97) {
+        best = cost(n);
+        k = n;
+      }
+    }
+  }
+  return k;
 }
 
 // the same for a staged key row that is first rotated to table position `new_t` (in-kernel RoPE,

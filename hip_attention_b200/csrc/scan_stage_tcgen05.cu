@@ -422,7 +422,7 @@ int launch(const hipattn_scan_params_t& p, cudaStream_t stream) {
   const int BDST = cdiv(p.TQ, p.block_size_q);
   const int nblk_total = cdiv(p.n_chunks, 64);
   const int64_t units = (int64_t)p.B * p.H * BDST;
-  const int nblk = scan_ctas_per_unit(units, nblk_total);
+  const int nblk = scan_ctas_per_unit(units, nblk_total, 148 * (NR <= 32 ? (STREAM ? 5 : 6) : (NR <= 64 ? 4 : 3)));
   const int64_t grid = units * nblk;
   HIPATTN_REQUIRE(grid > 0 && grid < 0x7fffffffLL, HIPATTN_ERR_INVALID, "scan grid of %lld blocks", (long long)grid);
   auto kern = scan_stage_tcgen05_kernel<DT, D, NR, STREAM>;
