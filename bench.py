@@ -182,7 +182,12 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.samples, self.proc = index, [], None
+        self.index, self.samples, self.proc, self.t0 = index, [], None, 0.0
+
+    def mark(self):
+        """Samples received before this call are dropped: nvidia-smi is started early because it needs a moment to
+        deliver its first line, and only what it reports from here on describes the GPU under load."""
+        self.t0 = time.perf_counter()
 
     def start(self):
         try:
@@ -195,7 +200,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.samples.append(line.strip())
+            self.samples.append((time.perf_counter(), line.strip()))
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -204,7 +209,9 @@ class ClockSampler:
         self.proc.terminate()
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        for when, s in self.samples:
+            if when < self.t0:
+                continue
             f = [x.strip() for x in s.split(",")]
             if len(f) < 6:
                 continue
@@ -435,6 +442,9 @@ def run_prefill(a, w, dev, rank, world):
     lib = _lib.load()
     local = dev.index
     hs, kvs = kv_head_slice(rank, world, w["H"], w["HKV"])
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     q, k, v = make_qkv(w, dev, kvs)
     args = make_args(w)
     reduce = make_score_reduce()
@@ -456,11 +466,8 @@ def run_prefill(a, w, dev, rank, world):
             raise SystemExit(f"bench.py: device status word {st:#x} after {where}; the run is invalid")
 
     read_status(dev)
-    # clocks and throttle reasons are sampled from before the warm-up steps (nvidia-smi needs a moment to start) to the
-    # end of the timed steps
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    # clocks and throttle reasons: the samples from the first warm-up step to the end of the timed steps count
+    sampler.mark()
     for _ in range(max(a.warmup, 3)):
         out, md = step()
     barrier()
